@@ -1,0 +1,48 @@
+// C entry points of the kernel library.  Every function launches on the given
+// stream and returns 0, a cudaError_t (> 0) or a negative code from
+// common.cuh; exl3_last_error() gives the message of the calling thread's
+// last failure.  Element type codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+extern "C" {
+
+const char* exl3_last_error();
+int exl3_abi_version();
+
+int exl3_embed(const int* ids, const void* table, int table_dtype, float* h, int T, int H, int V,
+               float scale, cudaStream_t stream);
+int exl3_add_rmsnorm(float* h, const void* y, int y_dtype, float y_scale, const void* w, int w_dtype,
+                     float eps, void* out, int out_dtype, float out_scale, const int* rows, int n_rows,
+                     int H, cudaStream_t stream);
+int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, int rot, float pos_scale,
+                       const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                       void* k_pool, void* v_pool, int T, int nh, int nkv, int hd, int page, int write_kv,
+                       cudaStream_t stream);
+
+// y[M,N] = x[M,K] . w[N,K]^T (+ bias[N]); any sizes; float32 accumulation in a
+// fixed order over K.  in_dtype covers x, w and bias; out_dtype covers y.
+int exl3_gemm_simt(const void* x, const void* w, const void* bias, void* y, int in_dtype, int out_dtype,
+                   int M, int N, int K, cudaStream_t stream);
+// bfloat16 weights streamed once for M <= 16 rows of x (tensor-core mma, K % 8 == 0).
+int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
+                   int K, cudaStream_t stream);
+
+// Attention of single query tokens over the paged cache.  Token t belongs to
+// batch row tok_seq[t] and sits at position tok_pos[t]; it sees keys
+// max(0, pos - window + 1) .. pos (window 0: from 0).  n_splits > 1 cuts the
+// keys into chunks of split_keys and needs scratch; see attention_simt.cu.
+int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
+                     const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                     const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, float scale,
+                     int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                     cudaStream_t stream);
+size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
+
+int exl3_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream);
+int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature, int* out,
+                            int R, int V, cudaStream_t stream);
+}

@@ -1,0 +1,323 @@
+// Attention of query tokens over the paged key/value cache on the CUDA cores.
+//
+//   s[j] = (q . K[j]) * scale,  j in [max(0, pos - window + 1), pos]
+//   out  = sum_j softmax(s)[j] * V[j]
+//
+// as in the reference's call of scaled-dot-product attention with an additive
+// causal mask (src/model.cpp:539-548, 576-578); query head h reads key/value
+// head h / (heads / kv_heads).  Scores, running maximum, running sum and the
+// output accumulator are float32.
+//
+// One kernel serves whole prompts and single decoded tokens, in float32 and in
+// bfloat16.  Work item: (token, kv head, chunk of split_keys keys).  A chunk is
+// aligned to absolute positions, so the way keys are grouped, and therefore
+// every rounding, depends only on the token's own position: not on the batch,
+// not on how the tokens were cut into steps.  Inside a chunk the four warps
+// take pages in turn; inside a warp each group of lanes owns the keys
+// congruent to its index and keeps a private (max, sum, acc); the groups, the
+// warps and the chunks are merged in a fixed order.
+//
+// Cache layout: pool[page][kv_head][slot][head_dim], page = block_table[row][pos / page_size].
+#include "api.h"
+#include "common.cuh"
+
+#include <math.h>
+
+namespace exl3 {
+
+constexpr int ATT_WARPS = 4;
+
+// merge (mo, lo, ao) into (m, l, a)
+template <int N>
+__device__ inline void merge_state(float& m, float& l, float (&a)[N], float mo, float lo, const float (&ao)[N]) {
+  const float mn = fmaxf(m, mo);
+  if (mn == -INFINITY) return;                       // both empty
+  const float cs = expf(m - mn), co = expf(mo - mn);
+  l = l * cs + lo * co;
+#pragma unroll
+  for (int i = 0; i < N; ++i) a[i] = a[i] * cs + ao[i] * co;
+  m = mn;
+}
+
+// Record layout in shared memory and scratch: [hd] accumulator, then max, then sum.
+template <typename T, int GT, int R>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict__ out,
+                   const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
+                   const int* __restrict__ tok_seq, int nh, int nkv, int hd, int page, int window,
+                   float scale, int split_keys, int max_splits, float* __restrict__ scratch, int lpk) {
+  constexpr int VEC = Elem<T>::vec;
+  constexpr int NA = R * VEC;
+  extern __shared__ float smem[];                    // [ATT_WARPS][GT][hd + 2]
+  const int t = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
+  const int G = nh / nkv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kpw = 32 / lpk;                          // keys a warp handles at once
+  const int grp = lane / lpk, li = lane - grp * lpk;
+  const int pos = tok_pos[t];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int hi = pos + 1;
+  // this block's chunk of keys
+  int c_lo = lo, c_hi = hi;
+  if (split_keys > 0) {
+    const int c = lo / split_keys + sp;
+    c_lo = max(lo, c * split_keys);
+    c_hi = min(hi, (c + 1) * split_keys);
+  }
+  const int* bt = block_table + (int64_t)tok_seq[t] * bt_stride;
+  const int rec = hd + 2;
+
+  for (int h0 = 0; h0 < G; h0 += GT) {
+    // this lane's slice of the queries
+    float qv[GT][NA];
+#pragma unroll
+    for (int hh = 0; hh < GT; ++hh) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int d = (r * lpk + li) * VEC;
+        float tmp[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) tmp[e] = 0.0f;
+        if (d < hd && h0 + hh < G)
+          load_vec(q + (int64_t)t * q_row_stride + (int64_t)(g * G + h0 + hh) * hd + d, tmp);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qv[hh][r * VEC + e] = tmp[e];
+      }
+    }
+    float m[GT], l[GT], acc[GT][NA];
+#pragma unroll
+    for (int hh = 0; hh < GT; ++hh) {
+      m[hh] = -INFINITY;
+      l[hh] = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NA; ++i) acc[hh][i] = 0.0f;
+    }
+
+    if (c_lo < c_hi) {
+      const int first_page = c_lo / page, last_page = (c_hi - 1) / page;
+      for (int pi = first_page + warp; pi <= last_page; pi += ATT_WARPS) {
+        const int pg = bt[pi];
+        const int64_t page_base = ((int64_t)pg * nkv + g) * page * hd;
+        for (int jj = grp; jj < page; jj += kpw) {     // same trip count for every lane
+          const int j = pi * page + jj;
+          const bool valid = (j >= c_lo) && (j < c_hi) && (pg >= 0);
+          float kv[NA], vv[NA];
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const int d = (r * lpk + li) * VEC;
+            float tk[VEC], tv[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { tk[e] = 0.0f; tv[e] = 0.0f; }
+            if (valid && d < hd) {
+              load_vec(k_pool + page_base + (int64_t)jj * hd + d, tk);
+              load_vec(v_pool + page_base + (int64_t)jj * hd + d, tv);
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { kv[r * VEC + e] = tk[e]; vv[r * VEC + e] = tv[e]; }
+          }
+#pragma unroll
+          for (int hh = 0; hh < GT; ++hh) {
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NA; ++i) s = fmaf(qv[hh][i], kv[i], s);
+            for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (valid) {
+              s *= scale;
+              const float mn = fmaxf(m[hh], s);
+              const float corr = expf(m[hh] - mn);      // exp(-inf) = 0 on the first key
+              const float p = expf(s - mn);
+              l[hh] = l[hh] * corr + p;
+#pragma unroll
+              for (int i = 0; i < NA; ++i) acc[hh][i] = acc[hh][i] * corr + p * vv[i];
+              m[hh] = mn;
+            }
+          }
+        }
+      }
+    }
+    // merge the lane groups of this warp (butterfly: both partners compute the same sum)
+#pragma unroll
+    for (int hh = 0; hh < GT; ++hh) {
+      for (int o = lpk; o < 32; o <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m[hh], o);
+        const float lo2 = __shfl_xor_sync(0xffffffffu, l[hh], o);
+        float ao[NA];
+#pragma unroll
+        for (int i = 0; i < NA; ++i) ao[i] = __shfl_xor_sync(0xffffffffu, acc[hh][i], o);
+        // keep the operand order the same on both partners
+        if ((lane & o) == 0) {
+          merge_state<NA>(m[hh], l[hh], acc[hh], mo, lo2, ao);
+        } else {
+          float m2 = mo, l2 = lo2;
+          merge_state<NA>(m2, l2, ao, m[hh], l[hh], acc[hh]);
+          m[hh] = m2; l[hh] = l2;
+#pragma unroll
+          for (int i = 0; i < NA; ++i) acc[hh][i] = ao[i];
+        }
+      }
+    }
+    __syncthreads();                                   // previous pass has read smem
+    if (grp == 0) {
+#pragma unroll
+      for (int hh = 0; hh < GT; ++hh) {
+        float* recp = smem + (warp * GT + hh) * rec;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int d = (r * lpk + li) * VEC;
+          if (d < hd) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) recp[d + e] = acc[hh][r * VEC + e];
+          }
+        }
+        if (li == 0) { recp[hd] = m[hh]; recp[hd + 1] = l[hh]; }
+      }
+    }
+    __syncthreads();
+    // merge the warps in order 0, 1, 2, 3; thread per (head, feature)
+    for (int idx = threadIdx.x; idx < GT * hd; idx += blockDim.x) {
+      const int hh = idx / hd, d = idx - hh * hd;
+      if (h0 + hh >= G) continue;
+      float mm = -INFINITY, ll = 0.0f, aa = 0.0f;
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        const float* recp = smem + (w * GT + hh) * rec;
+        const float mo = recp[hd], lo2 = recp[hd + 1];
+        const float mn = fmaxf(mm, mo);
+        if (mn == -INFINITY) continue;
+        const float cs = expf(mm - mn), co = expf(mo - mn);
+        ll = ll * cs + lo2 * co;
+        aa = aa * cs + recp[d] * co;
+        mm = mn;
+      }
+      const int head = g * G + h0 + hh;
+      if (max_splits <= 1) {
+        Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+      } else {
+        float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
+        sc[d] = aa;
+        if (d == 0) { sc[hd] = mm; sc[hd + 1] = ll; }
+      }
+    }
+  }
+}
+
+// out[t, head, :] from the per-chunk records, merged in chunk order.
+template <typename T>
+__global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, int nh, int hd,
+                                    int max_splits) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int rec = hd + 2;
+  const float* base = scratch + ((int64_t)t * nh + head) * max_splits * rec;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float mm = -INFINITY, ll = 0.0f, aa = 0.0f;
+    for (int s = 0; s < max_splits; ++s) {
+      const float* recp = base + (int64_t)s * rec;
+      const float mo = recp[hd], lo2 = recp[hd + 1];
+      const float mn = fmaxf(mm, mo);
+      if (mn == -INFINITY) continue;
+      const float cs = expf(mm - mn), co = expf(mo - mn);
+      ll = ll * cs + lo2 * co;
+      aa = aa * cs + recp[d] * co;
+      mm = mn;
+    }
+    Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+  }
+}
+
+template <typename T, int GT, int R>
+static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const void* k_pool,
+                         const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                         const int* tok_seq, int T_, int nh, int nkv, int hd, int page, int window,
+                         float scale, int split_keys, int max_splits, float* scratch, int lpk,
+                         cudaStream_t stream) {
+  const size_t smem = (size_t)ATT_WARPS * GT * (hd + 2) * sizeof(float);
+  dim3 grid(T_, nkv, max_splits);
+  attn_tokens_kernel<T, GT, R><<<grid, ATT_WARPS * 32, smem, stream>>>(
+      static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
+      static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, page, window,
+      scale, split_keys, max_splits, scratch, lpk);
+  int rc = launch_status("attn_tokens");
+  if (rc) return rc;
+  if (max_splits > 1) {
+    attn_combine_kernel<T><<<dim3(T_, nh), 64, 0, stream>>>(scratch, static_cast<T*>(out), nh, hd, max_splits);
+    rc = launch_status("attn_combine");
+  }
+  return rc;
+}
+
+template <typename T>
+static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
+                    const int* block_table, int bt_stride, const int* tok_pos, const int* tok_seq, int T_,
+                    int nh, int nkv, int hd, int page, int window, float scale, int split_keys,
+                    int max_splits, float* scratch, cudaStream_t stream) {
+  constexpr int VEC = Elem<T>::vec;
+  const int vecs = hd / VEC;                          // 16-byte pieces per head row
+  int lpk = 1;
+  while (lpk < vecs && lpk < 32) lpk <<= 1;
+  const int R = ceil_div(vecs, lpk);
+  const int G = nh / nkv;
+#define EXL3_ATT(GT, RR)                                                                                 \
+  return launch_tokens<T, GT, RR>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, \
+                                  tok_seq, T_, nh, nkv, hd, page, window, scale, split_keys, max_splits, \
+                                  scratch, lpk, stream)
+  if (R == 1) {
+    if (G == 1) EXL3_ATT(1, 1);
+    if (G == 2) EXL3_ATT(2, 1);
+    EXL3_ATT(4, 1);
+  }
+  if (R == 2) {
+    if (G == 1) EXL3_ATT(1, 2);
+    if (G == 2) EXL3_ATT(2, 2);
+    EXL3_ATT(4, 2);
+  }
+#undef EXL3_ATT
+  set_error("attn_tokens: head_dim %d is too large for this kernel", hd);
+  return ERR_UNSUPPORTED;
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits) {
+  if (max_splits <= 1) return 0;
+  return (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
+}
+
+extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype,
+                                const void* k_pool, const void* v_pool, const int* block_table,
+                                int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                int hd, int page, int window, float scale, int split_keys, int max_splits,
+                                float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 16 || hd % 16 != 0 || page < 1 || window < 0 ||
+      max_splits < 1 || split_keys < 0 || (max_splits > 1 && split_keys == 0)) {
+    set_error("attn_tokens: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d (a multiple of 16) page=%d "
+              "window=%d split_keys=%d max_splits=%d", T, nh, nkv, hd, page, window, split_keys, max_splits);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (split_keys % page != 0) {
+    set_error("attn_tokens: split_keys %d must be a multiple of the page size %d", split_keys, page);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (nkv > 65535 || max_splits > 65535) { set_error("attn_tokens: grid too large"); return ERR_UNSUPPORTED; }
+  const int vec = dtype == DT_F32 ? 4 : 8;
+  if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || q_row_stride % vec != 0) {
+    set_error("attn_tokens: q, k and v must be 16-byte aligned with a row stride in 16-byte units");
+    return ERR_ALIGNMENT;
+  }
+  if (exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits) > scratch_bytes) {
+    set_error("attn_tokens: scratch of %zu bytes is too small, need %zu", scratch_bytes,
+              exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits));
+    return ERR_SCRATCH;
+  }
+  if (dtype == DT_F32)
+    return dispatch<float>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
+                           nh, nkv, hd, page, window, scale, split_keys, max_splits, scratch, stream);
+  if (dtype == DT_BF16)
+    return dispatch<__nv_bfloat16>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos,
+                                   tok_seq, T, nh, nkv, hd, page, window, scale, split_keys, max_splits,
+                                   scratch, stream);
+  set_error("attn_tokens: unsupported element type %d", dtype);
+  return ERR_UNSUPPORTED;
+}

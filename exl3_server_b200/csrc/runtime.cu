@@ -1,0 +1,31 @@
+// Error channel shared by the entry points.
+#include "api.h"
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+namespace exl3 {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+}  // namespace exl3
+
+extern "C" const char* exl3_last_error() { return exl3::g_error; }
+extern "C" int exl3_abi_version() { return 1; }

@@ -1,0 +1,4 @@
+"""The model, the step function and the generation loop."""
+from .batch import StepBatch, Workspace
+from .engine import Engine, StepEntry, StepError, load_model, resolve_dtype
+from .model import Model, plan_manifest

@@ -1,0 +1,145 @@
+"""The engine: a loaded model, its cache, and the one step function.
+
+``Engine.step`` is the only way tokens reach the model.  Generation, trace
+replay, the benchmark and the tests all drive it.  It is the reference's
+``forward_multi(tokens, cache)`` (src/model.cpp:514-628) for a batch of
+sequences with unequal lengths: each entry appends its tokens to its slot at
+the slot's current length; prompts go in one step, then one token per step.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.kv import SequenceCache
+from ..cache.pages import CacheError
+from ..config.fields import ConfigError, read_config_json
+from ..config.registry import resolve_architecture
+from ..ops.lib import KernelLibraryError, library
+from ..weights.loader import load_tensors
+from .batch import StepBatch, Workspace, pack_step
+from .model import Model, plan_manifest
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    """A step that is refused before anything runs."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Union[str, Sequence[int], None] = "last"   # "last", "all", explicit places, or None
+
+
+def resolve_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {dtype}")
+        return dtype
+    try:
+        return DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(DTYPES)}, got {dtype!r}") from None
+
+
+def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", device="cuda:0") -> Model:
+    """Reads config.json, finds the architecture in the registry, checks the
+    checkpoint against the plan's tensor list and builds the model."""
+    from .. import models  # noqa: F401  (registers the architectures)
+    dt = resolve_dtype(dtype)
+    obj = read_config_json(model_dir)
+    arch = resolve_architecture(obj)
+    cfg = arch.config_class.from_dict(obj)
+    plan = arch.build_plan(cfg)
+    tensors = load_tensors(model_dir, plan_manifest(plan), dt, device)
+    model = Model(plan, tensors, dt, device)
+    model.config = cfg
+    return model
+
+
+class Engine:
+    """A model with a cache sized for ``max_tokens`` tokens (each live
+    sequence's count rounded up to whole pages of 64)."""
+
+    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None):
+        if model.device.type != "cuda":
+            raise KernelLibraryError("the engine runs on a CUDA device only; there is no CPU path")
+        library()                                       # fail now, loudly, if the kernels are missing
+        self.model = model
+        self.device = model.device
+        self.cache: SequenceCache = model.new_cache(max_tokens, max_slots)
+        self.workspace = Workspace(self.device)
+        self.steps_run = 0
+
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
+                    max_slots: Optional[int] = None) -> "Engine":
+        return cls(load_model(model_dir, dtype, device), max_tokens, max_slots)
+
+    # -- sequences -----------------------------------------------------------
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # -- the step ------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the given tokens, as one batch, from the cache.  Returns the
+        float32 logits ``[wanted, vocab]`` in the order of the entries and of
+        their ``want`` lists (None when nothing is wanted)."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        vocab = self.model.vocab
+        limit = self.model.plan.max_positions
+        seen = set()
+        slots, starts, toks, wants = [], [], [], []
+        for e in entries:
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            try:
+                start = self.cache.length(e.slot)
+            except CacheError as err:
+                raise StepError(str(err)) from None
+            t = [int(x) for x in e.tokens]
+            if not t:
+                raise StepError(f"slot {e.slot}: a step entry needs at least one token")
+            bad = [x for x in t if not 0 <= x < vocab]
+            if bad:
+                raise StepError(f"slot {e.slot}: token id {bad[0]} is outside the vocabulary of {vocab}")
+            if limit and start + len(t) > limit:
+                raise StepError(f"slot {e.slot}: {start + len(t)} positions exceed max_position_embeddings {limit}")
+            if e.want is None:
+                w: List[int] = []
+            elif isinstance(e.want, str):
+                if e.want == "last":
+                    w = [len(t) - 1]
+                elif e.want == "all":
+                    w = list(range(len(t)))
+                else:
+                    raise StepError(f"want must be 'last', 'all', a list of places or None, got {e.want!r}")
+            else:
+                w = [int(x) for x in e.want]
+                if any(not 0 <= x < len(t) for x in w):
+                    raise StepError(f"slot {e.slot}: wanted place outside the {len(t)} tokens of this step")
+            slots.append(e.slot)
+            starts.append(start)
+            toks.append(t)
+            wants.append(w)
+        self.cache.reserve({s: st + len(t) for s, st, t in zip(slots, starts, toks)})
+        batch = pack_step(slots, starts, toks, wants, self.cache.block_tables(slots), self.workspace, self.device)
+        logits = self.model.forward(batch, self.cache)
+        for s, st, t in zip(slots, starts, toks):
+            self.cache.commit(s, st + len(t))
+        self.steps_run += 1
+        return logits

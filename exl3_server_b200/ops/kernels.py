@@ -1,0 +1,219 @@
+"""Python faces of the CUDA entry points.
+
+Every function takes torch tensors that live on the current CUDA device,
+launches on torch's current stream and raises ``KernelLibraryError`` when the
+entry point refuses its arguments.  There is no other implementation behind
+these names: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .lib import KernelLibraryError, library
+
+DT_F32, DT_BF16 = 0, 1
+
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_c_void_p = ctypes.c_void_p
+_c_size_t = ctypes.c_size_t
+_c_int64 = ctypes.c_int64
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return DT_F32
+    if dt == torch.bfloat16:
+        return DT_BF16
+    raise KernelLibraryError(f"kernels take float32 or bfloat16 tensors, got {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    if t is None:
+        return _c_void_p(0)
+    if not t.is_cuda:
+        raise KernelLibraryError("kernel called with a tensor that is not on a CUDA device; "
+                                 "there is no CPU implementation of the product path")
+    return _c_void_p(t.data_ptr())
+
+
+def _stream() -> _c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = library().exl3_last_error().decode("utf-8", "replace")
+        raise KernelLibraryError(f"{what} failed (code {rc}): {msg}")
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelLibraryError(f"{name} must be contiguous")
+
+
+# ---------------------------------------------------------------------------
+
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]] * scale`` as float32 rows."""
+    T = ids.numel()
+    V, H = table.shape
+    _contig(table, "table")
+    if ids.dtype != torch.int32:
+        raise KernelLibraryError("embed: ids must be int32")
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(library().exl3_embed(_ptr(ids), _ptr(table), _c_int(dtype_code(table.dtype)), _ptr(out),
+                                _c_int(T), _c_int(H), _c_int(V), _c_float(scale), _stream()), "embed")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, y: Optional[torch.Tensor], y_scale: float, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, out_scale: float = 1.0, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += y * y_scale`` (when y is given), then RMSNorm of the rows of h
+    (all, or those listed in ``rows``) times ``weight`` times ``out_scale``."""
+    T, H = h.shape
+    if h.dtype != torch.float32:
+        raise KernelLibraryError("add_rmsnorm: the residual stream must be float32")
+    _contig(h, "h")
+    if y is not None:
+        _contig(y, "y")
+        if y.shape != h.shape:
+            raise KernelLibraryError(f"add_rmsnorm: y is {tuple(y.shape)}, h is {tuple(h.shape)}")
+    if weight.numel() != H:
+        raise KernelLibraryError(f"add_rmsnorm: weight has {weight.numel()} elements, rows have {H}")
+    n = T if rows is None else rows.numel()
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelLibraryError("add_rmsnorm: rows must be int32")
+    if out is None:
+        out = torch.empty((n, H), dtype=out_dtype, device=h.device)
+    _check(library().exl3_add_rmsnorm(
+        _ptr(h), _ptr(y), _c_int(dtype_code(y.dtype) if y is not None else 0), _c_float(y_scale),
+        _ptr(weight), _c_int(dtype_code(weight.dtype)), _c_float(eps), _ptr(out),
+        _c_int(dtype_code(out.dtype)), _c_float(out_scale), _ptr(rows), _c_int(n), _c_int(H), _stream()),
+        "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    _contig(gate_up, "gate_up")
+    if out is None:
+        out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().exl3_silu_mul(_ptr(gate_up), _ptr(out), _c_int(dtype_code(gate_up.dtype)), _c_int(T),
+                                   _c_int(I), _stream()), "silu_mul")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos_scale: float,
+                  tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], heads: int, kv_heads: int,
+                  head_dim: int, page: int, write_kv: bool) -> None:
+    """Rotates q and k inside ``qkv`` and writes rotated k and v to the cache."""
+    T = qkv.shape[0]
+    _contig(qkv, "qkv")
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelLibraryError("rope_kv_write: qkv width does not match the head counts")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rot:
+        raise KernelLibraryError("rope_kv_write: inv_freq must be float32 with rot/2 entries")
+    if write_kv and (k_pool.dtype != qkv.dtype or v_pool.dtype != qkv.dtype):
+        raise KernelLibraryError("rope_kv_write: cache and activations differ in element type")
+    _check(library().exl3_rope_kv_write(
+        _ptr(qkv), _c_int(dtype_code(qkv.dtype)), _ptr(inv_freq), _c_int(rot), _c_float(pos_scale),
+        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), _c_int(block_table.stride(0)),
+        _ptr(k_pool) if write_kv else _c_void_p(0), _ptr(v_pool) if write_kv else _c_void_p(0), _c_int(T),
+        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(1 if write_kv else 0),
+        _stream()), "rope_kv_write")
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` on the CUDA cores, float32 accumulation in K order."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemm: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != w.dtype or (bias is not None and bias.dtype != w.dtype):
+        raise KernelLibraryError("gemm: x, w and bias must share an element type")
+    _contig(x, "x")
+    _contig(w, "w")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(library().exl3_gemm_simt(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(x.dtype)),
+                                    _c_int(dtype_code(out.dtype)), _c_int(M), _c_int(N), _c_int(K),
+                                    _stream()), "gemm_simt")
+    return out
+
+
+GEMV_MAX_ROWS = 16
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for at most 16 rows of x, weights read once."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemv: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemv_bf16: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(library().exl3_gemv_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                    _c_int(M), _c_int(N), _c_int(K), _stream()), "gemv_bf16")
+    return out
+
+
+def attn_tokens_scratch_bytes(T: int, heads: int, head_dim: int, max_splits: int) -> int:
+    lib = library()
+    lib.exl3_attn_tokens_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_attn_tokens_scratch_bytes(_c_int(T), _c_int(heads), _c_int(head_dim), _c_int(max_splits)))
+
+
+def attn_tokens(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
+                v_pool: torch.Tensor, block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                T: int, heads: int, kv_heads: int, head_dim: int, page: int, window: int, scale: float,
+                split_keys: int, max_splits: int, scratch: Optional[torch.Tensor]) -> torch.Tensor:
+    """Attention of T query tokens over the paged cache (see attention_simt.cu)."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelLibraryError("attn_tokens: q, cache and out differ in element type")
+    nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(library().exl3_attn_tokens(
+        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T),
+        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale),
+        _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _stream()), "attn_tokens")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelLibraryError("argmax: logits must be float32")
+    _contig(logits, "logits")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(library().exl3_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), _stream()), "argmax")
+    return out
+
+
+def sample_temperature(logits: torch.Tensor, uniform: torch.Tensor, temperature: float,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or uniform.dtype != torch.float32 or uniform.numel() != R:
+        raise KernelLibraryError("sample_temperature: logits [R,V] and uniform [R] must be float32")
+    _contig(logits, "logits")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(library().exl3_sample_temperature(_ptr(logits), _ptr(uniform), _c_float(1.0 / temperature),
+                                             _ptr(out), _c_int(R), _c_int(V), _stream()),
+           "sample_temperature")
+    return out

@@ -1,0 +1,103 @@
+"""The attention mixer: grouped-query attention over the paged cache.
+
+Per token: ``q, k, v = r Wq^T, r Wk^T, r Wv^T`` (+ biases when the checkpoint
+has them, src/model.cpp:558-560, 370-376); heads are contiguous slices of the
+projection (``feature = head * head_dim + d``, src/model.cpp:562-564); q and k
+get the position encoding; k (rotated) and v go to the cache
+(src/model.cpp:566-574); ``o = softmax(q K^T * scale + causal) V`` with query
+head h reading kv head ``h // (heads / kv_heads)`` (src/model.cpp:576-578);
+``y = concat_h(o) Wo^T`` (src/model.cpp:579-580).  ``window`` > 0 limits a
+query at position p to keys ``p - window + 1 .. p``.
+
+The three input projections are one fused matrix, so a step reads ``r`` once.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ops import kernels as K
+from ..weights.loader import TensorSpec
+from .base import BuildContext, KVRequest, StateRequest
+from .linear import Linear
+from .registry import position_class, register_mixer
+from .spec import MixerSpec, PositionSpec
+
+# Keys per work item of the attention kernel; a multiple of the cache's page size.
+SPLIT_KEYS = 256
+
+
+class Attention:
+    @staticmethod
+    def tensor_specs(spec: MixerSpec, prefix: str) -> List[TensorSpec]:
+        q, kv = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
+        out = [
+            TensorSpec(prefix + "q_proj.weight", (q, spec.width)),
+            TensorSpec(prefix + "k_proj.weight", (kv, spec.width)),
+            TensorSpec(prefix + "v_proj.weight", (kv, spec.width)),
+            TensorSpec(prefix + "o_proj.weight", (spec.width, q)),
+        ]
+        for name, n in (("q_proj", q), ("k_proj", kv), ("v_proj", kv), ("o_proj", spec.width)):
+            out.append(TensorSpec(prefix + name + ".bias", (n,), optional=True, init="zeros"))
+        return out
+
+    def __init__(self, spec: MixerSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        if spec.heads < 1 or spec.kv_heads < 1 or spec.heads % spec.kv_heads != 0:
+            raise ValueError(f"attention: {spec.heads} heads cannot share {spec.kv_heads} kv heads")
+        if spec.head_dim % 16 != 0:
+            raise ValueError(f"attention: head_dim must be a multiple of 16, got {spec.head_dim}")
+        self.spec = spec
+        self.ctx = ctx
+        names = ("q_proj", "k_proj", "v_proj")
+        w = torch.cat([tensors[prefix + n + ".weight"].to(ctx.dtype) for n in names], dim=0)
+        biases = [tensors.get(prefix + n + ".bias") for n in names]
+        b = None
+        if any(x is not None for x in biases):
+            sizes = (spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim, spec.kv_heads * spec.head_dim)
+            b = torch.cat([(x.to(ctx.dtype) if x is not None else torch.zeros(n, dtype=ctx.dtype, device=w.device))
+                           for x, n in zip(biases, sizes)])
+        self.qkv = Linear(w, b, ctx.dtype)
+        self.o = Linear(tensors[prefix + "o_proj.weight"], tensors.get(prefix + "o_proj.bias"), ctx.dtype)
+        pos = spec.position or PositionSpec(kind="none", dims=0)
+        self.position = position_class(pos.kind)(pos, spec.head_dim, ctx)
+        self.scale = spec.softmax_scale if spec.softmax_scale is not None else spec.head_dim ** -0.5
+
+    def cache_request(self) -> Optional[KVRequest]:
+        return KVRequest(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
+        s = self.spec
+        if kv is None:
+            raise RuntimeError("attention needs a cache view")
+        qkv = self.qkv(x)
+        self.position.rotate_and_store(qkv, batch, kv, s.heads, s.kv_heads, s.head_dim)
+        T = qkv.shape[0]
+        out = torch.empty((T, s.heads * s.head_dim), dtype=qkv.dtype, device=qkv.device)
+        self.attend(qkv, out, batch, kv)
+        return self.o(out)
+
+    def attend(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> None:
+        s = self.spec
+        T = qkv.shape[0]
+        split = max(SPLIT_KEYS, kv.page_size)
+        if split % kv.page_size:
+            split = kv.page_size * (split // kv.page_size + 1)
+        n = (batch.max_kv_len + split - 1) // split
+        if s.window > 0:
+            n = min(n, (s.window + split - 2) // split + 1)
+        n = max(1, n)
+        scratch = None
+        if n > 1:
+            scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
+        K.attn_tokens(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
+                      s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+
+    def weight_bytes(self) -> int:
+        return self.qkv.weight_bytes() + self.o.weight_bytes()
+
+
+register_mixer("attention", Attention)

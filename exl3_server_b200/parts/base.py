@@ -1,0 +1,72 @@
+"""What every part is built with and what it may ask of the cache.
+
+Interfaces (duck-typed; the classes below only document them):
+
+``Norm``           ``tensor_specs(spec, prefix)``; ``__init__(spec, tensors, prefix, ctx)``;
+                   ``add_norm(stream, rows=None, out_scale=1.0) -> r``: folds the stream's
+                   pending sublayer output into the float32 residual and returns the
+                   normed rows in the activation dtype.
+``Position``       ``__init__(spec, head_dim, ctx)``;
+                   ``rotate_and_store(qkv, batch, kv, heads, kv_heads, head_dim)``: encodes
+                   positions into q and k inside ``qkv`` and writes k, v to the cache view
+                   (when the view owns its storage).
+``Mixer``          ``tensor_specs(spec, prefix)``; ``__init__(spec, tensors, prefix, ctx)``;
+                   ``cache_request() -> KVRequest | None``; ``state_request() -> StateRequest | None``;
+                   ``forward(x, batch, kv, state) -> y`` with x, y ``[tokens, width]``.
+``FeedForward``    ``tensor_specs(spec, prefix)``; ``__init__(spec, tensors, prefix, ctx)``;
+                   ``forward(x, batch) -> y``.
+``Arrangement``    ``__init__(layer_spec, mixer, feed_forward, mixer_norm, feed_forward_norm)``;
+                   ``forward(stream, batch, kv, state)``.
+
+``batch`` is an ``engine.batch.StepBatch``; ``kv`` a ``cache.kv.KVLayerView`` or None;
+``state`` the layer's ``[slots, *shape]`` tensor or None (rows are picked with
+``batch.slot_ids``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class BuildContext:
+    dtype: torch.dtype            # activations and matrix weights: bfloat16 or float32
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class KVRequest:
+    """Keys and values for every position (window 0) or the last ``window``."""
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """A tensor of fixed size per sequence, zero when a sequence starts."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class ResidualStream:
+    """The float32 residual ``h`` plus at most one sublayer output that has
+    not been added yet.  The add is fused into the next norm."""
+
+    def __init__(self, h: torch.Tensor):
+        self.h = h
+        self.pending: Optional[torch.Tensor] = None
+        self.pending_scale: float = 1.0
+
+    def push(self, y: torch.Tensor, scale: float) -> None:
+        if self.pending is not None:
+            raise RuntimeError("residual stream already holds an output that was not folded in")
+        self.pending = y
+        self.pending_scale = scale
+
+    def take(self):
+        y, s = self.pending, self.pending_scale
+        self.pending, self.pending_scale = None, 1.0
+        return y, s

@@ -1,0 +1,53 @@
+"""A projection ``y = x @ W^T (+ b)`` with W kept in the checkpoint's
+``(out, in)`` order (the reference transposes to ``(in, out)`` at load,
+src/model.cpp:214-228; the kernels here read rows of W, so no transpose).
+
+Which kernel runs depends only on the element type and the row count:
+float32 goes through the CUDA-core kernel with a fixed order of summation
+(the true 32-bit path); bfloat16 with at most 16 rows streams the weights once
+through the tensor-core GEMV; larger bfloat16 products are the library's
+(cuBLAS through ``torch``), as the reference's are MLX's (src/model.cpp:549).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import kernels as K
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], dtype: torch.dtype):
+        if weight.dim() != 2:
+            raise ValueError(f"Linear: weight must be 2-dimensional, got {tuple(weight.shape)}")
+        self.weight = weight.to(dtype).contiguous()
+        self.bias = None if bias is None else bias.to(dtype).contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        self.dtype = dtype
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        out_dtype = out_dtype or self.dtype
+        M = x.shape[0]
+        if self.dtype == torch.float32:
+            return K.gemm_simt(x, self.weight, self.bias, torch.float32)
+        fast = self.in_features % 8 == 0
+        if fast and M <= K.GEMV_MAX_ROWS:
+            return K.gemv_bf16(x, self.weight, self.bias, out_dtype)
+        if out_dtype == torch.bfloat16 and fast:
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+        if fast:
+            # float32 results for many rows (logits at many positions): the
+            # GEMV in groups of 16 rows keeps float32 accumulators end to end
+            out = torch.empty((M, self.out_features), dtype=out_dtype, device=x.device)
+            for m0 in range(0, M, K.GEMV_MAX_ROWS):
+                m1 = min(M, m0 + K.GEMV_MAX_ROWS)
+                K.gemv_bf16(x[m0:m1], self.weight, self.bias, out_dtype, out=out[m0:m1])
+            return out
+        return K.gemm_simt(x, self.weight, self.bias, out_dtype)
+
+    def weight_bytes(self) -> int:
+        n = self.weight.numel() * self.weight.element_size()
+        if self.bias is not None:
+            n += self.bias.numel() * self.bias.element_size()
+        return n

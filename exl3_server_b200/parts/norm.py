@@ -1,0 +1,43 @@
+"""RMSNorm fused with the residual add.
+
+``r = h * rsqrt(mean(h^2) + eps) * w`` with the weight multiplying directly
+(no ``1 + w``), as the reference's ``mx::fast::rms_norm`` calls use it
+(src/model.cpp:556, 582, 589).  The sum of squares, the reciprocal root and the
+residual add ``h += scale * y`` are float32.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ops import kernels as K
+from ..weights.loader import TensorSpec
+from .base import BuildContext, ResidualStream
+from .registry import register_norm
+from .spec import NormSpec
+
+
+class RMSNorm:
+    @staticmethod
+    def tensor_specs(spec: NormSpec, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(prefix + "weight", (spec.width,), init="ones")]
+
+    def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        self.spec = spec
+        w = tensors[prefix + "weight"]
+        # a weight stored in 32-bit stays 32-bit; the kernel reads either
+        self.weight = w.contiguous() if w.dtype == torch.float32 else w.to(ctx.dtype).contiguous()
+        self.out_dtype = ctx.dtype
+
+    def add_norm(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
+                 out_scale: float = 1.0) -> torch.Tensor:
+        y, s = stream.take()
+        return K.add_rmsnorm(stream.h, y, s, self.weight, self.spec.eps, self.out_dtype,
+                             out_scale=out_scale, rows=rows)
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+
+register_norm("rms", RMSNorm)

@@ -1,0 +1,50 @@
+"""Position encodings applied to queries and keys.
+
+``rope``: half-split rotary embedding over the first ``dims`` features of each
+head: for d < dims/2, ``f_d = theta^(-2d/dims)``, angle ``a = pos * scale * f_d``,
+``x'[d] = x[d] cos a - x[d + dims/2] sin a``,
+``x'[d + dims/2] = x[d + dims/2] cos a + x[d] sin a`` — the reference's
+``mx::fast::rope(x, hd, traditional=false, theta, 1.0, offset)``
+(src/model.cpp:566-567).  The frequency table is computed once in float64 and
+kept as float32; angles and sin/cos are float32 in the kernel.  A scaled or
+extended variant only needs another table.
+
+``none``: no rotation; keys and values are still written to the cache.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels as K
+from .base import BuildContext
+from .registry import register_position
+from .spec import PositionSpec
+
+
+class RotaryPosition:
+    def __init__(self, spec: PositionSpec, head_dim: int, ctx: BuildContext):
+        if spec.dims % 2 != 0 or not 0 <= spec.dims <= head_dim:
+            raise ValueError(f"rope: dims {spec.dims} must be even and at most head_dim {head_dim}")
+        self.spec = spec
+        self.inv_freq = self.frequencies(spec).to(ctx.device)
+
+    @staticmethod
+    def frequencies(spec: PositionSpec) -> torch.Tensor:
+        d = torch.arange(0, spec.dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * d / max(1, spec.dims))
+        return f.to(torch.float32)
+
+    def rotate_and_store(self, qkv: torch.Tensor, batch, kv, heads: int, kv_heads: int, head_dim: int) -> None:
+        write = kv is not None and kv.owns
+        K.rope_kv_write(qkv, self.inv_freq, self.spec.dims, float(self.spec.scale), batch.tok_pos,
+                        batch.tok_seq, kv.block_table, kv.k if write else None, kv.v if write else None,
+                        heads, kv_heads, head_dim, kv.page_size, write)
+
+
+class NoPosition(RotaryPosition):
+    def __init__(self, spec: PositionSpec, head_dim: int, ctx: BuildContext):
+        super().__init__(PositionSpec(kind="none", dims=0), head_dim, ctx)
+
+
+register_position("rope", RotaryPosition)
+register_position("none", NoPosition)
