@@ -8,9 +8,11 @@ Entry points::
 """
 from . import models  # noqa: F401  (registers the architectures)
 from .config import ConfigError, LlamaConfig, register_architecture, resolve_architecture
-from .engine import Engine, Model, StepEntry, StepError, load_model
+from .engine import (Engine, GenerateOptions, GenerateResult, Model, StepEntry, StepError, generate,
+                     load_model)
+from .sampling import SampleOptions
 from .weights import WeightsError
 from .weights.random_init import write_random_model
 
-__all__ = ["ConfigError", "LlamaConfig", "register_architecture", "resolve_architecture", "Engine", "Model",
+__all__ = ["ConfigError", "LlamaConfig", "register_architecture", "resolve_architecture", "Engine", "Model", "GenerateOptions", "GenerateResult", "SampleOptions", "generate",
            "StepEntry", "StepError", "load_model", "WeightsError", "write_random_model"]

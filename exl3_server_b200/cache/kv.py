@@ -52,7 +52,8 @@ class KVGroup:
 
     def allocate(self, dtype: torch.dtype, device) -> None:
         r = self.request
-        shape = (len(self.owners), self.pool.n_pages, r.kv_heads, self.page_size, r.head_dim)
+        # one page more than the pool hands out: rows that only pad a batch write there
+        shape = (len(self.owners), self.pool.n_pages + 1, r.kv_heads, self.page_size, r.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
 
@@ -120,7 +121,17 @@ class SequenceCache:
             for g in self.groups:
                 g.allocate(dtype, device)
             for i, s in self._state_requests.items():
-                self.state[i] = torch.zeros((self.slots.n_slots, *s.shape), dtype=s.dtype, device=device)
+                # one row more than there are slots, for rows that only pad a batch
+                self.state[i] = torch.zeros((self.slots.n_slots + 1, *s.shape), dtype=s.dtype, device=device)
+
+    @property
+    def pad_page(self) -> int:
+        """A page no sequence owns; padding rows of a batch write and read it."""
+        return self.n_pages
+
+    @property
+    def pad_slot(self) -> int:
+        return self.slots.n_slots
 
     # -- slots ---------------------------------------------------------------
     def open(self) -> int:
@@ -165,9 +176,11 @@ class SequenceCache:
         for g, slot, n in plan:
             g.pages[slot].extend(g.pool.alloc(n))
 
-    def commit(self, slot: int, new_len: int) -> None:
-        """Records the new length and gives back pages that fell out of a window."""
+    def commit(self, slot: int, new_len: int) -> bool:
+        """Records the new length and gives back pages that fell out of a
+        window; returns whether any page was given back."""
         self.lengths[slot] = new_len
+        any_gone = False
         for g in self.groups:
             first = g.first_needed_page(new_len)
             pages = g.pages[slot]
@@ -176,6 +189,8 @@ class SequenceCache:
                 g.pool.free(gone)
                 for i in range(min(first, len(pages))):
                     pages[i] = -1
+                any_gone = True
+        return any_gone
 
     def truncate(self, slot: int, new_len: int) -> None:
         """Forgets the positions from ``new_len`` on (the reference's

@@ -11,6 +11,7 @@ extern "C" {
 
 const char* exl3_last_error();
 int exl3_abi_version();
+long long exl3_launch_count();
 
 int exl3_embed(const int* ids, const void* table, int table_dtype, float* h, int T, int H, int V,
                float scale, cudaStream_t stream);

@@ -2,12 +2,14 @@
 #include "api.h"
 #include "common.cuh"
 
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
 
 namespace exl3 {
 
 static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -22,6 +24,7 @@ int launch_status(const char* what) {
     set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
     return (int)e;
   }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }
 
@@ -29,3 +32,6 @@ int launch_status(const char* what) {
 
 extern "C" const char* exl3_last_error() { return exl3::g_error; }
 extern "C" int exl3_abi_version() { return 1; }
+// Kernel launches made through this library since it was loaded (launches
+// recorded into a CUDA graph count once, when they are captured).
+extern "C" long long exl3_launch_count() { return exl3::g_launches.load(std::memory_order_relaxed); }

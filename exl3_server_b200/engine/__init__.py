@@ -2,3 +2,4 @@
 from .batch import StepBatch, Workspace
 from .engine import Engine, StepEntry, StepError, load_model, resolve_dtype
 from .model import Model, plan_manifest
+from .generate import GenerateOptions, GenerateResult, generate, plan_batches

@@ -75,12 +75,32 @@ class Engine:
         self.device = model.device
         self.cache: SequenceCache = model.new_cache(max_tokens, max_slots)
         self.workspace = Workspace(self.device)
+        self.decode_runners = {}
         self.steps_run = 0
 
     @classmethod
     def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
                     max_slots: Optional[int] = None) -> "Engine":
         return cls(load_model(model_dir, dtype, device), max_tokens, max_slots)
+
+    @property
+    def stop_token_ids(self) -> List[int]:
+        return list(self.model.plan.stop_token_ids)
+
+    @property
+    def cache_tokens(self) -> int:
+        return self.cache.max_tokens
+
+    def generate(self, prompts, options=None, cancelled=None, on_token=None):
+        """See ``engine.generate.generate``."""
+        from .generate import generate
+        return generate(self, prompts, options, cancelled, on_token)
+
+    def decode_session(self, slots, max_new: int = 0):
+        """Sequences that go on one token per step from a CUDA graph; see
+        ``engine.decode.DecodeSession``."""
+        from .decode import DecodeSession
+        return DecodeSession(self, slots, None, max_new)
 
     # -- sequences -----------------------------------------------------------
     def open(self) -> int:
@@ -91,6 +111,23 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def _decode_step(self, slots, starts, toks, wants) -> Optional[torch.Tensor]:
+        """One token per entry: the recorded decode graph runs it (the same
+        model code and kernels, launched from a CUDA graph)."""
+        from .decode import runner_for
+        runner = runner_for(self, len(slots), max(starts) + 1)
+        runner.load(slots, starts, [t[0] for t in toks])
+        logits = runner.run(max(starts) + 1)
+        for s, st in zip(slots, starts):
+            self.cache.commit(s, st + 1)
+        self.steps_run += 1
+        rows = [i for i, w in enumerate(wants) for _ in w]
+        if not rows:
+            return None
+        if rows == list(range(len(slots))):
+            return logits[:len(slots)].clone()
+        return logits[torch.tensor(rows, device=logits.device)]
 
     # -- the step ------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -137,6 +174,8 @@ class Engine:
             toks.append(t)
             wants.append(w)
         self.cache.reserve({s: st + len(t) for s, st, t in zip(slots, starts, toks)})
+        if all(len(t) == 1 for t in toks):
+            return self._decode_step(slots, starts, toks, wants)
         batch = pack_step(slots, starts, toks, wants, self.cache.block_tables(slots), self.workspace, self.device)
         logits = self.model.forward(batch, self.cache)
         for s, st, t in zip(slots, starts, toks):

@@ -1,0 +1,157 @@
+"""The generation loop above the step function.
+
+Requests are run in batches, one batch after another, as many as there are
+requests.  The prompts of a batch, of unequal lengths, go through the model in
+one step; then every live request advances one token per step.  A request ends
+on a stop token (which is kept in its tokens), at ``max_tokens`` or when the
+caller cancels; its slot goes back to the cache at once and the others carry
+on.  This is the reference's serial loop (src/engine.cpp:341-353, stop rules of
+``Emitter::emit`` src/engine.cpp:103-109, reasons "stop" / "length" /
+"cancelled" src/engine.h:63) made batched; unlike the reference no forward
+pass is spent after a request's last token (src/engine.cpp:349-350).
+
+The loop only needs an object with ``open()``, ``close(slot)`` and
+``step(entries) -> logits`` and ``decode_session(slots, max_new)`` (an object
+with ``step(tokens) -> logits``, ``next_ids`` and ``close()``); its decisions are
+tested with a scripted one.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling.options import SampleOptions
+from ..sampling.sampler import RowSampler, sample_rows
+from .engine import StepEntry
+
+PAGE = 64
+
+
+@dataclass
+class GenerateOptions:
+    sample: SampleOptions = field(default_factory=SampleOptions)
+    max_tokens: int = 512                       # src/engine.h:50
+    ignore_eos: bool = False
+    stop_token_ids: Optional[Sequence[int]] = None   # None: the model's eos ids
+    max_batch: int = 64                         # most requests that start together
+
+
+@dataclass
+class GenerateResult:
+    tokens: List[int] = field(default_factory=list)   # generated ids, stop token included
+    finish_reason: str = ""                            # "stop" | "length" | "cancelled"
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+
+
+def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, cache_tokens: int) -> List[List[int]]:
+    """Splits request indices, in order, into batches that fit the cache: a
+    request may grow to its prompt plus ``max_tokens`` tokens, counted in whole
+    pages."""
+    def need(n: int) -> int:
+        return (n + max_tokens + PAGE - 1) // PAGE * PAGE
+
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, n in enumerate(prompt_lens):
+        if n == 0:
+            continue                              # answered without a forward pass
+        if need(n) > cache_tokens:
+            raise ValueError(f"request {i}: {n} prompt + {max_tokens} new tokens do not fit a cache of "
+                             f"{cache_tokens} tokens")
+        if cur and (len(cur) >= max_batch or used + need(n) > cache_tokens):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need(n)
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[GenerateOptions] = None,
+             cancelled: Optional[Callable[[], bool]] = None,
+             on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerateResult]:
+    """Generates for every prompt (lists of token ids).  ``on_token(request,
+    token)`` is called for each new token; ``cancelled()`` is polled once per
+    step."""
+    opt = options or GenerateOptions()
+    if opt.max_tokens < 0 or opt.max_batch < 1:
+        raise ValueError("max_tokens must be >= 0 and max_batch >= 1")
+    stops = set(opt.stop_token_ids if opt.stop_token_ids is not None else engine.stop_token_ids)
+    results = [GenerateResult(prompt_tokens=len(p)) for p in prompts]
+    for i, p in enumerate(prompts):
+        if len(p) == 0 or opt.max_tokens == 0:
+            results[i].finish_reason = "stop" if len(p) == 0 else "length"   # src/engine.cpp:227-230
+    todo = [len(p) if opt.max_tokens > 0 else 0 for p in prompts]
+    for batch in plan_batches(todo, opt.max_tokens, opt.max_batch, engine.cache_tokens):
+        _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
+    return results
+
+
+def _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token) -> None:
+    slots = {i: engine.open() for i in batch}
+    samplers = {i: RowSampler(opt.sample, i, prompts[i]) for i in batch}
+    live = list(batch)
+    session = None
+    try:
+        t0 = time.perf_counter()
+        logits = engine.step([StepEntry(slots[i], prompts[i], "last") for i in live])
+        argmax = None
+        first = True
+        d0 = t0
+        while live:
+            if cancelled is not None and cancelled():
+                for i in live:
+                    results[i].finish_reason = "cancelled"
+                break
+            picked = sample_rows(logits, [samplers[i] for i in live], argmax)
+            if first:
+                # the prefill ends when its logits have been used once
+                pf = time.perf_counter() - t0
+                for i in live:
+                    results[i].prefill_seconds = pf
+                d0 = time.perf_counter()
+                first = False
+            nxt = []
+            retired = False
+            for i, tok in zip(live, picked):
+                r = results[i]
+                r.tokens.append(tok)
+                r.completion_tokens += 1
+                if on_token is not None:
+                    on_token(i, tok)
+                if not opt.ignore_eos and tok in stops:
+                    r.finish_reason = "stop"
+                elif r.completion_tokens >= opt.max_tokens:
+                    r.finish_reason = "length"
+                if r.finish_reason:
+                    r.decode_seconds = time.perf_counter() - d0
+                    if session is not None:
+                        session.close()
+                        session = None
+                    engine.close(slots.pop(i))          # the slot is free for the next batch at once
+                    retired = True
+                else:
+                    nxt.append((i, tok))
+            live = [i for i, _ in nxt]
+            if not live:
+                break
+            if session is None or retired:
+                if session is not None:
+                    session.close()
+                remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
+                session = engine.decode_session([slots[i] for i in live], max_new=remaining)
+            logits = session.step([tok for _, tok in nxt])
+            argmax = session.next_ids
+        for i in live:                                   # cancelled rows
+            results[i].decode_seconds = time.perf_counter() - d0
+    finally:
+        if session is not None:
+            session.close()
+        for s in slots.values():
+            engine.close(s)

@@ -50,6 +50,13 @@ def _check(rc: int, what: str) -> None:
         raise KernelLibraryError(f"{what} failed (code {rc}): {msg}")
 
 
+def launch_count() -> int:
+    """Kernel launches made through the library so far."""
+    lib = library()
+    lib.exl3_launch_count.restype = ctypes.c_longlong
+    return int(lib.exl3_launch_count())
+
+
 def _contig(t: torch.Tensor, name: str) -> None:
     if not t.is_contiguous():
         raise KernelLibraryError(f"{name} must be contiguous")
