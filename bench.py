@@ -110,6 +110,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (stated in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 decode points")
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="run one part only (for profiling small cases); prints a short JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -184,6 +186,29 @@ def main() -> int:
         for s in slots:
             engine.close(s)
         return ms, launches, kv
+
+    if args.only == "decode":
+        ms, launches, _ = time_decode(B, C, Kst, W)
+        print(json.dumps({"only": "decode", "batch": B, "context": C, "layers": args.layers,
+                          "ms_per_step": ms / Kst, "tok_s": B * Kst / (ms / 1e3), "gpu_launches": int(launches)}))
+        return 0
+    if args.only == "prefill":
+        s = engine.open()
+        toks = prompts(1, args.prefill_tokens)[0]
+        for _ in range(W):
+            engine.step([E.StepEntry(s, toks, "last")])
+            engine.cache.truncate(s, 0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(Kst):
+            engine.step([E.StepEntry(s, toks, "last")])
+            engine.cache.truncate(s, 0)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / Kst
+        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "layers": args.layers, "ms": ms,
+                          "tok_s": args.prefill_tokens / (ms / 1e3)}))
+        return 0
 
     # ---- main: decode at the default batch and context ----------------------
     clocks = ClockSampler()

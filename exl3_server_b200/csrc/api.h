@@ -43,6 +43,13 @@ int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype, 
                      cudaStream_t stream);
 size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
 
+// Whole prompts on the tensor cores (bfloat16, head_dim 64 or 128, pages of 64); see attention_prefill.cu.
+int exl3_attn_prefill_supported(int dtype, int hd, int page);
+int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
+                      const void* v_pool, const int* block_table, int bt_stride, const int* row_start,
+                      const int* row_pos0, const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv,
+                      int hd, int page, int window, float scale, cudaStream_t stream);
+
 int exl3_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream);
 int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature, int* out,
                             int R, int V, cudaStream_t stream);

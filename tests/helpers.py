@@ -12,6 +12,7 @@ from exl3_server_b200 import LlamaConfig, write_random_model
 # Tiny configurations that differ in every size and option.
 #  A: MiniCPM-style; grouped heads 4/2, head 16, tied head, all three scale constants.
 #  B: plain Llama; one kv head, head 32, untied, other theta and eps, no scaling.
+#  D: heads of 64 (the tensor-core attention's shape), width 136, vocabulary 301.
 #  C: odd sizes: width 96, 6/3 heads of 48, vocabulary 263, a window of 24 keys on
 #     layers 0 and 2 (full attention on 1 and 3), biases on every projection.
 TINY: Dict[str, dict] = {
@@ -33,6 +34,13 @@ TINY: Dict[str, dict] = {
         sliding_window=24,
         layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]),
         norm_std=0.05, biases=True),
+    # D: heads of 64, the shape the tensor-core kernels take; a window on the last layer.
+    "D": dict(cfg=LlamaConfig(
+        hidden_size=136, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+        intermediate_size=208, vocab_size=301, tie_word_embeddings=True, rope_theta=100000.0,
+        rms_norm_eps=1e-5, scale_emb=2.0, scale_depth=1.0, dim_model_base=68, max_position_embeddings=4096,
+        sliding_window=80, layer_types=["full_attention", "sliding_attention"]),
+        norm_std=0.1, biases=False),
 }
 
 

@@ -1,0 +1,330 @@
+"""Each CUDA kernel alone against a plain float32/float64 torch computation of
+the same operation, at sizes other than the engine tests use (widths and
+vocabularies that are no power of two, head sizes in steps of 16, grouped
+heads, windows, ragged batches)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def K():
+    from exl3_server_b200.ops import kernels
+    return kernels
+
+
+def close(got, want, tol, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = float((got - want).abs().max() / max(1e-30, float(want.abs().max())))
+    assert err <= tol, f"{what}: relative error {err:.3e} > {tol:.0e}"
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1.2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    torch.manual_seed(0)
+    table = torch.randn(1003, 72, device=DEV).to(dtype)
+    ids = torch.tensor([0, 1002, 5, 5, 77], dtype=torch.int32, device=DEV)
+    out = K().embed(ids, table, 12.0)
+    assert out.dtype == torch.float32
+    close(out, table.float()[ids.long()] * 12.0, 1e-7, "embed")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [72, 2304, 1000])
+def test_add_rmsnorm(dtype, H):
+    torch.manual_seed(1)
+    T = 7
+    h = torch.randn(T, H, device=DEV)
+    y = torch.randn(T, H, device=DEV).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(dtype)
+    h0 = h.clone()
+    out = K().add_rmsnorm(h, y, 0.37, w, 1e-5, dtype, out_scale=0.5)
+    hn = h0.double() + y.double() * 0.37
+    close(h, hn, 1e-6, "residual")
+    want = hn * torch.rsqrt((hn * hn).mean(-1, keepdim=True) + 1e-5) * w.double() * 0.5
+    close(out, want, TOL[dtype], "norm")
+    # without a pending output, on listed rows only, float32 weight in the bfloat16 path
+    rows = torch.tensor([6, 2], dtype=torch.int32, device=DEV)
+    h1 = h.clone()
+    out = K().add_rmsnorm(h, None, 1.0, w.float(), 1e-5, dtype, rows=rows)
+    assert torch.equal(h, h1) and out.shape == (2, H)
+    hh = h1.double()[[6, 2]]
+    close(out, hh * torch.rsqrt((hh * hh).mean(-1, keepdim=True) + 1e-5) * w.double(), TOL[dtype], "rows")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    torch.manual_seed(2)
+    gu = (3 * torch.randn(5, 2 * 173, device=DEV)).to(dtype)
+    g, u = gu.double()[:, :173], gu.double()[:, 173:]
+    close(K().silu_mul(gu), g * torch.sigmoid(g) * u, TOL[dtype], "silu_mul")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,Kd", [(1, 50, 24), (5, 263, 96), (70, 130, 200), (3, 64, 7), (17, 33, 65)])
+def test_gemm_simt(dtype, M, N, Kd):
+    torch.manual_seed(3)
+    x = torch.randn(M, Kd, device=DEV).to(dtype)
+    w = torch.randn(N, Kd, device=DEV).to(dtype)
+    b = torch.randn(N, device=DEV).to(dtype)
+    want = x.double() @ w.double().T + b.double()
+    close(K().gemm_simt(x, w, b, dtype), want, TOL[dtype], "gemm")
+    if dtype == torch.bfloat16:
+        close(K().gemm_simt(x, w, None, torch.float32), x.double() @ w.double().T, 2e-6, "gemm f32 out")
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(4)
+    x = torch.randn(70, 300, device=DEV)
+    w = torch.randn(90, 300, device=DEV)
+    full = K().gemm_simt(x, w, None, torch.float32)
+    for r in (0, 13, 69):
+        assert torch.equal(K().gemm_simt(x[r:r + 1].contiguous(), w, None, torch.float32)[0], full[r])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,Kd", [(2304, 2304), (263, 96), (50, 40), (1000, 5768), (16, 8)])
+def test_gemv_bf16(M, N, Kd):
+    torch.manual_seed(5)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    want = x.double() @ w.double().T
+    close(K().gemv_bf16(x, w, None, torch.float32), want, 2e-6, "gemv f32 out")
+    close(K().gemv_bf16(x, w, b, torch.bfloat16), want + b.double(), TOL[torch.bfloat16], "gemv bf16 out")
+    # a row's result does not depend on the other rows
+    one = K().gemv_bf16(x[M - 1:].contiguous(), w, None, torch.float32)
+    assert torch.equal(one[0], K().gemv_bf16(x, w, None, torch.float32)[M - 1])
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    x = torch.zeros(17, 64, device=DEV).bfloat16()
+    w = torch.zeros(8, 64, device=DEV).bfloat16()
+    with pytest.raises(KernelLibraryError, match="M <= 16"):
+        K().gemv_bf16(x, w, None, torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="multiple of 8"):
+        K().gemv_bf16(x[:2, :60].contiguous(), w[:, :60].contiguous(), None, torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="not on a CUDA device"):
+        K().gemv_bf16(x.cpu(), w, None, torch.bfloat16)
+
+
+# -- attention ---------------------------------------------------------------
+
+class PagedCase:
+    """Sequences with random keys and values scattered over shuffled pages."""
+
+    def __init__(self, lens, new, nh, nkv, hd, dtype, seed=0, page=64, spare_pages=5):
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.new, self.nh, self.nkv, self.hd, self.page = lens, new, nh, nkv, hd, page
+        B = len(lens)
+        need = [(n + page - 1) // page for n in lens]
+        n_pages = sum(need) + spare_pages
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        width = max(need)
+        table = torch.full((B, width), -1, dtype=torch.int32)
+        self.k = [torch.randn(n, nkv, hd, generator=g).to(dtype) for n in lens]
+        self.v = [torch.randn(n, nkv, hd, generator=g).to(dtype) for n in lens]
+        kp = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)      # stale junk in unused places
+        vp = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)
+        it = iter(perm)
+        for b in range(B):
+            for i in range(need[b]):
+                pg = next(it)
+                table[b, i] = pg
+                a, e = i * page, min(lens[b], (i + 1) * page)
+                kp[pg, :, :e - a] = self.k[b][a:e].transpose(0, 1)
+                vp[pg, :, :e - a] = self.v[b][a:e].transpose(0, 1)
+        self.k_pool, self.v_pool, self.table = kp.to(DEV), vp.to(DEV), table.to(DEV)
+        T = sum(new)
+        self.q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        self.tok_seq = torch.tensor([b for b in range(B) for _ in range(new[b])], dtype=torch.int32, device=DEV)
+        self.tok_pos = torch.tensor([lens[b] - new[b] + i for b in range(B) for i in range(new[b])],
+                                    dtype=torch.int32, device=DEV)
+        starts = [0]
+        for n in new:
+            starts.append(starts[-1] + n)
+        self.row_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        self.row_pos0 = torch.tensor([lens[b] - new[b] for b in range(B)], dtype=torch.int32, device=DEV)
+        self.tile_seq = torch.tensor([b for b in range(B) for _ in range(0, new[b], 64)], dtype=torch.int32, device=DEV)
+        self.tile_q0 = torch.tensor([a for b in range(B) for a in range(0, new[b], 64)], dtype=torch.int32, device=DEV)
+
+    def reference(self, window, scale):
+        outs = []
+        t = 0
+        G = self.nh // self.nkv
+        for b, (n, m) in enumerate(zip(self.lens, self.new)):
+            k = self.k[b].double().repeat_interleave(G, dim=1)       # [n, nh, hd]
+            v = self.v[b].double().repeat_interleave(G, dim=1)
+            q = self.q[t:t + m].double()
+            s = torch.einsum("qhd,khd->hqk", q, k) * scale
+            qpos = torch.arange(n - m, n)[:, None]
+            kpos = torch.arange(n)[None, :]
+            allow = kpos <= qpos
+            if window > 0:
+                allow &= kpos > qpos - window
+            s = s.masked_fill(~allow, float("-inf"))
+            outs.append(torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v))
+            t += m
+        return torch.cat(outs).reshape(-1, self.nh * self.hd)
+
+
+ATT_SHAPES = [  # heads, kv heads, head_dim
+    (4, 2, 16), (4, 1, 32), (6, 3, 48), (3, 3, 64), (8, 2, 128), (5, 1, 80), (2, 2, 256),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 100])
+def test_attn_tokens(dtype, nh, nkv, hd, window):
+    # whole prompts and single tokens in one call, chunks of 128 keys so that several are merged
+    case = PagedCase(lens=[300, 64, 1, 700], new=[300, 1, 1, 40], nh=nh, nkv=nkv, hd=hd, dtype=dtype, seed=hd + nh)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    scale = 0.7 / math.sqrt(hd)
+    split = 128
+    n = (max(case.lens) + split - 1) // split
+    scratch = torch.empty(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    K().attn_tokens(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                    nh, nkv, hd, 64, window, scale, split, n, scratch)
+    close(out, case.reference(window, scale), 2e-6 if dtype == torch.float32 else 1e-2, "attn_tokens")
+
+
+def test_attn_tokens_finds_one_far_key_among_many():
+    """One key far back matches the query strongly: the output must be that
+    key's value, not an average, and a window that excludes it must lose it."""
+    nh = nkv = 2
+    hd = 64
+    case = PagedCase(lens=[900], new=[1], nh=nh, nkv=nkv, hd=hd, dtype=torch.float32, seed=3)
+    far = 37
+    kp, table = case.k_pool, case.table
+    pg = int(table[0, far // 64])
+    qv = case.q[0].clone()                                                    # [nh, hd]
+    kp[pg, :, far % 64] = (qv * 40.0 / qv.norm(dim=-1, keepdim=True)).to(DEV)  # score stands out by far
+    case.k[0][far] = kp[pg, :, far % 64].cpu()
+    q = (case.q.reshape(1, nh * hd) * 1.0).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    scratch = torch.empty(K().attn_tokens_scratch_bytes(1, nh, hd, 4) // 4, device=DEV)
+    K().attn_tokens(q, q.stride(0), out, kp, case.v_pool, table, case.tok_pos, case.tok_seq, 1, nh, nkv, hd, 64, 0,
+                    1.0, 256, 4, scratch)
+    close(out, case.v[0][far].reshape(1, -1), 1e-3, "far key")
+    close(out, case.reference(0, 1.0), 2e-6, "far key vs reference")
+    K().attn_tokens(q, q.stride(0), out, kp, case.v_pool, table, case.tok_pos, case.tok_seq, 1, nh, nkv, hd, 64, 800,
+                    1.0, 256, 4, scratch)
+    close(out, case.reference(800, 1.0), 2e-6, "window excludes the far key")
+    assert float((out.cpu() - case.v[0][far].reshape(1, -1)).abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 2, 128), (4, 1, 128)])
+@pytest.mark.parametrize("window", [0, 24, 100])
+def test_attn_prefill(nh, nkv, hd, window):
+    # prompts from position 0, a prompt continued at position 500, single tokens, a full tile, one row more
+    case = PagedCase(lens=[300, 64, 1, 700, 65, 128], new=[300, 64, 1, 200, 65, 1], nh=nh, nkv=nkv, hd=hd,
+                     dtype=torch.bfloat16, seed=hd + nh + window)
+    T = case.q.shape[0]
+    # q lives inside a wider fused buffer, as in the engine
+    buf = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    buf[:, :nh * hd] = case.q.reshape(T, nh * hd).to(DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    scale = 1.3 / math.sqrt(hd)
+    assert K().attn_prefill_supported(torch.bfloat16, hd, 64)
+    K().attn_prefill(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
+                     case.tile_seq, case.tile_q0, case.tile_seq.numel(), nh, nkv, hd, 64, window, scale)
+    close(out, case.reference(window, scale), 1e-2, "attn_prefill")
+
+
+def test_attn_prefill_is_refused_for_other_shapes():
+    assert not K().attn_prefill_supported(torch.float32, 64, 64)
+    assert not K().attn_prefill_supported(torch.bfloat16, 48, 64)
+    assert not K().attn_prefill_supported(torch.bfloat16, 64, 32)
+
+
+# -- rotary + cache write ------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (6, 3, 48, 48), (2, 1, 64, 32), (3, 3, 80, 0)])
+def test_rope_kv_write(dtype, nh, nkv, hd, rot):
+    torch.manual_seed(6)
+    page = 64
+    lens_before, new = [70, 0, 130], [3, 5, 1]
+    B = 3
+    n_pages = 8
+    table = torch.tensor([[5, 2, -1], [7, -1, -1], [0, 3, 6]], dtype=torch.int32, device=DEV)
+    T = sum(new)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+    orig = qkv.clone()
+    tok_seq = torch.tensor([b for b in range(B) for _ in range(new[b])], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lens_before[b] + i for b in range(B) for i in range(new[b])], dtype=torch.int32, device=DEV)
+    kp = torch.zeros(n_pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    theta = 2500.0
+    inv = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(1, rot))).float().to(DEV)
+    K().rope_kv_write(qkv, inv, rot, 1.0, tok_pos, tok_seq, table, kp, vp, nh, nkv, hd, page, True)
+
+    def rotate(x, pos):                                  # x [heads, hd] float64
+        if rot == 0:
+            return x
+        a = pos * inv.double().cpu()
+        c, s = torch.cos(a), torch.sin(a)
+        x0, x1, rest = x[:, :rot // 2], x[:, rot // 2:rot], x[:, rot:]
+        return torch.cat([x0 * c - x1 * s, x1 * c + x0 * s, rest], dim=-1)
+
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+    for t in range(T):
+        b, pos = int(tok_seq[t]), int(tok_pos[t])
+        row = orig[t].double().cpu()
+        q = row[:nh * hd].reshape(nh, hd)
+        k = row[nh * hd:(nh + nkv) * hd].reshape(nkv, hd)
+        v = row[(nh + nkv) * hd:].reshape(nkv, hd)
+        close(qkv[t, :nh * hd].reshape(nh, hd), rotate(q, pos), tol, "q")
+        pg = int(table[b, pos // page])
+        close(kp[pg, :, pos % page], rotate(k, pos), tol, "k in cache")
+        assert torch.equal(vp[pg, :, pos % page].cpu().double(), v), "v in cache"
+    written = sum(new) * nkv * hd
+    assert int((vp != 0).sum()) <= written               # nothing else was touched
+
+
+# -- sampling ------------------------------------------------------------------
+
+@pytest.mark.parametrize("V", [7, 1000, 122753])
+def test_argmax_first_maximum(V):
+    torch.manual_seed(7)
+    x = torch.randn(5, V, device=DEV)
+    x[1, V // 2] = 50.0
+    x[1, V - 1] = 50.0                                   # a tie: the first wins
+    x[2, 0] = 60.0
+    x[3, V - 1] = 70.0
+    got = K().argmax(x).cpu().tolist()
+    assert got == [int(torch.argmax(x[0])), V // 2, 0, V - 1, int(torch.argmax(x[4]))]
+
+
+def test_sample_temperature_is_inverse_cdf_in_index_order():
+    torch.manual_seed(8)
+    V = 5000
+    x = 3 * torch.randn(4, V, device=DEV)
+    temp = 0.8
+    p = torch.softmax(x.double() / temp, -1).cpu()
+    cdf = torch.cumsum(p, -1)
+    for u in (0.0, 0.013, 0.5, 0.77, 0.999999):
+        got = K().sample_temperature(x, torch.full((4,), u, device=DEV), temp).cpu().tolist()
+        for r in range(4):
+            want = int(torch.searchsorted(cdf[r], torch.tensor(u, dtype=torch.float64)))
+            # float32 running sums may move the boundary by one token of negligible mass
+            assert abs(got[r] - want) <= 1 or abs(float(cdf[r, got[r]]) - u) < 1e-4, (u, r, got[r], want)
+
+
+def test_sample_temperature_distribution():
+    x = torch.log(torch.tensor([[0.6, 0.3, 0.1]], device=DEV)).repeat(4096, 1)
+    u = torch.rand(4096, device=DEV)
+    got = K().sample_temperature(x, u, 1.0)
+    freq = torch.bincount(got.long(), minlength=3).double().cpu() / 4096
+    assert torch.allclose(freq, torch.tensor([0.6, 0.3, 0.1], dtype=torch.float64), atol=0.03)
