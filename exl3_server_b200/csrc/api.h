@@ -18,7 +18,8 @@ int exl3_embed(const int* ids, const void* table, int table_dtype, float* h, int
 int exl3_add_rmsnorm(float* h, const void* y, int y_dtype, float y_scale, const void* w, int w_dtype,
                      float eps, void* out, int out_dtype, float out_scale, const int* rows, int n_rows,
                      int H, cudaStream_t stream);
-int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+// interleave 0: gu = [gate (I) | up (I)]; 8: eight gate columns, then the eight up columns of the same features.
+int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, int interleave, cudaStream_t stream);
 int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, int rot, float pos_scale,
                        const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
                        void* k_pool, void* v_pool, int T, int nh, int nkv, int hd, int page, int write_kv,
@@ -29,8 +30,9 @@ int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, int rot, flo
 int exl3_gemm_simt(const void* x, const void* w, const void* bias, void* y, int in_dtype, int out_dtype,
                    int M, int N, int K, cudaStream_t stream);
 // bfloat16 weights streamed once for M <= 16 rows of x (tensor-core mma, K % 8 == 0).
+// epilogue 1: rows of w are 8 gate rows then 8 up rows, repeated; y[M, N/2] = silu(gate) * up.
 int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
-                   int K, cudaStream_t stream);
+                   int K, int epilogue, cudaStream_t stream);
 
 // Attention of single query tokens over the paged cache.  Token t belongs to
 // batch row tok_seq[t] and sits at position tok_pos[t]; it sees keys
@@ -50,7 +52,9 @@ int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype,
                       const int* row_pos0, const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv,
                       int hd, int page, int window, float scale, cudaStream_t stream);
 
-int exl3_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream);
+size_t exl3_argmax_scratch_bytes(int R, int V);
+int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,
+                cudaStream_t stream);
 int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature, int* out,
                             int R, int V, cudaStream_t stream);
 }

@@ -49,13 +49,16 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
                    float scale, int split_keys, int max_splits, float* __restrict__ scratch, int lpk) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
+  constexpr int U = R == 1 ? 4 : 2;                  // key groups in flight per lane
   extern __shared__ float smem[];                    // [ATT_WARPS][GT][hd + 2]
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
   const int G = nh / nkv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kpw = 32 / lpk;                          // keys a warp handles at once
   const int grp = lane / lpk, li = lane - grp * lpk;
-  const int pos = tok_pos[t];
+  const int pos = __ldcg(tok_pos + t);
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int hi = pos + 1;
   // this block's chunk of keys
@@ -80,7 +83,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 #pragma unroll
         for (int e = 0; e < VEC; ++e) tmp[e] = 0.0f;
         if (d < hd && h0 + hh < G)
-          load_vec(q + (int64_t)t * q_row_stride + (int64_t)(g * G + h0 + hh) * hd + d, tmp);
+          load_vec_cg(q + (int64_t)t * q_row_stride + (int64_t)(g * G + h0 + hh) * hd + d, tmp);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) qv[hh][r * VEC + e] = tmp[e];
       }
@@ -99,38 +102,54 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       for (int pi = first_page + warp; pi <= last_page; pi += ATT_WARPS) {
         const int pg = bt[pi];
         const int64_t page_base = ((int64_t)pg * nkv + g) * page * hd;
-        for (int jj = grp; jj < page; jj += kpw) {     // same trip count for every lane
-          const int j = pi * page + jj;
-          const bool valid = (j >= c_lo) && (j < c_hi) && (pg >= 0);
-          float kv[NA], vv[NA];
+        // U groups of keys at a time: all their loads are issued before the first is used
+        for (int jj0 = grp; jj0 < page; jj0 += kpw * U) {   // same trip count for every lane
+          uint4 rk[U][R], rv[U][R];
+          bool valid[U];
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const int d = (r * lpk + li) * VEC;
-            float tk[VEC], tv[VEC];
+          for (int u = 0; u < U; ++u) {
+            const int jj = jj0 + u * kpw;
+            const int j = pi * page + jj;
+            valid[u] = (jj < page) && (j >= c_lo) && (j < c_hi) && (pg >= 0);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) { tk[e] = 0.0f; tv[e] = 0.0f; }
-            if (valid && d < hd) {
-              load_vec(k_pool + page_base + (int64_t)jj * hd + d, tk);
-              load_vec(v_pool + page_base + (int64_t)jj * hd + d, tv);
+            for (int r = 0; r < R; ++r) {
+              const int d = (r * lpk + li) * VEC;
+              if (valid[u] && d < hd) {
+                rk[u][r] = load_raw_cg(k_pool + page_base + (int64_t)jj * hd + d);
+                rv[u][r] = load_raw_cg(v_pool + page_base + (int64_t)jj * hd + d);
+              } else {
+                rk[u][r] = make_uint4(0, 0, 0, 0);
+                rv[u][r] = make_uint4(0, 0, 0, 0);
+              }
             }
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) { kv[r * VEC + e] = tk[e]; vv[r * VEC + e] = tv[e]; }
           }
 #pragma unroll
-          for (int hh = 0; hh < GT; ++hh) {
-            float s = 0.0f;
+          for (int u = 0; u < U; ++u) {
+            float kv[NA], vv[NA];
 #pragma unroll
-            for (int i = 0; i < NA; ++i) s = fmaf(qv[hh][i], kv[i], s);
-            for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (valid) {
-              s *= scale;
-              const float mn = fmaxf(m[hh], s);
-              const float corr = expf(m[hh] - mn);      // exp(-inf) = 0 on the first key
-              const float p = expf(s - mn);
-              l[hh] = l[hh] * corr + p;
+            for (int r = 0; r < R; ++r) {
+              float tk[VEC], tv[VEC];
+              unpack_raw(rk[u][r], tk, (const T*)nullptr);
+              unpack_raw(rv[u][r], tv, (const T*)nullptr);
 #pragma unroll
-              for (int i = 0; i < NA; ++i) acc[hh][i] = acc[hh][i] * corr + p * vv[i];
-              m[hh] = mn;
+              for (int e = 0; e < VEC; ++e) { kv[r * VEC + e] = tk[e]; vv[r * VEC + e] = tv[e]; }
+            }
+#pragma unroll
+            for (int hh = 0; hh < GT; ++hh) {
+              float s = 0.0f;
+#pragma unroll
+              for (int i = 0; i < NA; ++i) s = fmaf(qv[hh][i], kv[i], s);
+              for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+              if (valid[u]) {
+                s *= scale;
+                const float mn = fmaxf(m[hh], s);
+                const float corr = expf(m[hh] - mn);    // exp(-inf) = 0 on the first key
+                const float p = expf(s - mn);
+                l[hh] = l[hh] * corr + p;
+#pragma unroll
+                for (int i = 0; i < NA; ++i) acc[hh][i] = acc[hh][i] * corr + p * vv[i];
+                m[hh] = mn;
+              }
             }
           }
         }
@@ -201,25 +220,35 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
   }
 }
 
-// out[t, head, :] from the per-chunk records, merged in chunk order.
+// out[t, head, :] from the per-chunk records.  With M the largest of the
+// chunks' maxima and w_s = exp(m_s - M): out = sum_s acc_s w_s / sum_s l_s w_s,
+// both sums in chunk order.  The records are read with independent loads.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, int nh, int hd,
                                     int max_splits) {
+  extern __shared__ float sw[];                      // [max_splits] weights, then [max_splits] sums
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, head = blockIdx.y;
   const int rec = hd + 2;
   const float* base = scratch + ((int64_t)t * nh + head) * max_splits * rec;
+  float* sl = sw + max_splits;
+  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) {
+    sw[s] = __ldcg(base + (int64_t)s * rec + hd);
+    sl[s] = __ldcg(base + (int64_t)s * rec + hd + 1);
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int s = 0; s < max_splits; ++s) mx = fmaxf(mx, sw[s]);
+  __syncthreads();
+  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) sw[s] = expf(sw[s] - mx);   // empty chunk: exp(-inf) = 0
+  __syncthreads();
+  float ll = 0.0f;
+  for (int s = 0; s < max_splits; ++s) ll += sl[s] * sw[s];
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float mm = -INFINITY, ll = 0.0f, aa = 0.0f;
-    for (int s = 0; s < max_splits; ++s) {
-      const float* recp = base + (int64_t)s * rec;
-      const float mo = recp[hd], lo2 = recp[hd + 1];
-      const float mn = fmaxf(mm, mo);
-      if (mn == -INFINITY) continue;
-      const float cs = expf(mm - mn), co = expf(mo - mn);
-      ll = ll * cs + lo2 * co;
-      aa = aa * cs + recp[d] * co;
-      mm = mn;
-    }
+    float aa = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < max_splits; ++s) aa += __ldcg(base + (int64_t)s * rec + d) * sw[s];
     Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
   }
 }
@@ -232,14 +261,15 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
                          cudaStream_t stream) {
   const size_t smem = (size_t)ATT_WARPS * GT * (hd + 2) * sizeof(float);
   dim3 grid(T_, nkv, max_splits);
-  attn_tokens_kernel<T, GT, R><<<grid, ATT_WARPS * 32, smem, stream>>>(
-      static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
-      static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, page, window,
-      scale, split_keys, max_splits, scratch, lpk);
+  launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
+             static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
+             static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, page, window,
+             scale, split_keys, max_splits, scratch, lpk);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
   if (max_splits > 1) {
-    attn_combine_kernel<T><<<dim3(T_, nh), 64, 0, stream>>>(scratch, static_cast<T*>(out), nh, hd, max_splits);
+    launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
+               (const float*)scratch, static_cast<T*>(out), nh, hd, max_splits);
     rc = launch_status("attn_combine");
   }
   return rc;

@@ -50,6 +50,37 @@ __device__ inline void load_vec(const __nv_bfloat16* p, float (&v)[8]) {
     v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+// The same through L2 only.  Kernels launched with programmatic dependent
+// launch overlap their predecessors on an SM, so L1 may still hold a line of a
+// buffer from before its producer rewrote it; everything a step's kernels
+// hand to each other is read this way.  Weights may use any load.
+__device__ inline void load_vec_cg(const float* p, float (&v)[4]) {
+  float4 r = __ldcg(reinterpret_cast<const float4*>(p));
+  v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+}
+__device__ inline void load_vec_cg(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 r = __ldcg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+// 16 raw bytes through L2 only, and their widening to floats afterwards: lets a
+// kernel put several loads in flight before it uses the first.
+__device__ inline uint4 load_raw_cg(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ inline void unpack_raw(const uint4& r, float (&v)[4], const float*) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+__device__ inline void unpack_raw(const uint4& r, float (&v)[8], const __nv_bfloat16*) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
 __device__ inline void store_vec(float* p, const float (&v)[4]) {
   *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
 }
@@ -95,5 +126,33 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Called after every launch by the entry points.
 int launch_status(const char* what);
+
+// Programmatic dependent launch.  A kernel launched with launch_pdl may start
+// while the kernel before it in the stream is still running; it must call
+// pdl_wait() before it reads anything that kernel wrote and before it writes
+// anything at all.  What comes before pdl_wait() may only touch data that no
+// kernel of the step writes (weights).  pdl_trigger() lets the next kernel in
+// the stream start early in the same way.  Without the launch attribute both
+// calls do nothing.
+__device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ inline void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);     // errors are read by launch_status()
+}
 
 }  // namespace exl3

@@ -5,6 +5,7 @@
 #include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace exl3 {
 
@@ -16,6 +17,14 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_error, sizeof(g_error), fmt, ap);
   va_end(ap);
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("EXL3_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 int launch_status(const char* what) {

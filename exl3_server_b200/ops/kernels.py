@@ -106,15 +106,16 @@ def add_rmsnorm(h: torch.Tensor, y: Optional[torch.Tensor], y_scale: float, weig
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleave: int = 0) -> torch.Tensor:
+    """``silu(gate) * up``.  ``interleave`` 0: ``gate_up = [gate | up]``; 8: eight
+    gate columns, then the eight up columns of the same features, and so on."""
     T, I2 = gate_up.shape
     I = I2 // 2
     _contig(gate_up, "gate_up")
     if out is None:
         out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
     _check(library().exl3_silu_mul(_ptr(gate_up), _ptr(out), _c_int(dtype_code(gate_up.dtype)), _c_int(T),
-                                   _c_int(I), _stream()), "silu_mul")
+                                   _c_int(I), _c_int(interleave), _stream()), "silu_mul")
     return out
 
 
@@ -162,8 +163,10 @@ GEMV_MAX_ROWS = 16
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x @ w.T (+ bias)`` for at most 16 rows of x, weights read once."""
+              out: Optional[torch.Tensor] = None, gated: bool = False) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` for at most 16 rows of x, weights read once.  With
+    ``gated`` the rows of w are eight gate rows then the eight up rows of the
+    same features, repeated, and ``silu(gate) * up`` comes out (N / 2 wide)."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -173,9 +176,10 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     _contig(x, "x")
     _contig(w, "w")
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
     _check(library().exl3_gemv_bf16(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)),
-                                    _c_int(M), _c_int(N), _c_int(K), _stream()), "gemv_bf16")
+                                    _c_int(M), _c_int(N), _c_int(K), _c_int(1 if gated else 0), _stream()),
+           "gemv_bf16")
     return out
 
 
@@ -227,7 +231,12 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     _contig(logits, "logits")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _check(library().exl3_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), _stream()), "argmax")
+    lib = library()
+    lib.exl3_argmax_scratch_bytes.restype = _c_size_t
+    need = int(lib.exl3_argmax_scratch_bytes(_c_int(R), _c_int(V)))
+    scratch = torch.empty(need // 4, dtype=torch.float32, device=logits.device) if need else None
+    _check(lib.exl3_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), _ptr(scratch), _c_size_t(need),
+                           _stream()), "argmax")
     return out
 
 

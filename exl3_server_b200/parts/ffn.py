@@ -31,18 +31,31 @@ class SwiGLU:
 
     def __init__(self, spec: FeedForwardSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
         self.spec = spec
-        w = torch.cat([tensors[prefix + "gate_proj.weight"].to(ctx.dtype),
-                       tensors[prefix + "up_proj.weight"].to(ctx.dtype)], dim=0)
+        wg = tensors[prefix + "gate_proj.weight"].to(ctx.dtype)
+        wu = tensors[prefix + "up_proj.weight"].to(ctx.dtype)
         bg, bu = tensors.get(prefix + "gate_proj.bias"), tensors.get(prefix + "up_proj.bias")
-        b = None
-        if bg is not None or bu is not None:
-            z = torch.zeros(spec.inner, dtype=ctx.dtype, device=w.device)
-            b = torch.cat([(bg.to(ctx.dtype) if bg is not None else z), (bu.to(ctx.dtype) if bu is not None else z)])
+        z = torch.zeros(spec.inner, dtype=ctx.dtype, device=wg.device)
+        has_bias = bg is not None or bu is not None
+        bg = bg.to(ctx.dtype) if bg is not None else z
+        bu = bu.to(ctx.dtype) if bu is not None else z
+        # Rows in eights: eight gate rows, then the eight up rows of the same
+        # features.  A 16-row tile of the decode projection then holds both halves
+        # of eight features and applies silu(gate) * up before it writes.
+        self.interleave = 8 if spec.inner % 8 == 0 else 0
+        if self.interleave:
+            n = spec.inner // 8
+            w = torch.stack([wg.view(n, 8, -1), wu.view(n, 8, -1)], dim=1).reshape(2 * spec.inner, -1)
+            b = torch.stack([bg.view(n, 8), bu.view(n, 8)], dim=1).reshape(-1) if has_bias else None
+        else:
+            w = torch.cat([wg, wu], dim=0)
+            b = torch.cat([bg, bu]) if has_bias else None
         self.gate_up = Linear(w, b, ctx.dtype)
         self.down = Linear(tensors[prefix + "down_proj.weight"], tensors.get(prefix + "down_proj.bias"), ctx.dtype)
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        return self.down(K.silu_mul(self.gate_up(x)))
+        if self.interleave and self.gate_up.streams_weights(x.shape[0]):
+            return self.down(self.gate_up.gated(x))
+        return self.down(K.silu_mul(self.gate_up(x), interleave=self.interleave))
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()

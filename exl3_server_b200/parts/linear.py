@@ -46,6 +46,16 @@ class Linear:
             return out
         return K.gemm_simt(x, self.weight, self.bias, out_dtype)
 
+    def streams_weights(self, rows: int) -> bool:
+        """Whether ``rows`` rows of input go through the weight-streaming GEMV."""
+        return self.dtype == torch.bfloat16 and self.in_features % 8 == 0 and rows <= K.GEMV_MAX_ROWS
+
+    def gated(self, x: torch.Tensor) -> torch.Tensor:
+        """For a weight whose rows are eight gate rows, then the eight up rows
+        of the same features, and so on: ``silu(gate) * up`` in one kernel
+        (only when ``streams_weights``)."""
+        return K.gemv_bf16(x, self.weight, self.bias, self.dtype, gated=True)
+
     def weight_bytes(self) -> int:
         n = self.weight.numel() * self.weight.element_size()
         if self.bias is not None:

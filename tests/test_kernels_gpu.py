@@ -104,6 +104,26 @@ def test_gemv_bf16(M, N, Kd):
     assert torch.equal(one[0], K().gemv_bf16(x, w, None, torch.float32)[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,Kd", [(176, 64), (5760, 2304), (200, 96)])
+def test_gemv_gated_and_interleaved_silu(M, I, Kd):
+    torch.manual_seed(9)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    wg = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    wu = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    bg, bu = torch.randn(I, device=DEV).bfloat16(), torch.randn(I, device=DEV).bfloat16()
+    n = I // 8
+    w = torch.stack([wg.view(n, 8, Kd), wu.view(n, 8, Kd)], dim=1).reshape(2 * I, Kd).contiguous()
+    b = torch.stack([bg.view(n, 8), bu.view(n, 8)], dim=1).reshape(-1).contiguous()
+    g = x.double() @ wg.double().T + bg.double()
+    u = x.double() @ wu.double().T + bu.double()
+    want = g * torch.sigmoid(g) * u
+    close(K().gemv_bf16(x, w, b, torch.bfloat16, gated=True), want, TOL[torch.bfloat16], "gated gemv")
+    close(K().gemv_bf16(x, w, b, torch.float32, gated=True), want, 2e-6, "gated gemv f32 out")
+    gu = K().gemv_bf16(x, w, b, torch.float32)
+    close(K().silu_mul(gu, interleave=8), want, 2e-6, "interleaved silu_mul")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(17, 64, device=DEV).bfloat16()
@@ -251,7 +271,8 @@ def test_attn_prefill_is_refused_for_other_shapes():
 # -- rotary + cache write ------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (6, 3, 48, 48), (2, 1, 64, 32), (3, 3, 80, 0)])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (6, 3, 48, 48), (2, 1, 64, 32), (3, 3, 80, 0),
+                                           (2, 1, 32, 24), (36, 36, 64, 64)])
 def test_rope_kv_write(dtype, nh, nkv, hd, rot):
     torch.manual_seed(6)
     page = 64
