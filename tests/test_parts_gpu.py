@@ -1,0 +1,319 @@
+"""Each part alone against the plain implementation's function for it, and a
+toy architecture, defined here, that is registered, built and stepped without
+any change to the framework: a mixer with per-sequence state of its own beside
+attention layers, a layer that runs twice and a layer that reads another
+layer's keys and values."""
+import json
+import math
+import os
+from dataclasses import dataclass
+from typing import Dict, List
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import batched_trace, rel_err, run_trace, tail_trace, whole_trace
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def ctx(dtype):
+    from exl3_server_b200.parts import BuildContext
+    return BuildContext(dtype=dtype, device=DEV)
+
+
+def one_sequence_batch(cache, n, start=0):
+    """A step of n tokens for one fresh sequence (positions start..)."""
+    from exl3_server_b200.engine.batch import Workspace, pack_step
+    slot = cache.open()
+    if start:
+        cache.reserve({slot: start})
+        cache.commit(slot, start)
+    cache.reserve({slot: start + n})
+    return pack_step([slot], [start], [[0] * n], [[n - 1]], cache.block_tables([slot]), Workspace(DEV), DEV), slot
+
+
+TOLS = {torch.float32: 3e-6, torch.bfloat16: 2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from exl3_server_b200.parts import NormSpec, ResidualStream, norm_class
+    torch.manual_seed(0)
+    H = 200
+    w = (1 + 0.2 * torch.randn(H)).to(dtype)
+    part = norm_class("rms")(NormSpec("rms", H, 3e-6), {"n.weight": w.to(DEV)}, "n.", ctx(dtype))
+    h = torch.randn(5, H, device=DEV)
+    y = torch.randn(5, H, device=DEV).to(dtype)
+    stream = ResidualStream(h.clone())
+    stream.push(y, 0.5)
+    r = part.add_norm(stream)
+    hn = h.double().cpu() + 0.5 * y.double().cpu()
+    assert stream.pending is None and rel_err(stream.h.cpu().numpy(), hn.numpy()) < 1e-6
+    assert rel_err(r.float().cpu().numpy(), P.rms_norm(hn, w.double(), 3e-6).numpy()) <= TOLS[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_position_part_and_cache_write(dtype):
+    from exl3_server_b200.cache import SequenceCache
+    from exl3_server_b200.parts import KVRequest, PositionSpec, position_class
+    torch.manual_seed(1)
+    nh, nkv, hd, n, start = 4, 2, 32, 70, 60
+    cache = SequenceCache([(KVRequest(nkv, hd), None, None)], 512, dtype=dtype, device=DEV)
+    batch, slot = one_sequence_batch(cache, n, start)
+    part = position_class("rope")(PositionSpec("rope", dims=hd, theta=5000.0), hd, ctx(dtype))
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, device=DEV).to(dtype)
+    orig = qkv.double().cpu()
+    kv = cache.view(0, batch.block_tables)
+    part.rotate_and_store(qkv, batch, kv, nh, nkv, hd)
+    pos = torch.arange(start, start + n)
+    q = orig[:, :nh * hd].view(n, nh, hd).transpose(0, 1)
+    k = orig[:, nh * hd:(nh + nkv) * hd].view(n, nkv, hd).transpose(0, 1)
+    v = orig[:, (nh + nkv) * hd:].view(n, nkv, hd)
+    want_q = P.rope(q, pos, 5000.0).transpose(0, 1).reshape(n, -1)
+    want_k = P.rope(k, pos, 5000.0)                     # [nkv, n, hd]
+    # Angles are float32 by design: the frequency and the product pos * f are each rounded to
+    # 24 bits, so an angle near position p is off by up to 2 * p * 2^-24 radians, and a rotated
+    # value by that times its size.  The plain implementation's angles are float64.
+    tol = max(TOLS[dtype], 2 * (start + n) * 2.0 ** -24)
+    assert rel_err(qkv[:, :nh * hd].float().cpu().numpy(), want_q.numpy()) <= tol
+    pages = cache.groups[0].pages[slot]
+    for i, p in enumerate(range(start, start + n)):
+        got_k = kv.k[pages[p // 64], :, p % 64].float().cpu()
+        got_v = kv.v[pages[p // 64], :, p % 64].double().cpu()
+        assert rel_err(got_k.numpy(), want_k[:, i].numpy()) <= tol
+        assert torch.equal(got_v, v[i])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 20])
+def test_attention_part(dtype, window):
+    from exl3_server_b200.cache import SequenceCache
+    from exl3_server_b200.parts import MixerSpec, PositionSpec, mixer_class
+    torch.manual_seed(2)
+    H, nh, nkv, hd, n = 72, 6, 2, 16, 90
+    spec = MixerSpec("attention", width=H, heads=nh, kv_heads=nkv, head_dim=hd, window=window,
+                     position=PositionSpec("rope", dims=hd, theta=300.0))
+    names = {"q_proj": (nh * hd, H), "k_proj": (nkv * hd, H), "v_proj": (nkv * hd, H), "o_proj": (H, nh * hd)}
+    t = {}
+    for nm, shape in names.items():
+        t[f"a.{nm}.weight"] = (torch.randn(shape) / math.sqrt(shape[1])).to(dtype).to(DEV)
+        t[f"a.{nm}.bias"] = (0.1 * torch.randn(shape[0])).to(dtype).to(DEV)
+    part = mixer_class("attention")(spec, t, "a.", ctx(dtype))
+    cache = SequenceCache([(part.cache_request(), part.state_request(), None)], 512, dtype=dtype, device=DEV)
+    batch, _ = one_sequence_batch(cache, n)
+    x = torch.randn(n, H, device=DEV).to(dtype)
+    y = part.forward(x, batch, cache.view(0, batch.block_tables), None)
+    w = {k: v.double().cpu() for k, v in t.items()}
+    xd = x.double().cpu()
+    q = P.linear(xd, w["a.q_proj.weight"], w["a.q_proj.bias"]).view(n, nh, hd).transpose(0, 1)
+    k = P.linear(xd, w["a.k_proj.weight"], w["a.k_proj.bias"]).view(n, nkv, hd).transpose(0, 1)
+    v = P.linear(xd, w["a.v_proj.weight"], w["a.v_proj.bias"]).view(n, nkv, hd).transpose(0, 1)
+    pos = torch.arange(n)
+    o = P.attention(P.rope(q, pos, 300.0), P.rope(k, pos, 300.0), v, window).transpose(0, 1).reshape(n, -1)
+    want = P.linear(o, w["a.o_proj.weight"], w["a.o_proj.bias"])
+    assert rel_err(y.float().cpu().numpy(), want.numpy()) <= TOLS[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inner,rows", [(176, 3), (100, 3), (176, 40)])
+def test_feed_forward_part(dtype, inner, rows):
+    """inner 100 is not a multiple of 8 (plain layout); 40 rows take the large-batch path."""
+    from exl3_server_b200.parts import FeedForwardSpec, feed_forward_class
+    torch.manual_seed(3)
+    H = 64
+    t = {"f.gate_proj.weight": (torch.randn(inner, H) / 8).to(dtype).to(DEV),
+         "f.up_proj.weight": (torch.randn(inner, H) / 8).to(dtype).to(DEV),
+         "f.down_proj.weight": (torch.randn(H, inner) / 10).to(dtype).to(DEV),
+         "f.gate_proj.bias": (0.1 * torch.randn(inner)).to(dtype).to(DEV)}
+    part = feed_forward_class("swiglu")(FeedForwardSpec("swiglu", H, inner), t, "f.", ctx(dtype))
+    x = torch.randn(rows, H, device=DEV).to(dtype)
+    y = part.forward(x, None)
+    w = {k: v.double().cpu() for k, v in t.items()}
+    want = P.swiglu(x.double().cpu(), w["f.gate_proj.weight"], w["f.up_proj.weight"], w["f.down_proj.weight"],
+                    bg=w["f.gate_proj.bias"])
+    assert rel_err(y.float().cpu().numpy(), want.numpy()) <= TOLS[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head(dtype):
+    from exl3_server_b200.parts import EmbeddingSpec, HeadSpec, NormSpec, norm_class
+    from exl3_server_b200.parts.embedding import Embedding, Head
+    torch.manual_seed(4)
+    V, H = 263, 96
+    E = torch.randn(V, H).to(dtype)
+    wn = (1 + 0.1 * torch.randn(H)).to(dtype)
+    t = {"emb": E.to(DEV), "n.weight": wn.to(DEV)}
+    emb = Embedding(EmbeddingSpec(V, H, 12.0, "emb"), t, ctx(dtype))
+    head = Head(HeadSpec(V, H, input_divisor=3.0, tied=True, name="lm"), t, emb, ctx(dtype))
+    norm = norm_class("rms")(NormSpec("rms", H, 1e-5), t, "n.", ctx(dtype))
+    ids = torch.tensor([3, 262, 0, 77], dtype=torch.int32, device=DEV)
+    stream = emb.forward(ids)
+    h = P.embedding(ids.long().cpu(), E.double(), 12.0)
+    assert rel_err(stream.h.cpu().numpy(), h.numpy()) < 1e-6
+    rows = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    logits = head.forward(stream, norm, rows)
+    assert logits.dtype == torch.float32 and logits.shape == (2, V)
+    want = P.linear(P.rms_norm(h[[3, 1]], wn.double(), 1e-5) / 3.0, E.double())
+    assert rel_err(logits.cpu().numpy(), want.numpy()) <= TOLS[dtype]
+
+
+# -- a toy architecture defined outside the framework --------------------------
+
+@dataclass
+class ToyConfig:
+    width: int
+    vocab: int
+    decay: float
+    layout: List[str]                 # per layer: "ema" or "attn"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["width"], d["vocab"], d["decay"], list(d["layout"]))
+
+    def to_dict(self):
+        return {"architectures": ["ToyEmaLM"], "model_type": "toy_ema", "width": self.width, "vocab": self.vocab,
+                "decay": self.decay, "layout": self.layout}
+
+
+class EmaMixer:
+    """y_t = (a * s_{t-1} + (1 - a) * x_t) * w, with the running mean s kept
+    per sequence in the cache's fixed-size state (float32)."""
+
+    @staticmethod
+    def tensor_specs(spec, prefix):
+        from exl3_server_b200.weights import TensorSpec
+        return [TensorSpec(prefix + "scale", (spec.width,), init="ones")]
+
+    def __init__(self, spec, tensors, prefix, ctx):
+        self.spec = spec
+        self.a = float(spec.params["decay"])
+        self.w = tensors[prefix + "scale"].float()
+
+    def cache_request(self):
+        return None
+
+    def state_request(self):
+        from exl3_server_b200.parts import StateRequest
+        return StateRequest((self.spec.width,), torch.float32)
+
+    def forward(self, x, batch, kv, state):
+        a = self.a
+        xf = x.float()
+        if batch.max_new == 1:                               # one token per row: safe inside a CUDA graph
+            idx = batch.slot_ids.long()
+            s = a * state[idx] + (1 - a) * xf
+            state.index_copy_(0, idx, s)
+            return (s * self.w).to(x.dtype)
+        out = torch.empty_like(xf)
+        t0 = 0
+        for slot, n in zip(batch.host_slots, batch.host_new):
+            s = state[slot].clone()
+            for i in range(n):
+                s = a * s + (1 - a) * xf[t0 + i]
+                out[t0 + i] = s * self.w
+            state[slot] = s
+            t0 += n
+        return out.to(x.dtype)
+
+
+def toy_plan(cfg: ToyConfig):
+    from exl3_server_b200.parts import (EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerSpec, MixerSpec, ModelPlan,
+                                        NormSpec, PositionSpec, ScheduleEntry)
+    layers = []
+    for i, kind in enumerate(cfg.layout):
+        p = f"toy.{i}."
+        if kind == "ema":
+            mixer = MixerSpec("test_ema", width=cfg.width, params={"decay": cfg.decay})
+        else:
+            mixer = MixerSpec("attention", width=cfg.width, heads=2, kv_heads=1, head_dim=16,
+                              position=PositionSpec("rope", dims=16, theta=100.0))
+        layers.append(LayerSpec("prenorm", mixer, FeedForwardSpec("swiglu", cfg.width, 2 * cfg.width),
+                                NormSpec("rms", cfg.width, 1e-5), NormSpec("rms", cfg.width, 1e-5), 0.5,
+                                names={"mixer": p + "mix.", "feed_forward": p + "ff.", "mixer_norm": p + "n1.",
+                                       "feed_forward_norm": p + "n2."}))
+    n = len(layers)
+    # every layer once, then layer 0 again (it has state or a cache of its own for the second run),
+    # then the last attention layer once more, reading the keys and values of its first run
+    schedule = [ScheduleEntry(i) for i in range(n)] + [ScheduleEntry(0)]
+    last_attn = max(i for i, k in enumerate(cfg.layout) if k == "attn")
+    schedule.append(ScheduleEntry(last_attn, cache_from=last_attn))
+    return ModelPlan("ToyEmaLM", EmbeddingSpec(cfg.vocab, cfg.width, 1.0, "toy.emb"), layers, schedule,
+                     NormSpec("rms", cfg.width, 1e-5), "toy.norm.", HeadSpec(cfg.vocab, cfg.width, 1.0, True, "toy.head"),
+                     max_positions=0)
+
+
+def toy_plain_logits(w: Dict[str, torch.Tensor], cfg: ToyConfig, ids: List[int]) -> torch.Tensor:
+    """The toy model on one whole sequence, float64, plain loops."""
+    w = {k: v.double() for k, v in w.items()}
+    L = len(ids)
+    h = w["toy.emb"][torch.tensor(ids)]
+    n = len(cfg.layout)
+    last_attn = max(i for i, k in enumerate(cfg.layout) if k == "attn")
+    kv_of = {}
+    for si, li in enumerate(list(range(n)) + [0, last_attn]):
+        p = f"toy.{li}."
+        r = P.rms_norm(h, w[p + "n1.weight"], 1e-5)
+        if cfg.layout[li] == "ema":
+            s = torch.zeros(cfg.width, dtype=P.F)             # this run of the layer has its own state
+            y = torch.empty_like(r)
+            for t in range(L):
+                s = cfg.decay * s + (1 - cfg.decay) * r[t]
+                y[t] = s * w[p + "mix.scale"]
+        else:
+            q = P.linear(r, w[p + "mix.q_proj.weight"]).view(L, 2, 16).transpose(0, 1)
+            k = P.linear(r, w[p + "mix.k_proj.weight"]).view(L, 1, 16).transpose(0, 1)
+            v = P.linear(r, w[p + "mix.v_proj.weight"]).view(L, 1, 16).transpose(0, 1)
+            pos = torch.arange(L)
+            q, k = P.rope(q, pos, 100.0), P.rope(k, pos, 100.0)
+            if si == n + 1:
+                k, v = kv_of[last_attn]                         # reads the first run's keys and values
+            else:
+                kv_of[li] = (k, v)
+            y = P.linear(P.attention(q, k, v).transpose(0, 1).reshape(L, -1), w[p + "mix.o_proj.weight"])
+        h = h + 0.5 * y
+        r = P.rms_norm(h, w[p + "n2.weight"], 1e-5)
+        h = h + 0.5 * P.swiglu(r, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["toy.norm.weight"], 1e-5), w["toy.emb"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    from exl3_server_b200 import Engine
+    from exl3_server_b200.config import register_architecture, unregister_architecture
+    from exl3_server_b200.engine.model import plan_manifest
+    from exl3_server_b200.parts import register_mixer, unregister
+    from exl3_server_b200.weights import write_safetensors
+    from exl3_server_b200.weights.random_init import random_tensors
+    cfg = ToyConfig(width=32, vocab=50, decay=0.8, layout=["ema", "attn", "ema", "attn"])
+    register_mixer("test_ema", EmaMixer)
+    register_architecture(["ToyEmaLM", "toy_ema"], ToyConfig, toy_plan)
+    try:
+        folder = str(tmp_path)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg.to_dict(), f)
+        tensors = dict(random_tensors(plan_manifest(toy_plan(cfg)), seed=3, std=0.15, norm_std=0.1))
+        write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+        # two groups of needs: attention layers share one key/value group; ema layers have state only
+        assert len(eng.cache.groups) == 1 and len(eng.cache.state) == 3       # layer 0 runs twice: two states
+        assert eng.cache.entry_owns == [False, True, False, True, False, False]
+        rng = np.random.default_rng(0)
+        reqs = {f"r{i}": rng.integers(0, cfg.vocab, n).tolist() for i, n in enumerate([70, 5, 33, 1])}
+        want = {rid: toy_plain_logits(tensors, cfg, t).numpy() for rid, t in reqs.items()}
+        tol = 1e-5 if dtype == "float32" else 5e-2
+        ids = list(reqs)
+        traces = [whole_trace(reqs), tail_trace(reqs, 32),
+                  batched_trace(reqs, [[ids[0], ids[1], ids[3]], [ids[2], ids[1]]],
+                                {ids[0]: 60, ids[1]: 2, ids[2]: 33, ids[3]: 1})]
+        for trace in traces:
+            got = run_trace(eng, trace)
+            for rid in got:
+                assert rel_err(got[rid], want[rid]) <= tol, rid
+        assert eng.cache.tokens_held() == 0
+    finally:
+        unregister_architecture(["ToyEmaLM", "toy_ema"])
+        unregister("mixer", "test_ema")
