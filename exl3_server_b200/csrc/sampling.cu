@@ -215,3 +215,68 @@ extern "C" int exl3_sample_temperature(const float* logits, const float* uniform
   sample_temperature_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, uniform, inv_temperature, out, V);
   return launch_status("sample_temperature");
 }
+
+// ---------------------------------------------------------------------------
+// The entry point that allocates nothing (see no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace exl3 {
+
+// Partial maxima for up to 64 rows x 256 chunks of 2048 logits: 64 * 256 floats,
+// then 64 * 256 ints.  In host code this name is only a handle for
+// cudaGetSymbolAddress, not a device address.
+static __device__ __align__(256) unsigned char g_argmax_static_scratch[EXL3_ARGMAX_STATIC_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static void* g_static_scratch_ptr[STATIC_MAX_DEVICES] = {};
+static std::mutex g_static_scratch_mutex;
+
+// The device address of the array on the current device, looked up once per device.
+static int static_scratch(void** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_error("argmax_static: cudaGetDevice failed: %s", cudaGetErrorString(e)); return (int)e; }
+  if (dev < 0 || dev >= STATIC_MAX_DEVICES) { set_error("argmax_static: device %d is out of range", dev); return ERR_UNSUPPORTED; }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_argmax_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("argmax_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : ERR_UNSUPPORTED;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  *ptr = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace exl3
+
+extern "C" int exl3_argmax_static(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (R < 0 || V < 1) { set_error("argmax_static: bad sizes rows=%d vocab=%d", R, V); return ERR_BAD_ARGUMENT; }
+  if (R > EXL3_ARGMAX_STATIC_MAX_ROWS || V > EXL3_ARGMAX_STATIC_MAX_VOCAB) {
+    set_error("argmax_static: rows=%d vocab=%d exceed the built-in scratch (at most %d rows, vocab %d)", R, V,
+              EXL3_ARGMAX_STATIC_MAX_ROWS, EXL3_ARGMAX_STATIC_MAX_VOCAB);
+    return ERR_SCRATCH;
+  }
+  void* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  // Same two kernels as exl3_argmax, for every vocabulary size, so that the
+  // array is what the second kernel reads.  Every (row, chunk) entry that the
+  // second kernel reads is written by the first in this call.
+  const int nchunks = ceil_div(V, ARGMAX_CHUNK);
+  float* pv = static_cast<float*>(scratch);
+  int* pi = reinterpret_cast<int*>(pv + (size_t)R * nchunks);
+  launch_pdl(argmax_partial_kernel, dim3(nchunks, R), dim3(ARGMAX_THREADS), 0, stream, logits, pv, pi, V, nchunks);
+  rc = launch_status("argmax_static (partial)");
+  if (rc) return rc;
+  launch_pdl(argmax_final_kernel, dim3(R), dim3(ARGMAX_THREADS), 0, stream, (const float*)pv, (const int*)pi, out,
+             nchunks);
+  return launch_status("argmax_static (final)");
+}
