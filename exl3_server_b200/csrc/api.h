@@ -34,6 +34,13 @@ int exl3_gemm_simt(const void* x, const void* w, const void* bias, void* y, int 
 int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
                    int K, int epilogue, cudaStream_t stream);
 
+// bfloat16 GEMM on tcgen05 tensor cores with TMA loads (K and N multiples of 8); epilogue 1 as in
+// exl3_gemv_bf16 (N a multiple of 16, output N/2 wide).  exl3_gemm_tc_status() returns and clears the
+// code a kernel left when one of its bounded waits ran out (0: none).
+int exl3_gemm_tc(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int epilogue,
+                 cudaStream_t stream);
+int exl3_gemm_tc_status();
+
 // Attention of single query tokens over the paged cache.  Token t belongs to
 // batch row tok_seq[t] and sits at position tok_pos[t]; it sees keys
 // max(0, pos - window + 1) .. pos (window 0: from 0).  n_splits > 1 cuts the
@@ -47,6 +54,7 @@ size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
 
 // Whole prompts on the tensor cores (bfloat16, head_dim 64 or 128, pages of 64); see attention_prefill.cu.
 int exl3_attn_prefill_supported(int dtype, int hd, int page);
+int exl3_attn_prefill_tile(int hd);
 int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
                       const void* v_pool, const int* block_table, int bt_stride, const int* row_start,
                       const int* row_pos0, const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv,

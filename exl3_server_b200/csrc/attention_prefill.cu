@@ -3,12 +3,13 @@
 //
 // Same mathematics as attention_simt.cu (the reference's masked
 // scaled-dot-product attention, src/model.cpp:539-548, 576-578), organised as a
-// streaming softmax: a block owns 64 consecutive queries of one sequence and
-// one head; each of its 4 warps owns 16 query rows.  It walks the sequence's
+// streaming softmax: a block owns 128 (heads of 64) or 64 (heads of 128)
+// consecutive queries of one sequence and one head; each of its 4 warps owns
+// 32 or 16 query rows.  It walks the sequence's
 // key pages (64 keys per page) from the first page any of its queries may see
 // to the page of its last query.  Per page: S = Q K^T with mma.m16n8k16, mask,
 // running max / sum update in registers, O += P V.  K and V pages are copied
-// to shared memory with cp.async, double buffered, in an XOR-swizzled layout
+// to shared memory with cp.async, several pages ahead, in an XOR-swizzled layout
 // that ldmatrix reads without bank conflicts.
 //
 // Requires head_dim 64 or 128 and a page size of 64; other shapes go through
@@ -20,9 +21,11 @@
 
 namespace exl3 {
 
-constexpr int PF_BQ = 64;       // queries per block
+constexpr int PF_BQ = 64;       // queries per block of 4 warps
+#ifndef PF_WARPS_64
+#define PF_WARPS_64 4            // warps per block for heads of 64 (16 query rows each)
+#endif
 constexpr int PF_BK = 64;       // keys per step = page size
-constexpr int PF_THREADS = 128;
 
 __device__ inline void cp_async16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -60,30 +63,35 @@ __device__ inline int swz(int row, int chunk) {
   return row * HD + ((chunk ^ (row & 7)) << 3);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(PF_THREADS)
+// MT: 16-row tiles per warp; a block owns 64 * MT queries.  With MT = 2 every K
+// and V fragment read from shared memory feeds two mma instructions.
+template <int HD, int MT, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                     const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
                     const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
+  constexpr int BQ = 16 * MT * WARPS;
+  constexpr int PF_THREADS = WARPS * 32;
   constexpr int CH = HD / 8;                         // 16-byte chunks per row
   constexpr int KS = HD / 16;                        // k16 steps over the head dimension
   constexpr int NB = PF_BK / 8;                      // n8 blocks of keys per page
   constexpr int DB = HD / 8;                         // n8 blocks of output features
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
-  __nv_bfloat16* sK = sQ + PF_BQ * HD;                                       // [2][64][HD]
-  __nv_bfloat16* sV = sK + 2 * PF_BK * HD;                                   // [2][64][HD]
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [BQ][HD]
+  __nv_bfloat16* sK = sQ + BQ * HD;                                          // [STAGES][64][HD]
+  __nv_bfloat16* sV = sK + STAGES * PF_BK * HD;                              // [STAGES][64][HD]
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // tiles are listed by rising position; the ones with most keys to visit start first
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = row_start[b + 1] - row_start[b];
   const int pos0 = row_pos0[b];
   const int g = head / (nh / nkv);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
-  const int rows = min(PF_BQ, n_new - q0);           // valid queries in this tile
+  const int rows = min(BQ, n_new - q0);              // valid queries in this tile
   const int p_first = pos0 + q0, p_last = pos0 + q0 + rows - 1;
   const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   const int page_lo = k_lo / PF_BK, page_hi = p_last / PF_BK;
@@ -91,7 +99,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
 
   // Q tile -> shared (rows past the end repeat the last valid row; they are never stored)
   const __nv_bfloat16* qbase = q + (int64_t)(row_start[b] + q0) * q_row_stride + (int64_t)head * HD;
-  for (int c = tid; c < PF_BQ * CH; c += PF_THREADS) {
+  for (int c = tid; c < BQ * CH; c += PF_THREADS) {
     const int r = c / CH, ch = c - r * CH;
     cp_async16(sQ + swz<HD>(r, ch), qbase + (int64_t)min(r, rows - 1) * q_row_stride + ch * 8);
   }
@@ -107,143 +115,176 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
       cp_async16(dv + swz<HD>(r, ch), vp + r * HD + ch * 8);
     }
   };
-  load_page(page_lo, 0);
-  cp_async_commit();
+  // STAGES - 1 pages are in flight ahead of the one being used
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (page_lo + st <= page_hi) load_page(page_lo + st, st);
+    cp_async_commit();
+  }
 
-  uint32_t qf[KS][4];
-  float o[DB][4];
+  uint32_t qf[MT][KS][4];
+  float o[MT][DB][4];
+  float m_run[MT][2], l_run[MT][2];
 #pragma unroll
-  for (int i = 0; i < DB; ++i)
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  // positions of this thread's two query rows
-  const int r_a = warp * 16 + gid, r_b = r_a + 8;
-  const int p_a = p_first + r_a, p_b = p_first + r_b;
+    for (int i = 0; i < DB; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[mt][i][j] = 0.0f;
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.0f;
+  }
+  const int wrow = warp * 16 * MT;                    // this warp's first row in the tile
 
   for (int pi = page_lo; pi <= page_hi; ++pi) {
-    const int stage = (pi - page_lo) & 1;
-    if (pi < page_hi) load_page(pi + 1, stage ^ 1);
+    const int stage = (pi - page_lo) % STAGES;
+    if (pi + STAGES - 1 <= page_hi) load_page(pi + STAGES - 1, (pi - page_lo + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     if (pi == page_lo) {
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks)
-        ldmatrix_x4(qf[ks], sQ + swz<HD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+          ldmatrix_x4(qf[mt][ks], sQ + swz<HD>(wrow + mt * 16 + (lane & 15), ks * 2 + (lane >> 4)));
     }
     const __nv_bfloat16* tk = sK + stage * PF_BK * HD;
     const __nv_bfloat16* tv = sV + stage * PF_BK * HD;
-
-    // S = Q K^T for 16 rows x 64 keys
-    float s[NB][4];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) s[nb][j] = 0.0f;
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-      for (int nb2 = 0; nb2 < NB / 2; ++nb2) {
-        uint32_t kb[4];
-        const int krow = nb2 * 16 + (lane & 7) + ((lane >> 4) << 3);
-        ldmatrix_x4(kb, tk + swz<HD>(krow, ks * 2 + ((lane >> 3) & 1)));
-        mma_16816(s[nb2 * 2], qf[ks], kb[0], kb[1]);
-        mma_16816(s[nb2 * 2 + 1], qf[ks], kb[2], kb[3]);
-      }
-    }
-    // scale (to base 2), mask
     const int key0 = pi * PF_BK;
-    const bool need_mask = (key0 + PF_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
+    // a warp whose rows all lie before this page has nothing to do here
+    const bool warp_active = key0 <= p_first + wrow + 16 * MT - 1;
+    if (warp_active) {
+      // S = Q K^T for 16 * MT rows x 64 keys
+      float s[MT][NB][4];
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float v = s[nb][j] * scale_log2;
-        if (need_mask) {
-          const int key = key0 + nb * 8 + tig * 2 + (j & 1);
-          const int p = (j < 2) ? p_a : p_b;
-          if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) s[mt][nb][j] = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int nb2 = 0; nb2 < NB / 2; ++nb2) {
+          uint32_t kb[4];
+          const int krow = nb2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+          ldmatrix_x4(kb, tk + swz<HD>(krow, ks * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816(s[mt][nb2 * 2], qf[mt][ks], kb[0], kb[1]);
+            mma_16816(s[mt][nb2 * 2 + 1], qf[mt][ks], kb[2], kb[3]);
+          }
         }
-        s[nb][j] = v;
       }
-    }
-    // running max and sum for the two rows of this thread
+      // scale (to base 2), mask, running max and sum
+      const bool need_mask = (key0 + PF_BK - 1 > p_first + wrow) || (window > 0 && key0 <= p_last - window);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float mx = -INFINITY;
+      for (int mt = 0; mt < MT; ++mt) {
+        const int p_a = p_first + wrow + mt * 16 + gid, p_b = p_a + 8;
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) mx = fmaxf(mx, fmaxf(s[nb][2 * h], s[nb][2 * h + 1]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float mn = fmaxf(m_run[h], mx);
-      const float base = (mn == -INFINITY) ? 0.0f : mn;      // a row that has seen no key yet
-      const float corr = exp2f(m_run[h] - base);
-      float sum = 0.0f;
+        for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        const float p0 = exp2f(s[nb][2 * h] - base), p1 = exp2f(s[nb][2 * h + 1] - base);
-        s[nb][2 * h] = p0;
-        s[nb][2 * h + 1] = p1;
-        sum += p0 + p1;
+          for (int j = 0; j < 4; ++j) {
+            float v = s[mt][nb][j] * scale_log2;
+            if (need_mask) {
+              const int key = key0 + nb * 8 + tig * 2 + (j & 1);
+              const int p = (j < 2) ? p_a : p_b;
+              if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+            }
+            s[mt][nb][j] = v;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) mx = fmaxf(mx, fmaxf(s[mt][nb][2 * h], s[mt][nb][2 * h + 1]));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float mn = fmaxf(m_run[mt][h], mx);
+          const float base = (mn == -INFINITY) ? 0.0f : mn;    // a row that has seen no key yet
+          const float corr = exp2f(m_run[mt][h] - base);
+          float sum = 0.0f;
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            const float p0 = exp2f(s[mt][nb][2 * h] - base), p1 = exp2f(s[mt][nb][2 * h + 1] - base);
+            s[mt][nb][2 * h] = p0;
+            s[mt][nb][2 * h + 1] = p1;
+            sum += p0 + p1;
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          l_run[mt][h] = l_run[mt][h] * corr + sum;
+          m_run[mt][h] = mn;
+#pragma unroll
+          for (int db = 0; db < DB; ++db) {
+            o[mt][db][2 * h] *= corr;
+            o[mt][db][2 * h + 1] *= corr;
+          }
+        }
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l_run[h] = l_run[h] * corr + sum;
-      m_run[h] = mn;
+      // O += P V
 #pragma unroll
-      for (int db = 0; db < DB; ++db) {
-        o[db][2 * h] *= corr;
-        o[db][2 * h + 1] *= corr;
-      }
-    }
-    // O += P V
+      for (int kk = 0; kk < PF_BK / 16; ++kk) {
+        uint32_t pa[MT][4];
 #pragma unroll
-    for (int kk = 0; kk < PF_BK / 16; ++kk) {
-      uint32_t pa[4];
-      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        for (int mt = 0; mt < MT; ++mt) {
+          pa[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+          pa[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+          pa[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+          pa[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+        }
 #pragma unroll
-      for (int db2 = 0; db2 < DB / 2; ++db2) {
-        uint32_t vb[4];
-        const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-        ldmatrix_x4_trans(vb, tv + swz<HD>(vrow, db2 * 2 + (lane >> 4)));
-        mma_16816(o[db2 * 2], pa, vb[0], vb[1]);
-        mma_16816(o[db2 * 2 + 1], pa, vb[2], vb[3]);
+        for (int db2 = 0; db2 < DB / 2; ++db2) {
+          uint32_t vb[4];
+          const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          ldmatrix_x4_trans(vb, tv + swz<HD>(vrow, db2 * 2 + (lane >> 4)));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816(o[mt][db2 * 2], pa[mt], vb[0], vb[1]);
+            mma_16816(o[mt][db2 * 2 + 1], pa[mt], vb[2], vb[3]);
+          }
+        }
       }
     }
     __syncthreads();                                   // this stage is overwritten by the next load
   }
 
   // normalise and store
-  const float inv_a = 1.0f / l_run[0], inv_b = 1.0f / l_run[1];
   __nv_bfloat16* obase = out + ((int64_t)(row_start[b] + q0) * nh + head) * HD;
 #pragma unroll
-  for (int db = 0; db < DB; ++db) {
-    const int d = db * 8 + tig * 2;
-    if (r_a < rows)
-      *reinterpret_cast<uint32_t*>(obase + (int64_t)r_a * nh * HD + d) = pack_bf16(o[db][0] * inv_a, o[db][1] * inv_a);
-    if (r_b < rows)
-      *reinterpret_cast<uint32_t*>(obase + (int64_t)r_b * nh * HD + d) = pack_bf16(o[db][2] * inv_b, o[db][3] * inv_b);
+  for (int mt = 0; mt < MT; ++mt) {
+    const int r_a = wrow + mt * 16 + gid, r_b = r_a + 8;
+    const float inv_a = 1.0f / l_run[mt][0], inv_b = 1.0f / l_run[mt][1];
+#pragma unroll
+    for (int db = 0; db < DB; ++db) {
+      const int d = db * 8 + tig * 2;
+      if (r_a < rows)
+        *reinterpret_cast<uint32_t*>(obase + (int64_t)r_a * nh * HD + d) =
+            pack_bf16(o[mt][db][0] * inv_a, o[mt][db][1] * inv_a);
+      if (r_b < rows)
+        *reinterpret_cast<uint32_t*>(obase + (int64_t)r_b * nh * HD + d) =
+            pack_bf16(o[mt][db][2] * inv_b, o[mt][db][3] * inv_b);
+    }
   }
 }
 
-template <int HD>
+template <int HD, int MT, int STAGES, int WARPS>
 static int launch_prefill(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
                           const int* block_table, int bt_stride, const int* row_start, const int* row_pos0,
                           const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv, int window,
                           float scale, cudaStream_t stream) {
-  const size_t smem = (size_t)(PF_BQ + 4 * PF_BK) * HD * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(16 * MT * WARPS + 2 * STAGES * PF_BK) * HD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, MT, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) { set_error("attn_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return (int)e; }
     configured = true;
   }
   dim3 grid(n_tiles, nh);
-  attn_prefill_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(
+  attn_prefill_kernel<HD, MT, STAGES, WARPS><<<grid, WARPS * 32, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out),
       static_cast<const __nv_bfloat16*>(k_pool), static_cast<const __nv_bfloat16*>(v_pool), block_table,
       bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
@@ -258,8 +299,11 @@ extern "C" int exl3_attn_prefill_supported(int dtype, int hd, int page) {
   return dtype == DT_BF16 && (hd == 64 || hd == 128) && page == PF_BK;
 }
 
-// Tiles: tile i covers queries tile_q0[i] .. tile_q0[i] + 63 (among the new
-// tokens) of batch row tile_seq[i].
+// Queries per block for a head size: 128 for heads of 64, 64 for heads of 128.
+extern "C" int exl3_attn_prefill_tile(int hd) { return hd == 64 ? 16 * PF_WARPS_64 : PF_BQ; }
+
+// Tiles: tile i covers queries tile_q0[i] .. tile_q0[i] + tile - 1 (among the new
+// tokens) of batch row tile_seq[i], with tile = exl3_attn_prefill_tile(hd).
 extern "C" int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
                                  const void* v_pool, const int* block_table, int bt_stride,
                                  const int* row_start, const int* row_pos0, const int* tile_seq,
@@ -280,8 +324,8 @@ extern "C" int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out,
     return ERR_ALIGNMENT;
   }
   if (hd == 64)
-    return launch_prefill<64>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, row_start, row_pos0,
+    return launch_prefill<64, 1, 3, PF_WARPS_64>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, row_start, row_pos0,
                               tile_seq, tile_q0, n_tiles, nh, nkv, window, scale, stream);
-  return launch_prefill<128>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, row_start, row_pos0,
+  return launch_prefill<128, 1, 3, 4>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, row_start, row_pos0,
                              tile_seq, tile_q0, n_tiles, nh, nkv, window, scale, stream);
 }

@@ -162,6 +162,29 @@ __global__ void silu_mul_kernel(const void* __restrict__ gu, void* __restrict__ 
   store_any(out, dtype, idx, g / (1.0f + expf(-g)) * u);
 }
 
+// The same with 16-byte accesses: a thread makes VEC outputs (I % VEC == 0, and
+// an interleave that is a multiple of VEC).
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_vec_kernel(const T* gu, T* out, int64_t total_vecs, int I, int interleave) {
+  constexpr int VEC = Elem<T>::vec;
+  pdl_wait();
+  pdl_trigger();
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_vecs) return;
+  const int per_row = I / VEC;
+  const int64_t t = idx / per_row;
+  const int i0 = (int)(idx - t * per_row) * VEC;
+  const int64_t go = t * 2 * I + (interleave == 0 ? i0 : (i0 / interleave) * 2 * interleave + (i0 % interleave));
+  const int64_t uo = go + (interleave == 0 ? I : interleave);
+  float g[VEC], u[VEC], o[VEC];
+  load_vec_cg(gu + go, g);
+  load_vec_cg(gu + uo, u);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+  store_vec(out + t * I + i0, o);
+}
+
 // One block per token.  qkv[t] = [q heads | k heads | v heads], each head_dim
 // wide.  q and k are rotated in place (half-split pairs d, d + rot/2 with
 // angle pos * pos_scale * inv_freq[d]); rotated k and plain v are written to
@@ -339,6 +362,18 @@ extern "C" int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I,
   }
   const int64_t blocks = (total + 255) / 256;
   if (blocks > 0x7fffffffLL) { set_error("silu_mul: too many elements"); return ERR_UNSUPPORTED; }
+  const int vec = dtype == DT_F32 ? 4 : 8;
+  if (I % vec == 0 && interleave % vec == 0 && aligned16(gu) && aligned16(out)) {
+    const int64_t vecs = total / vec;
+    const unsigned vblocks = (unsigned)((vecs + 255) / 256);
+    if (dtype == DT_F32)
+      launch_pdl(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(gu),
+                 static_cast<float*>(out), vecs, I, interleave);
+    else
+      launch_pdl(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream,
+                 static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), vecs, I, interleave);
+    return launch_status("silu_mul");
+  }
   launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, gu, out, dtype, total, I, interleave);
   return launch_status("silu_mul");
 }

@@ -8,13 +8,13 @@ copy.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 
-QUERY_TILE = 64     # queries per block of the tensor-core prefill attention
+QUERY_TILES = (64, 128)     # queries per block of the tensor-core prefill attention, by head size
 
 
 class Workspace:
@@ -49,9 +49,8 @@ class StepBatch:
     max_kv_len: int                   # longest sequence after this step
     max_new: int                      # most tokens any row brings
     workspace: Workspace
-    tile_seq: Optional[torch.Tensor] = None   # int32 [tiles]: batch row of each tile of 64 queries
-    tile_q0: Optional[torch.Tensor] = None    # int32 [tiles]: first new token of each tile
-    n_tiles: int = 0
+    # per tile size (64, 128 queries): (int32 [tiles] batch row, int32 [tiles] first new token, count)
+    tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     host_slots: List[int] = field(default_factory=list)
     host_new: List[int] = field(default_factory=list)
 
@@ -76,10 +75,15 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
     pos = np.arange(T, dtype=np.int64) - np.repeat(row_start[:-1], counts) + np.repeat(
         np.asarray(starts, dtype=np.int64), counts)
     wanted = [int(row_start[i]) + int(w) for i in range(B) for w in want[i]]
-    tile_rows = [i for i in range(B) for _ in range(0, counts[i], QUERY_TILE)]
-    tile_first = [a for i in range(B) for a in range(0, counts[i], QUERY_TILE)]
     pieces = [tok, pos, seq, np.asarray(slots, np.int64), row_start, np.asarray(starts, np.int64),
-              np.asarray(wanted, np.int64), np.asarray(tile_rows, np.int64), np.asarray(tile_first, np.int64)]
+              np.asarray(wanted, np.int64)]
+    tile_counts = []
+    for size in QUERY_TILES:
+        tile_rows = [i for i in range(B) for _ in range(0, counts[i], size)]
+        tile_first = [a for i in range(B) for a in range(0, counts[i], size)]
+        pieces += [np.asarray(tile_rows, np.int64), np.asarray(tile_first, np.int64)]
+        tile_counts.append(len(tile_rows))
+    n_fixed = len(pieces)
     widths = []
     for g in tables:
         arr = np.asarray(g, dtype=np.int64).reshape(B, -1)
@@ -99,10 +103,10 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
     def view(i: int) -> torch.Tensor:
         return dev[offsets[i]:offsets[i] + pieces[i].size]
 
-    bts = [view(9 + gi).view(B, widths[gi]) for gi in range(len(tables))]
+    bts = [view(n_fixed + gi).view(B, widths[gi]) for gi in range(len(tables))]
+    tiles = {size: (view(7 + 2 * i), view(8 + 2 * i), tile_counts[i]) for i, size in enumerate(QUERY_TILES)}
     return StepBatch(
         n_tokens=T, n_rows=B, token_ids=view(0), tok_pos=view(1), tok_seq=view(2), slot_ids=view(3),
         row_start=view(4), row_pos0=view(5), want_rows=view(6) if wanted else None, n_wanted=len(wanted),
         block_tables=bts, max_kv_len=max([s + c for s, c in zip(starts, counts)] + [0]),
-        max_new=max(counts + [0]), workspace=workspace, tile_seq=view(7), tile_q0=view(8),
-        n_tiles=len(tile_rows), host_slots=list(slots), host_new=counts)
+        max_new=max(counts + [0]), workspace=workspace, tiles=tiles, host_slots=list(slots), host_new=counts)

@@ -17,6 +17,8 @@ src/model.cpp:594-600); its batched decode step is src/glm5_forward.cpp:397-448.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -60,7 +62,7 @@ class DecodeRunner:
     whose contexts fit ``table_width`` pages."""
 
     def __init__(self, engine, rows: int, table_width: int):
-        self.engine = engine
+        self._engine = weakref.ref(engine)              # the engine owns its runners, not the reverse
         self.rows = rows
         self.width = table_width
         dev = engine.device
@@ -88,6 +90,13 @@ class DecodeRunner:
             t[:, 0] = cache.pad_page
             self.pad_tables.append(t)
 
+    @property
+    def engine(self):
+        eng = self._engine()
+        if eng is None:
+            raise RuntimeError("decode runner used after its engine was dropped")
+        return eng
+
     def _batch(self, max_kv_len: int, padding: bool) -> StepBatch:
         pos = self.pad_pos if padding else self.tok_pos.dev
         return StepBatch(
@@ -106,11 +115,20 @@ class DecodeRunner:
         torch.cuda.synchronize()
         before = K.launch_count()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, pool=self.pool):
-            logits = model.forward(self._batch(bucket, padding=False), cache)
-            K.argmax(logits, out=self.next_ids)
-            self.token_ids.dev.copy_(self.next_ids)
-            self.tok_pos.dev.add_(self.pos_inc.dev)
+        # No garbage collection while the stream is capturing: collecting another
+        # CUDA graph there destroys it with calls that are not allowed during a
+        # capture, and the capture fails.
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, pool=self.pool):
+                logits = model.forward(self._batch(bucket, padding=False), cache)
+                K.argmax(logits, out=self.next_ids)
+                self.token_ids.dev.copy_(self.next_ids)
+                self.tok_pos.dev.add_(self.pos_inc.dev)
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.launches[bucket] = K.launch_count() - before
         if self.pool is None:
             self.pool = g.pool()

@@ -183,6 +183,30 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+            gated: bool = False) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` in bfloat16 on the tcgen05 tensor cores; with ``gated``
+    the rows of w are interleaved in eights and ``silu(gate) * up`` comes out."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemm_tc: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemm_tc: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    if out is None:
+        out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=x.device)
+    _check(library().exl3_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(M), _c_int(N), _c_int(K),
+                                  _c_int(1 if gated else 0), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or the code a tensor-core GEMM left when a bounded wait ran out (cleared by this call)."""
+    return int(library().exl3_gemm_tc_status())
+
+
 def attn_tokens_scratch_bytes(T: int, heads: int, head_dim: int, max_splits: int) -> int:
     lib = library()
     lib.exl3_attn_tokens_scratch_bytes.restype = _c_size_t
@@ -207,6 +231,11 @@ def attn_tokens(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
 
 def attn_prefill_supported(dtype: torch.dtype, head_dim: int, page: int) -> bool:
     return bool(library().exl3_attn_prefill_supported(_c_int(dtype_code(dtype)), _c_int(head_dim), _c_int(page)))
+
+
+def attn_prefill_tile(head_dim: int) -> int:
+    """Queries per block of the prefill attention for this head size."""
+    return int(library().exl3_attn_prefill_tile(_c_int(head_dim)))
 
 
 def attn_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -83,12 +83,12 @@ class Attention:
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> None:
         s = self.spec
         T = qkv.shape[0]
-        if (batch.max_new > 1 and batch.tile_seq is not None
-                and K.attn_prefill_supported(qkv.dtype, s.head_dim, kv.page_size)):
-            # prompts: streaming-softmax kernel on the tensor cores, a block per 64 queries
+        if batch.max_new > 1 and batch.tiles and K.attn_prefill_supported(qkv.dtype, s.head_dim, kv.page_size):
+            # prompts: streaming-softmax kernel on the tensor cores, a block per tile of queries
+            tile_seq, tile_q0, n_tiles = batch.tiles[K.attn_prefill_tile(s.head_dim)]
             K.attn_prefill(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
-                           batch.tile_seq, batch.tile_q0, batch.n_tiles, s.heads, s.kv_heads, s.head_dim,
-                           kv.page_size, s.window, self.scale)
+                           tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
+                           self.scale)
             return
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:

@@ -53,7 +53,7 @@ class SwiGLU:
         self.down = Linear(tensors[prefix + "down_proj.weight"], tensors.get(prefix + "down_proj.bias"), ctx.dtype)
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        if self.interleave and self.gate_up.streams_weights(x.shape[0]):
+        if self.interleave and self.gate_up.fuses_gate():
             return self.down(self.gate_up.gated(x))
         return self.down(K.silu_mul(self.gate_up(x), interleave=self.interleave))
 

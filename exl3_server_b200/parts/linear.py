@@ -5,8 +5,10 @@ src/model.cpp:214-228; the kernels here read rows of W, so no transpose).
 Which kernel runs depends only on the element type and the row count:
 float32 goes through the CUDA-core kernel with a fixed order of summation
 (the true 32-bit path); bfloat16 with at most 16 rows streams the weights once
-through the tensor-core GEMV; larger bfloat16 products are the library's
+through the tensor-core GEMV; larger plain bfloat16 products are the library's
 (cuBLAS through ``torch``), as the reference's are MLX's (src/model.cpp:549).
+The gated feed-forward projection, whose epilogue is fused, runs on this
+library's own tcgen05 GEMM (``gated``).
 """
 from __future__ import annotations
 
@@ -50,11 +52,18 @@ class Linear:
         """Whether ``rows`` rows of input go through the weight-streaming GEMV."""
         return self.dtype == torch.bfloat16 and self.in_features % 8 == 0 and rows <= K.GEMV_MAX_ROWS
 
+    def fuses_gate(self) -> bool:
+        """Whether ``gated`` can run: bfloat16 with sizes the fused kernels take."""
+        return self.dtype == torch.bfloat16 and self.in_features % 8 == 0 and self.out_features % 16 == 0
+
     def gated(self, x: torch.Tensor) -> torch.Tensor:
         """For a weight whose rows are eight gate rows, then the eight up rows
-        of the same features, and so on: ``silu(gate) * up`` in one kernel
-        (only when ``streams_weights``)."""
-        return K.gemv_bf16(x, self.weight, self.bias, self.dtype, gated=True)
+        of the same features, and so on: ``silu(gate) * up`` in the projection's
+        own epilogue, so the gate/up product never goes to memory.  Up to 16 rows:
+        the weight-streaming GEMV; more: the tcgen05 tensor-core GEMM."""
+        if x.shape[0] <= K.GEMV_MAX_ROWS:
+            return K.gemv_bf16(x, self.weight, self.bias, self.dtype, gated=True)
+        return K.gemm_tc(x, self.weight, self.bias, gated=True)
 
     def weight_bytes(self) -> int:
         n = self.weight.numel() * self.weight.element_size()

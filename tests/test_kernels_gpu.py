@@ -60,11 +60,16 @@ def test_add_rmsnorm(dtype, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_silu_mul(dtype):
+@pytest.mark.parametrize("I", [173, 176, 5760])
+def test_silu_mul(dtype, I):
     torch.manual_seed(2)
-    gu = (3 * torch.randn(5, 2 * 173, device=DEV)).to(dtype)
-    g, u = gu.double()[:, :173], gu.double()[:, 173:]
+    gu = (3 * torch.randn(5, 2 * I, device=DEV)).to(dtype)
+    g, u = gu.double()[:, :I], gu.double()[:, I:]
     close(K().silu_mul(gu), g * torch.sigmoid(g) * u, TOL[dtype], "silu_mul")
+    if I % 8 == 0:
+        n = I // 8
+        inter = torch.stack([gu[:, :I].reshape(5, n, 8), gu[:, I:].reshape(5, n, 8)], dim=2).reshape(5, 2 * I)
+        close(K().silu_mul(inter.contiguous(), interleave=8), g * torch.sigmoid(g) * u, TOL[dtype], "interleaved")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -124,6 +129,38 @@ def test_gemv_gated_and_interleaved_silu(M, I, Kd):
     close(K().silu_mul(gu, interleave=8), want, 2e-6, "interleaved silu_mul")
 
 
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (128, 256, 192), (200, 512, 2304), (77, 264, 72), (1, 8, 8),
+                                    (2048, 2304, 5760), (300, 6912, 2304)])
+def test_gemm_tc(M, N, Kd):
+    torch.manual_seed(10)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    want = x.double() @ w.double().T
+    close(K().gemm_tc(x, w, None), want, TOL[torch.bfloat16], "gemm_tc")
+    close(K().gemm_tc(x, w, b), want + b.double(), TOL[torch.bfloat16], "gemm_tc + bias")
+    torch.cuda.synchronize()
+    assert K().gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M", [17, 300, 2048])
+@pytest.mark.parametrize("I,Kd", [(176, 64), (5760, 2304), (200, 96)])
+def test_gemm_tc_gated(M, I, Kd):
+    torch.manual_seed(11)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    wg = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    wu = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    bg, bu = torch.randn(I, device=DEV).bfloat16(), torch.randn(I, device=DEV).bfloat16()
+    n = I // 8
+    w = torch.stack([wg.view(n, 8, Kd), wu.view(n, 8, Kd)], dim=1).reshape(2 * I, Kd).contiguous()
+    b = torch.stack([bg.view(n, 8), bu.view(n, 8)], dim=1).reshape(-1).contiguous()
+    g = x.double() @ wg.double().T + bg.double()
+    u = x.double() @ wu.double().T + bu.double()
+    close(K().gemm_tc(x, w, b, gated=True), g * torch.sigmoid(g) * u, TOL[torch.bfloat16], "gated gemm_tc")
+    torch.cuda.synchronize()
+    assert K().gemm_tc_status() == 0
+
+
 def test_gemv_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(17, 64, device=DEV).bfloat16()
@@ -173,8 +210,12 @@ class PagedCase:
             starts.append(starts[-1] + n)
         self.row_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
         self.row_pos0 = torch.tensor([lens[b] - new[b] for b in range(B)], dtype=torch.int32, device=DEV)
-        self.tile_seq = torch.tensor([b for b in range(B) for _ in range(0, new[b], 64)], dtype=torch.int32, device=DEV)
-        self.tile_q0 = torch.tensor([a for b in range(B) for a in range(0, new[b], 64)], dtype=torch.int32, device=DEV)
+
+    def tiles(self, size):
+        B = len(self.new)
+        seq = torch.tensor([b for b in range(B) for _ in range(0, self.new[b], size)], dtype=torch.int32, device=DEV)
+        q0 = torch.tensor([a for b in range(B) for a in range(0, self.new[b], size)], dtype=torch.int32, device=DEV)
+        return seq, q0
 
     def reference(self, window, scale):
         outs = []
@@ -257,8 +298,9 @@ def test_attn_prefill(nh, nkv, hd, window):
     out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
     scale = 1.3 / math.sqrt(hd)
     assert K().attn_prefill_supported(torch.bfloat16, hd, 64)
+    tile_seq, tile_q0 = case.tiles(K().attn_prefill_tile(hd))
     K().attn_prefill(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
-                     case.tile_seq, case.tile_q0, case.tile_seq.numel(), nh, nkv, hd, 64, window, scale)
+                     tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale)
     close(out, case.reference(window, scale), 1e-2, "attn_prefill")
 
 
