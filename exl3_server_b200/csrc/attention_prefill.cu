@@ -51,6 +51,12 @@ __device__ inline void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit; ex2.approx(-inf) = +0
+__device__ inline float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ inline uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -66,7 +72,7 @@ __device__ inline int swz(int row, int chunk) {
 // MT: 16-row tiles per warp; a block owns 64 * MT queries.  With MT = 2 every K
 // and V fragment read from shared memory feeds two mma instructions.
 template <int HD, int MT, int STAGES, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, HD == 64 ? 4 : 2)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
@@ -177,22 +183,21 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
           }
         }
       }
-      // scale (to base 2), mask, running max and sum
+      // mask, running max and sum; the softmax scale is folded into the exponent:
+      // p = 2^(s * scale_log2 - m), one multiply-add and one ex2 per score
       const bool need_mask = (key0 + PF_BK - 1 > p_first + wrow) || (window > 0 && key0 <= p_last - window);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int p_a = p_first + wrow + mt * 16 + gid, p_b = p_a + 8;
+        if (need_mask) {
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
+          for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float v = s[mt][nb][j] * scale_log2;
-            if (need_mask) {
+            for (int j = 0; j < 4; ++j) {
               const int key = key0 + nb * 8 + tig * 2 + (j & 1);
               const int p = (j < 2) ? p_a : p_b;
-              if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+              if (key > p || (window > 0 && key <= p - window)) s[mt][nb][j] = -INFINITY;
             }
-            s[mt][nb][j] = v;
           }
         }
 #pragma unroll
@@ -202,13 +207,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
           for (int nb = 0; nb < NB; ++nb) mx = fmaxf(mx, fmaxf(s[mt][nb][2 * h], s[mt][nb][2 * h + 1]));
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          const float mn = fmaxf(m_run[mt][h], mx);
-          const float base = (mn == -INFINITY) ? 0.0f : mn;    // a row that has seen no key yet
-          const float corr = exp2f(m_run[mt][h] - base);
+          const float mn = fmaxf(m_run[mt][h], mx * scale_log2);   // scale > 0: max and scale commute
+          const float base = (mn == -INFINITY) ? 0.0f : mn;        // a row that has seen no key yet
+          const float corr = fast_exp2(m_run[mt][h] - base);
           float sum = 0.0f;
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb) {
-            const float p0 = exp2f(s[mt][nb][2 * h] - base), p1 = exp2f(s[mt][nb][2 * h + 1] - base);
+            const float p0 = fast_exp2(fmaf(s[mt][nb][2 * h], scale_log2, -base));
+            const float p1 = fast_exp2(fmaf(s[mt][nb][2 * h + 1], scale_log2, -base));
             s[mt][nb][2 * h] = p0;
             s[mt][nb][2 * h + 1] = p1;
             sum += p0 + p1;
@@ -217,10 +223,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
           sum += __shfl_xor_sync(0xffffffffu, sum, 2);
           l_run[mt][h] = l_run[mt][h] * corr + sum;
           m_run[mt][h] = mn;
+          if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-          for (int db = 0; db < DB; ++db) {
-            o[mt][db][2 * h] *= corr;
-            o[mt][db][2 * h + 1] *= corr;
+            for (int db = 0; db < DB; ++db) {
+              o[mt][db][2 * h] *= corr;
+              o[mt][db][2 * h + 1] *= corr;
+            }
           }
         }
       }

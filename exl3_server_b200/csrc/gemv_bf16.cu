@@ -33,8 +33,23 @@ __device__ inline void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_
 }
 
 constexpr int GEMV_MAX_WARPS = 16;
-constexpr int GEMV_UNROLL = 6;      // 32-wide K blocks a warp has in flight
+constexpr int GEMV_STAGES = 6;      // 32-wide K blocks a thread has in flight
 
+// 16 bytes global -> shared without passing through registers; src_bytes 0 writes zeros.
+__device__ inline void cp_async16_zfill(void* smem, const void* gmem, int src_bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ inline void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ inline void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A thread streams its own pieces of the weights (rows gid and gid + 8 of the
+// block's 16, the 16 bytes at tig * 8 of each 32-wide K block its warp owns)
+// through a ring of GEMV_STAGES slots in shared memory with cp.async.  Only the
+// thread that copied a slot reads it, so the ring needs no block barrier, costs
+// no registers, and keeps (GEMV_STAGES - 1) * 32 bytes of weights per thread in
+// flight.  Its pieces of the activations travel in the same ring.
+//
 // EPI 0: y[m, n] = acc (+ bias).  EPI 1 (gated feed-forward): the 16 rows of a
 // block are 8 gate rows followed by the 8 up rows of the same features;
 // y[m, block * 8 + r] = silu(gate_r) * up_r, so N / 2 features come out.
@@ -43,8 +58,10 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
                  const __nv_bfloat16* __restrict__ bias, TO* __restrict__ y, int M, int N, int K) {
   __shared__ float part[GEMV_MAX_WARPS][16][8 * NT + 1];
+  extern __shared__ uint4 ring[];                     // [GEMV_STAGES][2 + NT][blockDim.x]: weights a, b, then x
   pdl_trigger();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int r0 = blockIdx.x * 16;
   const int row_a = r0 + gid, row_b = r0 + gid + 8;
@@ -56,35 +73,58 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
   for (int t = 0; t < NT; ++t)
 #pragma unroll
     for (int i = 0; i < 4; ++i) c[t][i] = 0.0f;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-
   const int nblocks = (K + 31) / 32;
-  bool waited = false;
-  for (int kb0 = warp; kb0 < nblocks; kb0 += nwarps * GEMV_UNROLL) {
-    // weights first: they do not depend on the kernel before this one
-    uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
+  const int n_my = warp < nblocks ? (nblocks - warp + nwarps - 1) / nwarps : 0;   // K blocks of this warp
+  constexpr int SLOTS = 2 + NT;
+  auto issue_w = [&](int i) {
+    const int k = (warp + i * nwarps) * 32 + tig * 8;
+    const bool in = k < K;                            // K % 8 == 0: a piece is inside or outside
+    const int st = i % GEMV_STAGES;
+    cp_async16_zfill(&ring[(st * SLOTS + 0) * nthreads + tid], wa + (in ? k : 0), (in && ok_a) ? 16 : 0);
+    cp_async16_zfill(&ring[(st * SLOTS + 1) * nthreads + tid], wb + (in ? k : 0), (in && ok_b) ? 16 : 0);
+  };
+  // the activations take the same road (cp.async.cg reads through L2, which is what data
+  // written by the previous kernel needs), so no load latency is exposed in the loop
+  auto issue_x = [&](int i) {
+    const int k = (warp + i * nwarps) * 32 + tig * 8;
+    const bool in = k < K;
+    const int st = i % GEMV_STAGES;
 #pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; ++u) {
-      const int k = (kb0 + u * nwarps) * 32 + tig * 8;
-      const bool in = k < K;                          // K % 8 == 0: a piece is inside or outside
-      a[u] = (in && ok_a) ? ldg_stream(wa + k) : zero;
-      b[u] = (in && ok_b) ? ldg_stream(wb + k) : zero;
+    for (int t = 0; t < NT; ++t) {
+      const int m = t * 8 + gid;
+      const bool okx = in && m < M;
+      cp_async16_zfill(&ring[(st * SLOTS + 2 + t) * nthreads + tid], x + (okx ? (int64_t)m * K + k : 0), okx ? 16 : 0);
     }
-    if (!waited) { pdl_wait(); waited = true; }
+  };
+  // weights first: they do not depend on the kernel before this one
 #pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; ++u) {
-      const int k = (kb0 + u * nwarps) * 32 + tig * 8;
-      const bool in = k < K;
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int m = t * 8 + gid;
-        const uint4 xv = (in && m < M) ? __ldcg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + k)) : zero;
-        mma_bf16(c[t], a[u].x, b[u].x, a[u].y, b[u].y, xv.x, xv.y);
-        mma_bf16(c[t], a[u].z, b[u].z, a[u].w, b[u].w, xv.z, xv.w);
-      }
-    }
+  for (int i = 0; i < GEMV_STAGES - 1; ++i) {
+    if (i < n_my) issue_w(i);
+    cp_async_commit_group();
   }
-  if (!waited) pdl_wait();
+  pdl_wait();
+#pragma unroll
+  for (int i = 0; i < GEMV_STAGES - 1; ++i) {
+    if (i < n_my) issue_x(i);
+    cp_async_commit_group();
+  }
+  // Groups complete in order: W0..W(S-2), X0..X(S-2), then one group per iteration.  Block i
+  // needs the group at index S-1+i; at iteration i, 2(S-1)+i groups exist, so S-2 may pend.
+  for (int i = 0; i < n_my; ++i) {
+    cp_async_wait_group<GEMV_STAGES - 2>();
+    const int st = i % GEMV_STAGES;
+    const uint4 a = ring[(st * SLOTS + 0) * nthreads + tid];
+    const uint4 b = ring[(st * SLOTS + 1) * nthreads + tid];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const uint4 xv = ring[(st * SLOTS + 2 + t) * nthreads + tid];
+      mma_bf16(c[t], a.x, b.x, a.y, b.y, xv.x, xv.y);
+      mma_bf16(c[t], a.z, b.z, a.w, b.w, xv.z, xv.w);
+    }
+    // the slot read above is refilled only now, after its values were used
+    if (i + GEMV_STAGES - 1 < n_my) { issue_w(i + GEMV_STAGES - 1); issue_x(i + GEMV_STAGES - 1); }
+    cp_async_commit_group();
+  }
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     part[warp][gid][t * 8 + tig * 2] = c[t][0];
@@ -120,7 +160,14 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
 template <int NT, typename TO, int EPI>
 static int launch(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int warps,
                   cudaStream_t stream) {
-  launch_pdl(gemv_bf16_kernel<NT, TO, EPI>, dim3(ceil_div(N, 16)), dim3(warps * 32), 0, stream,
+  const size_t ring_bytes = (size_t)GEMV_STAGES * (2 + NT) * warps * 32 * sizeof(uint4);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemv_bf16_kernel<NT, TO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)((size_t)GEMV_STAGES * (2 + NT) * GEMV_MAX_WARPS * 32 * sizeof(uint4)));
+    configured = true;
+  }
+  launch_pdl(gemv_bf16_kernel<NT, TO, EPI>, dim3(ceil_div(N, 16)), dim3(warps * 32), ring_bytes, stream,
              static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
              static_cast<const __nv_bfloat16*>(bias), static_cast<TO*>(y), M, N, K);
   return launch_status("gemv_bf16");
@@ -143,13 +190,13 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
     return ERR_BAD_ARGUMENT;
   }
   if (!aligned16(x) || !aligned16(w)) { set_error("gemv_bf16: x and w must be 16-byte aligned"); return ERR_ALIGNMENT; }
-  // Few blocks: many warps per block, so that one pass of GEMV_UNROLL K blocks
-  // per warp covers K and every load is in flight at once.  Many blocks: fewer
-  // warps each.  The choice depends on N and K only, never on M.
+  // Few blocks: many warps per block, so that the ring covers most of K at
+  // once.  Many blocks: fewer warps each, several blocks per SM.  The choice
+  // depends on N and K only, never on M.
   const int nblocks = (K + 31) / 32;
   const int ctas = ceil_div(N, 16);
-  int warps = ctas >= 8 * 148 ? 4 : (ctas >= 3 * 148 ? 8 : 16);
-  while (warps > 1 && (warps / 2) * GEMV_UNROLL >= nblocks) warps >>= 1;
+  int warps = ctas >= 4 * 148 ? 4 : (ctas >= 2 * 148 ? 8 : 16);
+  while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
   const bool f32 = out_dtype == DT_F32;
   if (!f32 && out_dtype != DT_BF16) { set_error("gemv_bf16: unsupported output type %d", out_dtype); return ERR_UNSUPPORTED; }
 #define EXL3_GEMV(NT, EPI)                                                                     \
