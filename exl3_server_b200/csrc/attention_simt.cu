@@ -15,7 +15,10 @@
 // not on how the tokens were cut into steps.  Inside a chunk the four warps
 // take pages in turn; inside a warp each group of lanes owns the keys
 // congruent to its index and keeps a private (max, sum, acc); the groups, the
-// warps and the chunks are merged in a fixed order.
+// warps and the chunks are merged in a fixed order.  The chunks of a (token, kv
+// head) are merged by whichever of their blocks finishes last (a counter at the
+// start of the scratch memory tells it); the scratch must be zero when it is
+// first used and is left with zero counters by every launch.
 //
 // Cache layout: pool[page][kv_head][slot][head_dim], page = block_table[row][pos / page_size].
 #include "api.h"
@@ -26,6 +29,7 @@
 namespace exl3 {
 
 constexpr int ATT_WARPS = 4;
+constexpr int ATT_COUNTER_SLOTS = 65536;            // ints at the start of scratch, one per (token, kv head)
 
 // merge (mo, lo, ao) into (m, l, a)
 template <int N>
@@ -46,11 +50,13 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
                    const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, int nh, int nkv, int hd, int page, int window,
-                   float scale, int split_keys, int max_splits, float* __restrict__ scratch, int lpk) {
+                   float scale, int split_keys, int max_splits, float* __restrict__ scratch,
+                   int* __restrict__ counters, int lpk) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
-  constexpr int U = R == 1 ? 4 : 2;                  // key groups in flight per lane
-  extern __shared__ float smem[];                    // [ATT_WARPS][GT][hd + 2]
+  constexpr int U = R == 1 ? 4 : 2;                  // key groups whose loads are issued together
+  extern __shared__ float smem[];                    // [ATT_WARPS][GT][hd + 2], then [2][max_splits]
+  __shared__ int is_last;
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
@@ -218,6 +224,42 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       }
     }
   }
+  if (max_splits <= 1 || counters == nullptr) return;
+  // The block that finishes last among the chunks of this (token, kv head) merges
+  // them.  Which block that is varies; what it computes does not: the same sums
+  // in chunk order.  The counter goes back to zero for the next launch.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(counters + (int64_t)t * nkv + g, 1) == max_splits - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* sw = smem + ATT_WARPS * GT * rec;
+  float* sl = sw + max_splits;
+  for (int hq = 0; hq < G; ++hq) {
+    const int head = g * G + hq;
+    const float* base = scratch + ((int64_t)t * nh + head) * max_splits * rec;
+    __syncthreads();
+    for (int s2 = threadIdx.x; s2 < max_splits; s2 += blockDim.x) {
+      sw[s2] = __ldcg(base + (int64_t)s2 * rec + hd);
+      sl[s2] = __ldcg(base + (int64_t)s2 * rec + hd + 1);
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int s2 = 0; s2 < max_splits; ++s2) mx = fmaxf(mx, sw[s2]);
+    __syncthreads();
+    for (int s2 = threadIdx.x; s2 < max_splits; s2 += blockDim.x) sw[s2] = expf(sw[s2] - mx);
+    __syncthreads();
+    float ll = 0.0f;
+    for (int s2 = 0; s2 < max_splits; ++s2) ll += sl[s2] * sw[s2];
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      float aa = 0.0f;
+#pragma unroll 4
+      for (int s2 = 0; s2 < max_splits; ++s2) aa += __ldcg(base + (int64_t)s2 * rec + d) * sw[s2];
+      Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa / ll);
+    }
+  }
+  if (threadIdx.x == 0) counters[(int64_t)t * nkv + g] = 0;
 }
 
 // out[t, head, :] from the per-chunk records.  With M the largest of the
@@ -259,15 +301,20 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
                          const int* tok_seq, int T_, int nh, int nkv, int hd, int page, int window,
                          float scale, int split_keys, int max_splits, float* scratch, int lpk,
                          cudaStream_t stream) {
-  const size_t smem = (size_t)ATT_WARPS * GT * (hd + 2) * sizeof(float);
+  const size_t smem = ((size_t)ATT_WARPS * GT * (hd + 2) + 2 * (size_t)max_splits) * sizeof(float);
+  // The first ATT_COUNTER_BYTES of scratch are counters (zero between launches); records follow.
+  // worth it only for a few tokens: with many, the merge kernel overlaps better than one block's loop
+  const bool fused_merge = max_splits > 1 && T_ <= 2 && (int64_t)T_ * nkv <= ATT_COUNTER_SLOTS;
+  int* counters = fused_merge ? reinterpret_cast<int*>(scratch) : nullptr;
+  if (max_splits > 1) scratch = scratch + ATT_COUNTER_SLOTS;
   dim3 grid(T_, nkv, max_splits);
   launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
              static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
              static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, page, window,
-             scale, split_keys, max_splits, scratch, lpk);
+             scale, split_keys, max_splits, scratch, counters, lpk);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
-  if (max_splits > 1) {
+  if (max_splits > 1 && !fused_merge) {
     launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
                (const float*)scratch, static_cast<T*>(out), nh, hd, max_splits);
     rc = launch_status("attn_combine");
@@ -311,7 +358,7 @@ using namespace exl3;
 
 extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits) {
   if (max_splits <= 1) return 0;
-  return (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
+  return (size_t)ATT_COUNTER_SLOTS * sizeof(int) + (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
 }
 
 extern "C" int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype,

@@ -25,8 +25,10 @@ class Workspace:
         self._buf: Optional[torch.Tensor] = None
 
     def floats(self, n: int) -> torch.Tensor:
+        # zeroed when made: the attention kernel keeps counters in it that must start at zero
+        # (and returns them to zero itself)
         if self._buf is None or self._buf.numel() < n:
-            self._buf = torch.empty(max(n, 1 << 16), dtype=torch.float32, device=self.device)
+            self._buf = torch.zeros(max(n, 1 << 16), dtype=torch.float32, device=self.device)
         return self._buf
 
     def reserve(self, n: int) -> None:

@@ -26,6 +26,8 @@ from .spec import MixerSpec, PositionSpec
 
 # Keys per work item of the attention kernel; a multiple of the cache's page size.
 SPLIT_KEYS = 256
+# Work items (token x kv head x chunk) beyond which the bfloat16 path doubles the chunk length.
+BUSY_ITEMS = 1776
 
 
 class Attention:
@@ -93,6 +95,11 @@ class Attention:
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
             split = kv.page_size * (split // kv.page_size + 1)
+        # bfloat16 with more work items than the GPU holds at once: chunks twice as long, so that a
+        # block's fixed costs are spread over more keys.  float32 keeps one chunking for every
+        # batch, so that its results do not depend on the batch at all.
+        if qkv.dtype == torch.bfloat16 and T * s.kv_heads * ((batch.max_kv_len + split - 1) // split) > BUSY_ITEMS:
+            split *= 2
         n = (batch.max_kv_len + split - 1) // split
         if s.window > 0:
             n = min(n, (s.window + split - 2) // split + 1)

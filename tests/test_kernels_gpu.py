@@ -254,7 +254,7 @@ def test_attn_tokens(dtype, nh, nkv, hd, window):
     scale = 0.7 / math.sqrt(hd)
     split = 128
     n = (max(case.lens) + split - 1) // split
-    scratch = torch.empty(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
     K().attn_tokens(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
                     nh, nkv, hd, 64, window, scale, split, n, scratch)
     close(out, case.reference(window, scale), 2e-6 if dtype == torch.float32 else 1e-2, "attn_tokens")
@@ -274,7 +274,7 @@ def test_attn_tokens_finds_one_far_key_among_many():
     case.k[0][far] = kp[pg, :, far % 64].cpu()
     q = (case.q.reshape(1, nh * hd) * 1.0).to(DEV).contiguous()
     out = torch.empty_like(q)
-    scratch = torch.empty(K().attn_tokens_scratch_bytes(1, nh, hd, 4) // 4, device=DEV)
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(1, nh, hd, 4) // 4, device=DEV)
     K().attn_tokens(q, q.stride(0), out, kp, case.v_pool, table, case.tok_pos, case.tok_seq, 1, nh, nkv, hd, 64, 0,
                     1.0, 256, 4, scratch)
     close(out, case.v[0][far].reshape(1, -1), 1e-3, "far key")
