@@ -33,7 +33,6 @@ __device__ inline void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_
 }
 
 constexpr int GEMV_MAX_WARPS = 16;
-constexpr int GEMV_STAGES = 6;      // 32-wide K blocks a thread has in flight
 
 // 16 bytes global -> shared without passing through registers; src_bytes 0 writes zeros.
 __device__ inline void cp_async16_zfill(void* smem, const void* gmem, int src_bytes) {
@@ -45,7 +44,7 @@ template <int N> __device__ inline void cp_async_wait_group() { asm volatile("cp
 
 // A thread streams its own pieces of the weights (rows gid and gid + 8 of the
 // block's 16, the 16 bytes at tig * 8 of each 32-wide K block its warp owns)
-// through a ring of GEMV_STAGES slots in shared memory with cp.async.  Only the
+// through a ring of GEMV_STAGES (4 or 6) slots in shared memory with cp.async.  Only the
 // thread that copied a slot reads it, so the ring needs no block barrier, costs
 // no registers, and keeps (GEMV_STAGES - 1) * 32 bytes of weights per thread in
 // flight.  Its pieces of the activations travel in the same ring.
@@ -53,14 +52,15 @@ template <int N> __device__ inline void cp_async_wait_group() { asm volatile("cp
 // EPI 0: y[m, n] = acc (+ bias).  EPI 1 (gated feed-forward): the 16 rows of a
 // block are 8 gate rows followed by the 8 up rows of the same features;
 // y[m, block * 8 + r] = silu(gate_r) * up_r, so N / 2 features come out.
-template <int NT, typename TO, int EPI>
+template <int NT, typename TO, int EPI, int GEMV_STAGES>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
                  const __nv_bfloat16* __restrict__ bias, TO* __restrict__ y, int M, int N, int K) {
-  __shared__ float part[GEMV_MAX_WARPS][16][8 * NT + 1];
   extern __shared__ uint4 ring[];                     // [GEMV_STAGES][2 + NT][blockDim.x]: weights a, b, then x
   pdl_trigger();
   const int tid = threadIdx.x, nthreads = blockDim.x;
+  // partial tiles of the warps, behind the ring: [warps][16][8 NT + 1]
+  float (*part)[16][8 * NT + 1] = reinterpret_cast<float (*)[16][8 * NT + 1]>(ring + GEMV_STAGES * (2 + NT) * nthreads);
   const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int r0 = blockIdx.x * 16;
@@ -157,20 +157,34 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
   }
 }
 
-template <int NT, typename TO, int EPI>
+static size_t gemv_smem(int nt, int stages, int warps) {
+  return (size_t)stages * (2 + nt) * warps * 32 * sizeof(uint4) + (size_t)warps * 16 * (8 * nt + 1) * sizeof(float);
+}
+
+template <int NT, typename TO, int EPI, int STAGES>
 static int launch(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int warps,
                   cudaStream_t stream) {
-  const size_t ring_bytes = (size_t)GEMV_STAGES * (2 + NT) * warps * 32 * sizeof(uint4);
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(gemv_bf16_kernel<NT, TO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)((size_t)GEMV_STAGES * (2 + NT) * GEMV_MAX_WARPS * 32 * sizeof(uint4)));
+    cudaFuncSetAttribute(gemv_bf16_kernel<NT, TO, EPI, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)gemv_smem(NT, STAGES, GEMV_MAX_WARPS));
     configured = true;
   }
-  launch_pdl(gemv_bf16_kernel<NT, TO, EPI>, dim3(ceil_div(N, 16)), dim3(warps * 32), ring_bytes, stream,
+  launch_pdl(gemv_bf16_kernel<NT, TO, EPI, STAGES>, dim3(ceil_div(N, 16)), dim3(warps * 32),
+             gemv_smem(NT, STAGES, warps), stream,
              static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
              static_cast<const __nv_bfloat16*>(bias), static_cast<TO*>(y), M, N, K);
   return launch_status("gemv_bf16");
+}
+
+static int gemv_sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
 }
 
 }  // namespace exl3
@@ -190,19 +204,26 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
     return ERR_BAD_ARGUMENT;
   }
   if (!aligned16(x) || !aligned16(w)) { set_error("gemv_bf16: x and w must be 16-byte aligned"); return ERR_ALIGNMENT; }
-  // Few blocks: many warps per block, so that the ring covers most of K at
-  // once.  Many blocks: fewer warps each, several blocks per SM.  The choice
-  // depends on N and K only, never on M.
-  const int nblocks = (K + 31) / 32;
-  const int ctas = ceil_div(N, 16);
-  int warps = ctas >= 4 * 148 ? 4 : (ctas >= 2 * 148 ? 8 : 16);
-  while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
   const bool f32 = out_dtype == DT_F32;
   if (!f32 && out_dtype != DT_BF16) { set_error("gemv_bf16: unsupported output type %d", out_dtype); return ERR_UNSUPPORTED; }
-#define EXL3_GEMV(NT, EPI)                                                                     \
-  return f32 ? launch<NT, float, EPI>(x, w, bias, y, M, N, K, warps, stream)                   \
-             : launch<NT, __nv_bfloat16, EPI>(x, w, bias, y, M, N, K, warps, stream)
-  if (M <= 8) { if (epilogue) { EXL3_GEMV(1, 1); } else { EXL3_GEMV(1, 0); } }
-  if (epilogue) { EXL3_GEMV(2, 1); } else { EXL3_GEMV(2, 0); }
+  // Few blocks: many warps per block, so that the ring covers most of K at
+  // once.  Many blocks: fewer warps each, several blocks per SM.  The choice
+  // depends on N and K only, never on M, so a row's result does not depend on
+  // its batch.  (Measured: block shapes that make all blocks resident at once,
+  // or deeper rings, change nothing; a dependent kernel costs about 2 us however
+  // small, and mid-sized matrices stay near 3.5-4 TB/s for that reason.)
+  const int nt = M <= 8 ? 1 : 2;
+  const int nblocks = (K + 31) / 32;
+  const int ctas = ceil_div(N, 16);
+  int warps = ctas >= 4 * gemv_sm_count() ? 4 : (ctas >= 2 * gemv_sm_count() ? 8 : 16);
+  while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
+  const int stages = (nt == 2 && warps == 16) ? 4 : 6;      // 16 warps x 6 stages x 4 slots would not fit
+#define EXL3_GEMV(NT, EPI, ST)                                                                  \
+  return f32 ? launch<NT, float, EPI, ST>(x, w, bias, y, M, N, K, warps, stream)                \
+             : launch<NT, __nv_bfloat16, EPI, ST>(x, w, bias, y, M, N, K, warps, stream)
+#define EXL3_GEMV_ST(NT, EPI) if (stages == 6) { EXL3_GEMV(NT, EPI, 6); } else { EXL3_GEMV(NT, EPI, 4); }
+  if (nt == 1) { if (epilogue) { EXL3_GEMV_ST(1, 1) } else { EXL3_GEMV_ST(1, 0) } }
+  if (epilogue) { EXL3_GEMV_ST(2, 1) } else { EXL3_GEMV_ST(2, 0) }
+#undef EXL3_GEMV_ST
 #undef EXL3_GEMV
 }
