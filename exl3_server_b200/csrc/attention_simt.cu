@@ -31,12 +31,30 @@ namespace exl3 {
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_COUNTER_SLOTS = 65536;            // ints at the start of scratch, one per (token, kv head)
 
+// The exponential of the softmax.  float32 path: expf on natural-log scores.
+// bfloat16 path: scores are multiplied by log2(e) beforehand and ex2.approx is
+// one instruction; maxima are then in base-2 units everywhere (registers,
+// shared memory, scratch), consistently.
+template <typename T> struct SoftmaxExp;
+template <> struct SoftmaxExp<float> {
+  static constexpr float prescale = 1.0f;
+  __device__ static inline float exp(float x) { return expf(x); }
+};
+template <> struct SoftmaxExp<__nv_bfloat16> {
+  static constexpr float prescale = 1.4426950408889634f;
+  __device__ static inline float exp(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+};
+
 // merge (mo, lo, ao) into (m, l, a)
-template <int N>
+template <typename T, int N>
 __device__ inline void merge_state(float& m, float& l, float (&a)[N], float mo, float lo, const float (&ao)[N]) {
   const float mn = fmaxf(m, mo);
   if (mn == -INFINITY) return;                       // both empty
-  const float cs = expf(m - mn), co = expf(mo - mn);
+  const float cs = SoftmaxExp<T>::exp(m - mn), co = SoftmaxExp<T>::exp(mo - mn);
   l = l * cs + lo * co;
 #pragma unroll
   for (int i = 0; i < N; ++i) a[i] = a[i] * cs + ao[i] * co;
@@ -64,6 +82,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kpw = 32 / lpk;                          // keys a warp handles at once
   const int grp = lane / lpk, li = lane - grp * lpk;
+  const float scale_eff = scale * SoftmaxExp<T>::prescale;
   const int pos = __ldcg(tok_pos + t);
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int hi = pos + 1;
@@ -147,10 +166,10 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
               for (int i = 0; i < NA; ++i) s = fmaf(qv[hh][i], kv[i], s);
               for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
               if (valid[u]) {
-                s *= scale;
+                s *= scale_eff;
                 const float mn = fmaxf(m[hh], s);
-                const float corr = expf(m[hh] - mn);    // exp(-inf) = 0 on the first key
-                const float p = expf(s - mn);
+                const float corr = SoftmaxExp<T>::exp(m[hh] - mn);    // exp(-inf) = 0 on the first key
+                const float p = SoftmaxExp<T>::exp(s - mn);
                 l[hh] = l[hh] * corr + p;
 #pragma unroll
                 for (int i = 0; i < NA; ++i) acc[hh][i] = acc[hh][i] * corr + p * vv[i];
@@ -172,10 +191,10 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
         for (int i = 0; i < NA; ++i) ao[i] = __shfl_xor_sync(0xffffffffu, acc[hh][i], o);
         // keep the operand order the same on both partners
         if ((lane & o) == 0) {
-          merge_state<NA>(m[hh], l[hh], acc[hh], mo, lo2, ao);
+          merge_state<T, NA>(m[hh], l[hh], acc[hh], mo, lo2, ao);
         } else {
           float m2 = mo, l2 = lo2;
-          merge_state<NA>(m2, l2, ao, m[hh], l[hh], acc[hh]);
+          merge_state<T, NA>(m2, l2, ao, m[hh], l[hh], acc[hh]);
           m[hh] = m2; l[hh] = l2;
 #pragma unroll
           for (int i = 0; i < NA; ++i) acc[hh][i] = ao[i];
@@ -209,7 +228,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
         const float mo = recp[hd], lo2 = recp[hd + 1];
         const float mn = fmaxf(mm, mo);
         if (mn == -INFINITY) continue;
-        const float cs = expf(mm - mn), co = expf(mo - mn);
+        const float cs = SoftmaxExp<T>::exp(mm - mn), co = SoftmaxExp<T>::exp(mo - mn);
         ll = ll * cs + lo2 * co;
         aa = aa * cs + recp[d] * co;
         mm = mn;
@@ -248,7 +267,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     float mx = -INFINITY;
     for (int s2 = 0; s2 < max_splits; ++s2) mx = fmaxf(mx, sw[s2]);
     __syncthreads();
-    for (int s2 = threadIdx.x; s2 < max_splits; s2 += blockDim.x) sw[s2] = expf(sw[s2] - mx);
+    for (int s2 = threadIdx.x; s2 < max_splits; s2 += blockDim.x) sw[s2] = SoftmaxExp<T>::exp(sw[s2] - mx);
     __syncthreads();
     float ll = 0.0f;
     for (int s2 = 0; s2 < max_splits; ++s2) ll += sl[s2] * sw[s2];
@@ -283,7 +302,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __rest
   float mx = -INFINITY;
   for (int s = 0; s < max_splits; ++s) mx = fmaxf(mx, sw[s]);
   __syncthreads();
-  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) sw[s] = expf(sw[s] - mx);   // empty chunk: exp(-inf) = 0
+  for (int s = threadIdx.x; s < max_splits; s += blockDim.x) sw[s] = SoftmaxExp<T>::exp(sw[s] - mx);   // empty chunk: exp(-inf) = 0
   __syncthreads();
   float ll = 0.0f;
   for (int s = 0; s < max_splits; ++s) ll += sl[s] * sw[s];
