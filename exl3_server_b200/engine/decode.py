@@ -152,31 +152,35 @@ class DecodeRunner:
             raise RuntimeError("decode runner: a sequence outgrew the page table")
         host_table[row, :len(pages)] = torch.as_tensor(pages, dtype=torch.int32)
 
-    def load(self, slots: Sequence[int], lengths: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
+    def load(self, slots: Sequence[Optional[int]], lengths: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
         """Binds rows 0.. to the given slots at the given lengths (each row's
-        next token runs at that position); the other rows pad."""
+        next token runs at that position).  Rows beyond the list, and rows
+        whose slot is None, pad: pad page, position 0, never advancing."""
         cache = self.engine.cache
         n = len(slots)
+        live = [s is not None for s in slots]
         if tokens is not None:
             self.set_tokens(tokens)
         h = self.tok_pos.writable()
         h.zero_()
-        h[:n] = torch.as_tensor(list(lengths), dtype=torch.int32)
+        h[:n] = torch.as_tensor([int(l) if ok else 0 for l, ok in zip(lengths, live)], dtype=torch.int32)
         self.tok_pos.upload()
         h = self.pos_inc.writable()
         h.zero_()
-        h[:n] = 1
+        h[:n] = torch.as_tensor([1 if ok else 0 for ok in live], dtype=torch.int32)
         self.pos_inc.upload()
         h = self.slot_ids.writable()
         h.fill_(cache.pad_slot)
-        h[:n] = torch.as_tensor(list(slots), dtype=torch.int32)
+        h[:n] = torch.as_tensor([s if s is not None else cache.pad_slot for s in slots], dtype=torch.int32)
         self.slot_ids.upload()
         for gi, g in enumerate(cache.groups):
             t = self.tables[gi].writable()
             t.fill_(-1)
-            t[n:, 0] = cache.pad_page
+            t[:, 0] = cache.pad_page
             for r, s in enumerate(slots):
-                self._write_pages(t, r, g.pages[s])
+                if s is not None:
+                    t[r, 0] = -1
+                    self._write_pages(t, r, g.pages[s])
             self.tables[gi].upload()
 
     def set_tokens(self, tokens: Sequence[int]) -> None:
@@ -207,18 +211,31 @@ def runner_for(engine, n_rows: int, max_len: int) -> DecodeRunner:
     return engine.decode_runners[key]
 
 
+class FetchedIds:
+    """Token ids on their way to the host; ``get()`` waits for the copy."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, n: int):
+        self.host, self.event, self.n = host, event, n
+
+    def get(self) -> List[int]:
+        self.event.synchronize()
+        return self.host[:self.n].tolist()
+
+
 class DecodeSession:
     """A fixed set of sequences that advance one token per step.
 
     ``step(tokens)`` feeds the given token ids (host) or, with ``None``, the
     argmax of the previous step, which never leaves the device.  Pages are
     reserved as sequences cross page boundaries and the cache's lengths are
-    kept in step.
+    kept in step.  ``fetch_ids()`` starts the copy of the last step's argmax to
+    the host, so that the next step can be launched before the host looks at
+    it; ``park(rows)`` turns rows whose sequence has ended into padding.
     """
 
     def __init__(self, engine, slots: Sequence[int], first_tokens: Optional[Sequence[int]], max_new: int = 0):
         self.engine = engine
-        self.slots = list(slots)
+        self.slots: List[Optional[int]] = list(slots)
         cache = engine.cache
         self.lens = [cache.length(s) for s in self.slots]
         horizon = max(self.lens) + (max_new if max_new > 0 else 4 * SPLIT_BUCKET)
@@ -226,16 +243,18 @@ class DecodeSession:
         self._reserve()
         self.runner.load(self.slots, self.lens, first_tokens)
         self.launches_per_step = 0
+        self._pinned = [torch.zeros(self.runner.rows, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._fetches = 0
 
     def _reserve(self) -> Dict[int, int]:
-        """Makes sure every row has a page for its next position; returns the
-        rows whose page lists grew."""
+        """Makes sure every live row has a page for its next position; returns
+        the rows whose page lists grew."""
         cache = self.engine.cache
         page = cache.page_size
         grew: Dict[int, int] = {}
         want: Dict[int, int] = {}
         for r, s in enumerate(self.slots):
-            if any(len(g.pages[s]) * page <= self.lens[r] for g in cache.groups):
+            if s is not None and any(len(g.pages[s]) * page <= self.lens[r] for g in cache.groups):
                 want[s] = self.lens[r] + 1
                 grew[r] = s
         if want:
@@ -247,11 +266,12 @@ class DecodeSession:
         the sequences (valid until the next step)."""
         cache = self.engine.cache
         page = cache.page_size
-        if max(self.lens) + 1 > self.runner.width * page:
+        longest = max([n for n, s in zip(self.lens, self.slots) if s is not None] + [0])
+        if longest + 1 > self.runner.width * page:
             if tokens is None:
                 raise RuntimeError("decode session: contexts outgrew the page table while tokens are fed "
                                    "on the device; give max_new when the session is made")
-            self.runner = runner_for(self.engine, len(self.slots), max(self.lens) + 4 * SPLIT_BUCKET)
+            self.runner = runner_for(self.engine, len(self.slots), longest + 4 * SPLIT_BUCKET)
             self._reserve()
             self.runner.load(self.slots, self.lens, None)
         else:
@@ -260,10 +280,12 @@ class DecodeSession:
                 self.runner.push_tables(grew)
         if tokens is not None:
             self.runner.set_tokens(tokens)
-        logits = self.runner.run(max(self.lens) + 1)
+        logits = self.runner.run(longest + 1)
         self.launches_per_step = self.runner.launches.get(self.runner.last_bucket, 0)
         shrunk: Dict[int, int] = {}
         for r, s in enumerate(self.slots):
+            if s is None:
+                continue
             self.lens[r] += 1
             if self.lens[r] % page == 0:
                 if cache.commit(s, self.lens[r]):          # a windowed group gave pages back
@@ -280,8 +302,31 @@ class DecodeSession:
         """The argmax of the last step's logits, on the device."""
         return self.runner.next_ids[:len(self.slots)]
 
+    def fetch_ids(self) -> FetchedIds:
+        """Starts copying the last step's argmax to pinned host memory (it must
+        be asked for before the next step is launched, which overwrites it)."""
+        host = self._pinned[self._fetches % len(self._pinned)]
+        self._fetches += 1
+        host.copy_(self.runner.next_ids, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return FetchedIds(host, ev, len(self.slots))
+
+    def park(self, rows: Sequence[int]) -> None:
+        """The sequences of these rows have ended: their rows become padding
+        (steps already launched still wrote into their own pages, nothing
+        later does).  The cache learns their final lengths."""
+        cache = self.engine.cache
+        for r in rows:
+            s = self.slots[r]
+            if s is not None:
+                cache.commit(s, self.lens[r])
+                self.slots[r] = None
+        # positions come from the host's count, which includes the steps in flight
+        self.runner.load(self.slots, self.lens, None)
+
     def close(self) -> None:
         cache = self.engine.cache
         for s, n in zip(self.slots, self.lens):
-            if cache.slots.is_live(s):
+            if s is not None and cache.slots.is_live(s):
                 cache.commit(s, n)

@@ -52,7 +52,8 @@ def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, ca
     request may grow to its prompt plus ``max_tokens`` tokens, counted in whole
     pages."""
     def need(n: int) -> int:
-        return (n + max_tokens + PAGE - 1) // PAGE * PAGE
+        # one token more than asked for: greedy decoding runs one step ahead of the host
+        return (n + max_tokens + 1 + PAGE - 1) // PAGE * PAGE
 
     batches: List[List[int]] = []
     cur: List[int] = []
@@ -96,62 +97,117 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
 def _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token) -> None:
     slots = {i: engine.open() for i in batch}
     samplers = {i: RowSampler(opt.sample, i, prompts[i]) for i in batch}
-    live = list(batch)
+    state = {"d0": 0.0}
+
+    def emit(i: int, tok: int) -> bool:
+        """Records a token; True when the request has ended (its slot is freed at once)."""
+        r = results[i]
+        r.tokens.append(tok)
+        r.completion_tokens += 1
+        if on_token is not None:
+            on_token(i, tok)
+        if not opt.ignore_eos and tok in stops:
+            r.finish_reason = "stop"
+        elif r.completion_tokens >= opt.max_tokens:
+            r.finish_reason = "length"
+        if r.finish_reason:
+            r.decode_seconds = time.perf_counter() - state["d0"]
+            return True
+        return False
+
     session = None
+    live = list(batch)
     try:
         t0 = time.perf_counter()
         logits = engine.step([StepEntry(slots[i], prompts[i], "last") for i in live])
-        argmax = None
-        first = True
-        d0 = t0
-        while live:
-            if cancelled is not None and cancelled():
-                for i in live:
-                    results[i].finish_reason = "cancelled"
-                break
-            picked = sample_rows(logits, [samplers[i] for i in live], argmax)
-            if first:
-                # the prefill ends when its logits have been used once
-                pf = time.perf_counter() - t0
-                for i in live:
-                    results[i].prefill_seconds = pf
-                d0 = time.perf_counter()
-                first = False
-            nxt = []
-            retired = False
-            for i, tok in zip(live, picked):
-                r = results[i]
-                r.tokens.append(tok)
-                r.completion_tokens += 1
-                if on_token is not None:
-                    on_token(i, tok)
-                if not opt.ignore_eos and tok in stops:
-                    r.finish_reason = "stop"
-                elif r.completion_tokens >= opt.max_tokens:
-                    r.finish_reason = "length"
-                if r.finish_reason:
-                    r.decode_seconds = time.perf_counter() - d0
-                    if session is not None:
-                        session.close()
-                        session = None
-                    engine.close(slots.pop(i))          # the slot is free for the next batch at once
-                    retired = True
-                else:
-                    nxt.append((i, tok))
-            live = [i for i, _ in nxt]
-            if not live:
-                break
-            if session is None or retired:
-                if session is not None:
-                    session.close()
-                remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
-                session = engine.decode_session([slots[i] for i in live], max_new=remaining)
-            logits = session.step([tok for _, tok in nxt])
-            argmax = session.next_ids
-        for i in live:                                   # cancelled rows
-            results[i].decode_seconds = time.perf_counter() - d0
+        if cancelled is not None and cancelled():              # polled before every sampling (src/engine.cpp:344)
+            for i in live:
+                results[i].finish_reason = "cancelled"
+                results[i].prefill_seconds = time.perf_counter() - t0
+            return
+        picked = sample_rows(logits, [samplers[i] for i in live])
+        pf = time.perf_counter() - t0              # the prefill ends when its logits have been used once
+        for i in live:
+            results[i].prefill_seconds = pf
+        state["d0"] = time.perf_counter()
+        nxt = []
+        for i, tok in zip(live, picked):
+            if emit(i, tok):
+                engine.close(slots.pop(i))
+            else:
+                nxt.append((i, tok))
+        live = [i for i, _ in nxt]
+        if not live:
+            return
+        remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
+        session = engine.decode_session([slots[i] for i in live], max_new=remaining + 1)
+        greedy = all(samplers[i].opt.greedy and not samplers[i].opt.has_penalties for i in live)
+        if greedy and hasattr(session, "fetch_ids"):
+            _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state)
+        else:
+            session = _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, cancelled, state)
     finally:
         if session is not None:
             session.close()
         for s in slots.values():
             engine.close(s)
+
+
+def _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, cancelled, state):
+    """One step, then the host samples, then the next step.  Any sampler."""
+    live = [i for i, _ in nxt]
+    while live:
+        if cancelled is not None and cancelled():
+            for i in live:
+                results[i].finish_reason = "cancelled"
+                results[i].decode_seconds = time.perf_counter() - state["d0"]
+            break
+        logits = session.step([tok for _, tok in nxt])
+        picked = sample_rows(logits, [samplers[i] for i in live], session.next_ids)
+        nxt, retired = [], False
+        for i, tok in zip(live, picked):
+            if emit(i, tok):
+                if session is not None:
+                    session.close()
+                    session = None
+                engine.close(slots.pop(i))              # the slot is free for the next batch at once
+                retired = True
+            else:
+                nxt.append((i, tok))
+        live = [i for i, _ in nxt]
+        if live and (session is None or retired):
+            if session is not None:
+                session.close()
+            remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
+            session = engine.decode_session([slots[i] for i in live], max_new=remaining + 1)
+    return session
+
+
+def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, cancelled, state) -> None:
+    """Greedy decoding one step ahead of the host.  The argmax of a step feeds
+    the next step on the device, so step k + 1 is launched before the host has
+    seen the tokens of step k; the host reads them (pinned copy) and decides
+    who has ended while the GPU works.  A row that ended has run one step too
+    many into its own pages, is turned into padding, and its slot is freed."""
+    alive = [True] * len(rows)
+    session.step(first_tokens)
+    pending = session.fetch_ids()
+    while True:
+        if cancelled is not None and cancelled():
+            for r, i in enumerate(rows):
+                if alive[r]:
+                    results[i].finish_reason = "cancelled"
+                    results[i].decode_seconds = time.perf_counter() - state["d0"]
+            return
+        session.step(None)                      # launched before the pending tokens are looked at
+        following = session.fetch_ids()
+        toks = pending.get()
+        ended = [r for r, i in enumerate(rows) if alive[r] and emit(i, toks[r])]
+        if ended:
+            session.park(ended)
+            for r in ended:
+                alive[r] = False
+                engine.close(slots.pop(rows[r]))
+        if not any(alive):
+            return
+        pending = following
