@@ -224,11 +224,21 @@ def main() -> int:
     n_new = Kst + W
     e2e_prompts = prompts(B, C - n_new)
     e2e_opt = E.GenerateOptions(max_tokens=n_new, ignore_eos=True, max_batch=B)
+    from exl3_server_b200.engine.decode import TRANSFERRED
+
+    def timed_generate(opt):
+        before = dict(TRANSFERRED)
+        res = engine.generate(e2e_prompts, opt)
+        steps = max(r.completion_tokens for r in res) - 1
+        rate = sum(r.completion_tokens - 1 for r in res) / max(r.decode_seconds for r in res)
+        return rate, (TRANSFERRED["h2d"] - before["h2d"]) / steps, (TRANSFERRED["d2h"] - before["d2h"]) / steps
+
     engine.generate(e2e_prompts, e2e_opt)               # untimed: records the decode graph this shape needs
-    res = engine.generate(e2e_prompts, e2e_opt)
-    e2e = sum(r.completion_tokens - 1 for r in res) / max(r.decode_seconds for r in res)
-    h2d = 4 * (4 * B + (B + 1) + 8 + B * ((C + 63) // 64))      # ids, positions, rows, slots, starts, page tables
-    d2h = 4 * B
+    # default user path: greedy, the next step is launched before the host reads the last one's ids
+    e2e, h2d, d2h = timed_generate(e2e_opt)
+    # the same with the host feeding every step's token ids (what sampling with filters does)
+    fed_opt = E.GenerateOptions(max_tokens=n_new, ignore_eos=True, max_batch=B, run_ahead=False)
+    e2e_fed, h2d_fed, d2h_fed = timed_generate(fed_opt)
 
     # ---- prefill of one prompt ------------------------------------------------
     T = args.prefill_tokens
@@ -272,7 +282,10 @@ def main() -> int:
                    "page_size": 64, "l2": "inputs exceed L2 (weights and cache read per step)",
                    "peaks": peak_src},
         "clocks": clk,
-        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "host_fed": {"value": e2e_fed, "h2d_bytes_per_step": h2d_fed, "d2h_bytes_per_step": d2h_fed},
+                "note": "decode tok/s inside Engine.generate after its prefill (prompts: host lists, one pinned "
+                        "H2D copy); greedy ids feed the next step on the GPU and are read by the host every step"},
         "gpu_launches": int(launches),
         "prefill": prefill_rec,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",

@@ -36,6 +36,11 @@ def _pow2(n: int) -> int:
     return p
 
 
+# Bytes moved between host and device by decode sessions since the process began
+# (token ids and page-table rows up, token ids down); the benchmark reads them.
+TRANSFERRED = {"h2d": 0, "d2h": 0}
+
+
 class _Staged:
     """A device buffer with a pinned host copy.  The host copy is rewritten
     only after the previous upload from it has run."""
@@ -52,6 +57,7 @@ class _Staged:
 
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
+        TRANSFERRED["h2d"] += self.host.numel() * 4
         if self.event is None:
             self.event = torch.cuda.Event()
         self.event.record()
@@ -308,6 +314,7 @@ class DecodeSession:
         host = self._pinned[self._fetches % len(self._pinned)]
         self._fetches += 1
         host.copy_(self.runner.next_ids, non_blocking=True)
+        TRANSFERRED["d2h"] += host.numel() * 4
         ev = torch.cuda.Event()
         ev.record()
         return FetchedIds(host, ev, len(self.slots))

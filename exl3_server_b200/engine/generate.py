@@ -35,6 +35,7 @@ class GenerateOptions:
     ignore_eos: bool = False
     stop_token_ids: Optional[Sequence[int]] = None   # None: the model's eos ids
     max_batch: int = 64                         # most requests that start together
+    run_ahead: bool = True                      # greedy: launch step k + 1 before reading step k's tokens
 
 
 @dataclass
@@ -142,7 +143,7 @@ def _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
         remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
         session = engine.decode_session([slots[i] for i in live], max_new=remaining + 1)
         greedy = all(samplers[i].opt.greedy and not samplers[i].opt.has_penalties for i in live)
-        if greedy and hasattr(session, "fetch_ids"):
+        if greedy and opt.run_ahead and hasattr(session, "fetch_ids"):
             _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state)
         else:
             session = _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, cancelled, state)

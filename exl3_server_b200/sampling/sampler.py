@@ -36,7 +36,10 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[RowSampler],
     if logits.is_cuda and not any(r.opt.has_penalties for r in rows):
         from ..ops import kernels as K
         if all(r.opt.greedy for r in rows):
-            picked = (device_argmax if device_argmax is not None else K.argmax(logits)).cpu().tolist()
+            ids = device_argmax if device_argmax is not None else K.argmax(logits)
+            picked = ids.cpu().tolist()
+            from ..engine.decode import TRANSFERRED
+            TRANSFERRED["d2h"] += ids.numel() * 4
             for r, t in zip(rows, picked):
                 r.context.append(t)
             return picked
