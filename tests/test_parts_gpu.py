@@ -317,3 +317,152 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, d
     finally:
         unregister_architecture(["ToyEmaLM", "toy_ema"])
         unregister("mixer", "test_ema")
+
+
+# -- more toy parts from outside: a routed feed-forward and another position encoding ----
+
+class RoutedFeedForward:
+    """Two experts, each a small gated MLP; a token goes to the expert whose
+    router logit is larger (float32 logits) and is scaled by the softmax weight."""
+
+    @staticmethod
+    def tensor_specs(spec, prefix):
+        from exl3_server_b200.weights import TensorSpec
+        out = [TensorSpec(prefix + "router.weight", (2, spec.width))]
+        for e in range(2):
+            out += [TensorSpec(prefix + f"experts.{e}.gate_proj.weight", (spec.inner, spec.width)),
+                    TensorSpec(prefix + f"experts.{e}.up_proj.weight", (spec.inner, spec.width)),
+                    TensorSpec(prefix + f"experts.{e}.down_proj.weight", (spec.width, spec.inner))]
+        return out
+
+    def __init__(self, spec, tensors, prefix, ctx):
+        from exl3_server_b200.parts import FeedForwardSpec, feed_forward_class
+        self.router = tensors[prefix + "router.weight"].float()
+        dense = feed_forward_class("swiglu")
+        self.experts = [dense(FeedForwardSpec("swiglu", spec.width, spec.inner), tensors, prefix + f"experts.{e}.", ctx)
+                        for e in range(2)]
+
+    def forward(self, x, batch):
+        logits = x.float() @ self.router.T                       # router logits in float32
+        w = torch.softmax(logits, dim=-1)
+        pick = (logits[:, 1] > logits[:, 0]).to(x.dtype).unsqueeze(1)
+        # both experts run on every token (a toy: no grouping), the unpicked one is masked out;
+        # no host decision, so the same code runs inside the decode graph
+        y0, y1 = self.experts[0].forward(x, batch), self.experts[1].forward(x, batch)
+        scale = torch.where(pick.bool(), w[:, 1:2], w[:, 0:1]).to(x.dtype)
+        return (y0 * (1 - pick) + y1 * pick) * scale
+
+
+class HalfSpeedRope:
+    """Rotary embedding whose positions advance at half speed (a stand-in for
+    scaled variants): same kernel, other frequency table and position scale."""
+
+    def __init__(self, spec, head_dim, ctx):
+        self.dims = spec.dims
+        d = torch.arange(0, spec.dims // 2, dtype=torch.float64)
+        self.inv_freq = (spec.theta ** (-2.0 * d / spec.dims)).float().to(ctx.device)
+
+    def rotate_and_store(self, qkv, batch, kv, heads, kv_heads, head_dim):
+        from exl3_server_b200.ops import kernels as K
+        K.rope_kv_write(qkv, self.inv_freq, self.dims, 0.5, batch.tok_pos, batch.tok_seq, kv.block_table,
+                        kv.k if kv.owns else None, kv.v if kv.owns else None, heads, kv_heads, head_dim,
+                        kv.page_size, kv.owns)
+
+
+@dataclass
+class Toy2Config:
+    width: int
+    vocab: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["width"], d["vocab"])
+
+    def to_dict(self):
+        return {"architectures": ["ToyRoutedLM"], "width": self.width, "vocab": self.vocab}
+
+
+def toy2_plan(cfg):
+    from exl3_server_b200.parts import (EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerSpec, MixerSpec, ModelPlan,
+                                        NormSpec, PositionSpec, ScheduleEntry)
+    layers = []
+    for i in range(2):
+        p = f"t.{i}."
+        layers.append(LayerSpec(
+            "prenorm",
+            MixerSpec("attention", width=cfg.width, heads=2, kv_heads=2, head_dim=16,
+                      position=PositionSpec("test_half_speed_rope", dims=16, theta=50.0)),
+            FeedForwardSpec("test_routed" if i == 1 else "swiglu", cfg.width, 40),
+            NormSpec("rms", cfg.width, 1e-5), NormSpec("rms", cfg.width, 1e-5), 1.0,
+            names={"mixer": p + "a.", "feed_forward": p + "f.", "mixer_norm": p + "n1.", "feed_forward_norm": p + "n2."}))
+    return ModelPlan("ToyRoutedLM", EmbeddingSpec(cfg.vocab, cfg.width, 1.0, "t.emb"), layers,
+                     [ScheduleEntry(0), ScheduleEntry(1)], NormSpec("rms", cfg.width, 1e-5), "t.norm.",
+                     HeadSpec(cfg.vocab, cfg.width, 1.0, False, "t.head"), max_positions=0)
+
+
+def toy2_plain_logits(w, cfg, ids):
+    w = {k: v.double() for k, v in w.items()}
+    L = len(ids)
+    h = w["t.emb"][torch.tensor(ids)]
+    for i in range(2):
+        p = f"t.{i}."
+        r = P.rms_norm(h, w[p + "n1.weight"], 1e-5)
+        q = P.linear(r, w[p + "a.q_proj.weight"]).view(L, 2, 16).transpose(0, 1)
+        k = P.linear(r, w[p + "a.k_proj.weight"]).view(L, 2, 16).transpose(0, 1)
+        v = P.linear(r, w[p + "a.v_proj.weight"]).view(L, 2, 16).transpose(0, 1)
+        pos = torch.arange(L, dtype=P.F) * 0.5                          # half-speed positions
+        q, k = P.rope(q, pos, 50.0), P.rope(k, pos, 50.0)
+        h = h + P.linear(P.attention(q, k, v).transpose(0, 1).reshape(L, -1), w[p + "a.o_proj.weight"])
+        r = P.rms_norm(h, w[p + "n2.weight"], 1e-5)
+        if i == 0:
+            y = P.swiglu(r, w[p + "f.gate_proj.weight"], w[p + "f.up_proj.weight"], w[p + "f.down_proj.weight"])
+        else:
+            logits = r @ w[p + "f.router.weight"].T
+            sm = torch.softmax(logits, -1)
+            y = torch.empty_like(r)
+            for t in range(L):
+                e = 1 if logits[t, 1] > logits[t, 0] else 0
+                y[t] = sm[t, e] * P.swiglu(r[t:t + 1], w[p + f"f.experts.{e}.gate_proj.weight"],
+                                           w[p + f"f.experts.{e}.up_proj.weight"],
+                                           w[p + f"f.experts.{e}.down_proj.weight"])[0]
+        h = h + y
+    return P.linear(P.rms_norm(h, w["t.norm.weight"], 1e-5), w["t.head"])
+
+
+def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding of its own, both
+    defined here, registered and run through the engine in float32 (where a
+    routing decision cannot flip by rounding of the activations)."""
+    from exl3_server_b200 import Engine
+    from exl3_server_b200.config import register_architecture, unregister_architecture
+    from exl3_server_b200.engine.model import plan_manifest
+    from exl3_server_b200.parts import register_feed_forward, register_position, unregister
+    from exl3_server_b200.weights import write_safetensors
+    from exl3_server_b200.weights.random_init import random_tensors
+    cfg = Toy2Config(width=32, vocab=40)
+    register_feed_forward("test_routed", RoutedFeedForward)
+    register_position("test_half_speed_rope", HalfSpeedRope)
+    register_architecture(["ToyRoutedLM"], Toy2Config, toy2_plan)
+    try:
+        folder = str(tmp_path)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg.to_dict(), f)
+        tensors = dict(random_tensors(plan_manifest(toy2_plan(cfg)), seed=5, std=0.2, norm_std=0.1))
+        write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=512)
+        rng = np.random.default_rng(1)
+        reqs = {f"r{i}": rng.integers(0, cfg.vocab, n).tolist() for i, n in enumerate([50, 7, 33])}
+        want = {rid: toy2_plain_logits(tensors, cfg, t).numpy() for rid, t in reqs.items()}
+        ids = list(reqs)
+        for trace in (whole_trace(reqs), tail_trace(reqs, 32),
+                      batched_trace(reqs, [ids], {ids[0]: 40, ids[1]: 1, ids[2]: 33})):
+            got = run_trace(eng, trace)
+            for rid in got:
+                assert rel_err(got[rid], want[rid]) <= 2e-5, rid
+        # both experts were used, so the routing was exercised
+        r = torch.randn(64, 32, dtype=torch.float64) @ tensors["t.1.f.router.weight"].double().T
+        assert 0 < int((r[:, 1] > r[:, 0]).sum()) < 64
+    finally:
+        unregister_architecture(["ToyRoutedLM"])
+        unregister("feed_forward", "test_routed")
+        unregister("position", "test_half_speed_rope")
