@@ -40,6 +40,8 @@ int exl3_gemv_bf16(const void* x, const void* w, const void* bias, void* y, int 
 int exl3_gemm_tc(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int epilogue,
                  cudaStream_t stream);
 int exl3_gemm_tc_status();
+// Launches a kernel whose only wait can never be satisfied (short limit): status becomes 9.
+int exl3_gemm_tc_wait_selftest(cudaStream_t stream);
 
 // Attention of single query tokens over the paged cache.  Token t belongs to
 // batch row tok_seq[t] and sits at position tok_pos[t]; it sees keys

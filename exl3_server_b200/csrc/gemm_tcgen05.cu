@@ -53,9 +53,9 @@ __device__ inline void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TC_WAIT_LIMIT) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -262,6 +262,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
 }
 
+// A wait that nothing will ever satisfy, with a short limit: shows that a kernel
+// of this file gives up, records its code (9) and returns, leaving the context usable.
+__global__ void wait_selftest_kernel() {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (!mbar_wait(&bar, 0, 1u << 14) && threadIdx.x == 0) atomicExch(&g_tc_error, 9);
+}
+
 // ---- host side --------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -315,6 +327,11 @@ extern "C" int exl3_gemm_tc_status() {
   cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
   if (v) { int z = 0; cudaMemcpyToSymbol(g_tc_error, &z, sizeof(int)); }
   return v;
+}
+
+extern "C" int exl3_gemm_tc_wait_selftest(cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>();
+  return launch_status("gemm_tc_wait_selftest");
 }
 
 extern "C" int exl3_gemm_tc(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,

@@ -207,6 +207,11 @@ def gemm_tc_status() -> int:
     return int(library().exl3_gemm_tc_status())
 
 
+def gemm_tc_wait_selftest() -> None:
+    """Runs a kernel whose mbarrier wait is never satisfied; it must give up and set status 9."""
+    _check(library().exl3_gemm_tc_wait_selftest(_stream()), "gemm_tc_wait_selftest")
+
+
 def attn_tokens_scratch_bytes(T: int, heads: int, head_dim: int, max_splits: int) -> int:
     lib = library()
     lib.exl3_attn_tokens_scratch_bytes.restype = _c_size_t

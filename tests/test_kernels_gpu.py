@@ -161,6 +161,20 @@ def test_gemm_tc_gated(M, I, Kd):
     assert K().gemm_tc_status() == 0
 
 
+def test_gemm_tc_waits_are_bounded():
+    """A wait that nothing satisfies runs out, the kernel records a code and
+    returns; the context stays usable and the next GEMM is right."""
+    torch.cuda.synchronize()
+    assert K().gemm_tc_status() == 0
+    K().gemm_tc_wait_selftest()
+    torch.cuda.synchronize()
+    assert K().gemm_tc_status() == 9
+    assert K().gemm_tc_status() == 0                     # reading clears it
+    x = torch.randn(130, 64, device=DEV).bfloat16()
+    w = torch.randn(24, 64, device=DEV).bfloat16()
+    close(K().gemm_tc(x, w, None), x.double() @ w.double().T, TOL[torch.bfloat16], "gemm_tc after a timed-out wait")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(17, 64, device=DEV).bfloat16()
