@@ -63,6 +63,15 @@ int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype,
                       int hd, int page, int window, float scale, cudaStream_t stream);
 
 size_t exl3_argmax_scratch_bytes(int R, int V);
+// The same on tcgen05 tensor cores with TMA loads from the paged cache (heads of 64, tiles of 128 queries).
+int exl3_attn_prefill_tc_supported(int dtype, int hd, int page);
+int exl3_attn_prefill_tc_status();
+int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
+                         const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
+                         const int* row_start, const int* row_pos0, const int* tile_seq, const int* tile_q0,
+                         int n_tiles, int nh, int nkv, int hd, int page, int window, float scale,
+                         cudaStream_t stream);
+
 int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,
                 cudaStream_t stream);
 int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature, int* out,

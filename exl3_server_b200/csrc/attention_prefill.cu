@@ -189,14 +189,16 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int p_a = p_first + wrow + mt * 16 + gid, p_b = p_a + 8;
-        if (need_mask) {
+        if (need_mask) {                                  // selects, no branch per score
+          const int lo_a = (window > 0) ? p_a - window : -1, lo_b = (window > 0) ? p_b - window : -1;
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int key = key0 + nb * 8 + tig * 2 + (j & 1);
-              const int p = (j < 2) ? p_a : p_b;
-              if (key > p || (window > 0 && key <= p - window)) s[mt][nb][j] = -INFINITY;
+              const int p = (j < 2) ? p_a : p_b, lo = (j < 2) ? lo_a : lo_b;
+              const bool dead = (key > p) | (key <= lo);
+              s[mt][nb][j] = dead ? -INFINITY : s[mt][nb][j];
             }
           }
         }

@@ -1,0 +1,469 @@
+// Causal grouped-query attention of whole prompts over the paged cache on the
+// 5th-generation tensor cores (heads of 64, bfloat16, pages of 64 keys).
+//
+// Same mathematics as attention_prefill.cu and attention_simt.cu (the
+// reference's masked scaled-dot-product attention, src/model.cpp:539-548,
+// 576-578).  A block owns 128 consecutive queries of one sequence and one head
+// and walks the key pages its queries may see:
+//
+//   warp 4     issues everything asynchronous: TMA copies of the Q tile and of
+//              K and V pages (straight from the paged cache, 128B-swizzled),
+//              S = Q K^T and O += P V as tcgen05.mma with accumulators in tensor
+//              memory (two S buffers of 64 columns, O in 64, two P buffers of 32)
+//   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It reads its row
+//              of S with tcgen05.ld (no shuffles: the whole row is in its
+//              registers), masks, takes 2^(s * scale - m) with one multiply-add
+//              and one ex2 per score, writes P as bfloat16 back into tensor memory
+//              (the A operand of the second product is read from there), and at the
+//              end reads O, divides by the row sum and stores 128 bytes.
+//
+// O is rescaled lazily: the maximum used for the exponentials only moves when a
+// row's true maximum has grown by more than 2^8, so P stays below 256 and the
+// accumulator in tensor memory is touched (tcgen05.ld / st) only then.
+//
+// Every mbarrier wait is bounded; a kernel that gives up records a code that
+// exl3_attn_prefill_tc_status() returns, frees its tensor memory and exits.
+#include "api.h"
+#include "common.cuh"
+
+#include <cuda.h>
+#include <math.h>
+
+namespace exl3 {
+
+constexpr int FA_BQ = 128, FA_BK = 64, FA_HD = 64;
+constexpr int FA_THREADS = 160;
+constexpr int FA_TMEM_COLS = 256;                 // S0 (64) | S1 (64) | O (64) | P0 (32) | P1 (32)
+constexpr uint32_t FA_Q_BYTES = FA_BQ * FA_HD * 2, FA_KV_BYTES = FA_BK * FA_HD * 2;
+constexpr int FA_KV_STAGES = 5;
+constexpr uint32_t FA_SMEM = FA_Q_BYTES + 2 * FA_KV_STAGES * FA_KV_BYTES + 1024 + 256;
+constexpr uint32_t FA_WAIT_LIMIT = 1u << 24;   // polls of a few tens of cycles: a fraction of a second
+constexpr float FA_RESCALE_STEP = 8.0f;           // in base-2 units
+
+static __device__ int g_fa_error = 0;
+
+__device__ inline uint32_t fa_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ inline void fa_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fa_smem_u32(bar)), "r"(count));
+}
+__device__ inline void fa_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fa_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ inline void fa_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem_u32(bar)) : "memory");
+}
+__device__ inline bool fa_mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = fa_smem_u32(bar);
+  for (uint32_t i = 0; i < FA_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ inline void fa_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(fa_smem_u32(dst)), "l"(map), "r"(fa_smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ inline void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ inline void fa_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(fa_smem_u32(bar)) : "memory");
+}
+// Shared-memory operand descriptors (128B swizzle, version 1): K-major tiles have
+// rows of 128 bytes in groups of 8 rows, 1024 bytes apart; the MN-major V tile
+// has the same bytes, read as 8-key groups 1024 bytes apart.
+__device__ inline uint64_t fa_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16, D float32, A and B bfloat16, M = 128, N = 64; B K-major (S) or MN-major (PV)
+constexpr uint32_t FA_IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t FA_IDESC_PV = FA_IDESC_S | (1u << 16);
+
+__device__ inline void fa_umma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// the same with the A operand in tensor memory (lanes = rows, two bfloat16 per column)
+__device__ inline void fa_umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ inline void fa_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ inline void fa_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ inline void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ inline void fa_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ inline float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ inline uint32_t fa_pack(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
+                       const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
+                       const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
+  extern __shared__ unsigned char fa_smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = base;                                  // [128][64] bf16
+  unsigned char* sK = sQ + FA_Q_BYTES;                       // [stages][64][64]
+  unsigned char* sV = sK + FA_KV_STAGES * FA_KV_BYTES;       // [stages][64][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + FA_KV_STAGES * FA_KV_BYTES);
+  uint64_t* q_full = bars;                        // Q tile landed
+  uint64_t* kv_full = bars + 1;                   // [stages] K and V page landed
+  uint64_t* kv_free = kv_full + FA_KV_STAGES;     // [stages] the products that read the stage are done
+  uint64_t* s_full = kv_free + FA_KV_STAGES;      // [2] S buffer written by the tensor core
+  uint64_t* s_free = s_full + 2;                  // [2] S buffer read by all 128 softmax threads
+  uint64_t* p_full = s_free + 2;                  // [2] P buffer written by all 128 softmax threads
+  uint64_t* pv_done = p_full + 2;                 // [2] O += P V of that P buffer finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // tiles are listed by rising position; the ones with most keys to visit start first
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int b = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = row_start[b + 1] - row_start[b];
+  const int pos0 = row_pos0[b];
+  const int g = head / (nh / nkv);
+  const int rows = min(FA_BQ, n_new - q0);
+  const int p_first = pos0 + q0, p_last = pos0 + q0 + rows - 1;
+  const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int page_lo = k_lo / FA_BK, page_hi = p_last / FA_BK;
+  const int n_blocks = page_hi - page_lo + 1;
+  const int* bt = block_table + (int64_t)b * bt_stride;
+
+  if (threadIdx.x == 0) {
+    fa_mbar_init(q_full, 1);
+    for (int i = 0; i < FA_KV_STAGES; ++i) {
+      fa_mbar_init(kv_full + i, 1);
+      fa_mbar_init(kv_free + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      fa_mbar_init(s_full + i, 1);
+      fa_mbar_init(s_free + i, 128);
+      fa_mbar_init(p_full + i, 128);
+      fa_mbar_init(pv_done + i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem_u32(tmem_slot)), "r"(FA_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fa_fence_before();
+  __syncthreads();
+  fa_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;                  // columns: S0 0..63, S1 64..127, O 128..191
+  const uint32_t tmem_p = tmem_base + 192;                  // P0 192..223, P1 224..255 (two bfloat16 per column)
+  bool ok = true;
+
+  if (warp == 4) {
+    // ---- issuer: TMA and MMA -----------------------------------------------------------
+    if (lane == 0) {
+      fa_mbar_expect_tx(q_full, FA_Q_BYTES);
+      fa_tma_2d(sQ, &map_q, q_full, head * FA_HD, row_start[b] + q0);
+    }
+    auto load_kv = [&](int j) {                             // page j of this block's walk -> stage j % 3
+      const int st = j % FA_KV_STAGES;
+      const int pg = bt[page_lo + j];
+      if (lane == 0) {
+        fa_mbar_expect_tx(kv_full + st, 2 * FA_KV_BYTES);
+        fa_tma_2d(sK + st * FA_KV_BYTES, &map_k, kv_full + st, 0, (pg * nkv + g) * FA_BK);
+        fa_tma_2d(sV + st * FA_KV_BYTES, &map_v, kv_full + st, 0, (pg * nkv + g) * FA_BK);
+      }
+    };
+    auto issue_s = [&](int j) {                             // S[j & 1] = Q K_j^T
+      const int sb = j & 1, st = j % FA_KV_STAGES;
+      if (lane == 0) {
+        const uint64_t da = fa_desc(fa_smem_u32(sQ)), db = fa_desc(fa_smem_u32(sK + st * FA_KV_BYTES));
+#pragma unroll
+        for (int k = 0; k < FA_HD / 16; ++k) fa_umma(tmem_base + sb * 64, da + 2 * k, db + 2 * k, FA_IDESC_S, k > 0);
+        fa_commit(s_full + sb);
+      }
+      __syncwarp();
+    };
+    int loaded = 0;                                          // pages whose copies were started
+    for (; loaded < FA_KV_STAGES && loaded < n_blocks; ++loaded) load_kv(loaded);
+    ok = fa_mbar_wait(q_full, 0) && fa_mbar_wait(kv_full + 0, 0);
+    if (ok) { fa_fence_after(); issue_s(0); }
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int sb = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      // S of the next page while the softmax of this one runs
+      if (j + 1 < n_blocks) {
+        if (!fa_mbar_wait(kv_full + (j + 1) % FA_KV_STAGES, ((j + 1) / FA_KV_STAGES) & 1)) { ok = false; break; }
+        if (j + 1 >= 2 && !fa_mbar_wait(s_free + (sb ^ 1), (((j + 1) >> 1) - 1) & 1)) { ok = false; break; }
+        fa_fence_after();
+        issue_s(j + 1);
+      }
+      // O += P_j V_j
+      if (!fa_mbar_wait(p_full + sb, ph)) { ok = false; break; }
+      fa_fence_after();
+      if (lane == 0) {
+        const int st = j % FA_KV_STAGES;
+        const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES));
+#pragma unroll
+        for (int k = 0; k < FA_BK / 16; ++k)                // 16 keys: 8 columns of P, 16 rows of V
+          fa_umma_ts(tmem_o, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        fa_commit(pv_done + sb);
+        fa_commit(kv_free + st);
+      }
+      __syncwarp();
+      // Refill, off the critical path: the stage of page j - 1 was released a whole softmax
+      // ago, so this wait is over at once; waiting for page j's own products here would put
+      // the tensor core's latency into every iteration.
+      if (j >= 1 && loaded < n_blocks && loaded - FA_KV_STAGES <= j - 1) {
+        const int f = loaded - FA_KV_STAGES;                 // the page whose stage is reused
+        if (!fa_mbar_wait(kv_free + f % FA_KV_STAGES, (f / FA_KV_STAGES) & 1)) { ok = false; break; }
+        load_kv(loaded++);
+      }
+    }
+    if (!ok) {
+      // copies still in flight must land before the block's shared memory goes away
+      for (int j = max(0, loaded - FA_KV_STAGES); j < loaded; ++j)
+        fa_mbar_wait(kv_full + j % FA_KV_STAGES, (j / FA_KV_STAGES) & 1);
+    }
+    if (!ok && lane == 0) atomicExch(&g_fa_error, 1);
+  } else {
+    // ---- softmax and epilogue: thread r = query row r = TMEM lane r ---------------------
+    const int r = threadIdx.x;                               // 0..127
+    const int p = p_first + r;                               // this row's position
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_used = -INFINITY, l_run = 0.0f;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!fa_mbar_wait(s_full + st, ph)) { ok = false; break; }
+      fa_fence_after();
+      uint32_t sr[2][32];
+      fa_ld32(tmem_base + lane_addr + st * 64, sr[0]);
+      fa_ld32(tmem_base + lane_addr + st * 64 + 32, sr[1]);
+      fa_wait_ld();
+      fa_fence_before();
+      fa_mbar_arrive(s_free + st);
+      const int key0 = (page_lo + j) * FA_BK;
+      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
+      // four independent chains for the maximum (and below for the sum): the row is long and
+      // a single chain would make every step wait for the one before
+      // masking without branches (one test per page decides whether the page needs it at all)
+      if (need_mask) {
+        const int lo_key = (window > 0) ? p - window : -1;    // keys <= lo_key are out of the window
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int key = key0 + h * 32 + c;
+            const bool dead = (key > p) | (key <= lo_key);
+            sr[h][c] = dead ? 0xff800000u : sr[h][c];         // -inf
+          }
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      mx *= scale_log2;                                      // scale > 0: max and scale commute
+      // lazy rescale: move the reference maximum only when it is far behind
+      const bool grow = mx > m_used + FA_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : m_used;
+        const float corr = (m_used == -INFINITY) ? 0.0f : fa_exp2(m_used - m_new);   // 1 for rows that keep theirs
+        if (j > 0) {
+          // every earlier product must have landed in O before it is rewritten
+          if (!fa_mbar_wait(pv_done + (st ^ 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
+          fa_fence_after();
+          uint32_t o[2][32];
+          fa_ld32(tmem_o + lane_addr, o[0]);
+          fa_ld32(tmem_o + lane_addr + 32, o[1]);
+          fa_wait_ld();
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[h][c] = __float_as_uint(__uint_as_float(o[h][c]) * corr);
+          fa_st32(tmem_o + lane_addr, o[0]);
+          fa_st32(tmem_o + lane_addr + 32, o[1]);
+          fa_wait_st();
+          fa_fence_before();
+        }
+        l_run *= corr;
+        m_used = m_new;
+      }
+      const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+      // the P buffer of two pages ago must have been consumed
+      if (j >= 2 && !fa_mbar_wait(pv_done + st, ((j - 2) >> 1) & 1)) { ok = false; break; }
+      uint32_t pw[32];
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {                         // two keys per column
+        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), scale_log2, -mref));
+        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), scale_log2, -mref));
+        sum4[c & 3] += e0 + e1;
+        pw[c] = fa_pack(e0, e1);
+      }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l_run += sum;
+      fa_st32(tmem_p + lane_addr + st * 32, pw);
+      fa_wait_st();
+      fa_fence_before();
+      fa_mbar_arrive(p_full + st);
+    }
+    if (ok) {
+      // last product done -> O complete
+      const int jl = n_blocks - 1;
+      ok = fa_mbar_wait(pv_done + (jl & 1), (jl >> 1) & 1);
+      if (ok) {
+        fa_fence_after();
+        uint32_t o[2][32];
+        fa_ld32(tmem_o + lane_addr, o[0]);
+        fa_ld32(tmem_o + lane_addr + 32, o[1]);
+        fa_wait_ld();
+        if (r < rows) {
+          const float inv = 1.0f / l_run;
+          __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * FA_HD;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint4 w;
+            const int c = ch * 8;
+            w.x = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 0]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
+            w.y = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
+            w.z = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
+            w.w = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c) = w;
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(&g_fa_error, 2);
+  }
+
+  fa_fence_before();
+  __syncthreads();
+  fa_fence_after();
+  if (warp == 4)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FA_TMEM_COLS) : "memory");
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static FaEncodeFn fa_encode_fn() {
+  static FaEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<FaEncodeFn>(p);
+  }();
+  return fn;
+}
+// [rows, cols] bfloat16 with a row pitch in elements; boxes of box_rows x 64 columns, 128B swizzle.
+static int fa_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t pitch, int box_rows) {
+  FaEncodeFn fn = fa_encode_fn();
+  if (!fn) { set_error("attn_prefill_tc: the driver has no cuTensorMapEncodeTiled"); return ERR_UNSUPPORTED; }
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("attn_prefill_tc: cuTensorMapEncodeTiled failed with %d", (int)r); return ERR_BAD_ARGUMENT; }
+  return 0;
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" int exl3_attn_prefill_tc_supported(int dtype, int hd, int page) {
+  return dtype == DT_BF16 && hd == FA_HD && page == FA_BK;
+}
+extern "C" int exl3_attn_prefill_tc_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_fa_error, sizeof(int));
+  if (v) { int z = 0; cudaMemcpyToSymbol(g_fa_error, &z, sizeof(int)); }
+  return v;
+}
+
+// q: rows of the fused q|k|v buffer (row stride q_row_stride elements, T rows in all); tiles of 128 queries.
+// n_pool_rows = pages * kv_heads * 64 rows of head_dim in each of k_pool and v_pool.
+extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
+                                    const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
+                                    const int* row_start, const int* row_pos0, const int* tile_seq,
+                                    const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
+                                    float scale, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  if (!exl3_attn_prefill_tc_supported(DT_BF16, hd, page)) {
+    set_error("attn_prefill_tc: needs bfloat16, head_dim 64 and pages of 64, got head_dim %d page %d", hd, page);
+    return ERR_UNSUPPORTED;
+  }
+  if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || nh > 65535 || window < 0 || q_row_stride % 8 != 0) {
+    set_error("attn_prefill_tc: bad sizes tiles=%d T=%d heads=%d kv_heads=%d window=%d", n_tiles, T, nh, nkv, window);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out)) {
+    set_error("attn_prefill_tc: q, k, v and out must be 16-byte aligned");
+    return ERR_ALIGNMENT;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM);
+    if (e != cudaSuccess) { set_error("attn_prefill_tc: cannot get %u bytes of shared memory: %s", FA_SMEM, cudaGetErrorString(e)); return (int)e; }
+    configured = true;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  int rc = fa_make_map(&map_q, q, T, (int64_t)nh * hd, q_row_stride, FA_BQ);
+  if (rc) return rc;
+  rc = fa_make_map(&map_k, k_pool, n_pool_rows, hd, hd, FA_BK);
+  if (rc) return rc;
+  rc = fa_make_map(&map_v, v_pool, n_pool_rows, hd, hd, FA_BK);
+  if (rc) return rc;
+  dim3 grid(n_tiles, nh);
+  attn_prefill_tc_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(
+      map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
+      tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+  return launch_status("attn_prefill_tc");
+}

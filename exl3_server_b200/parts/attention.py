@@ -85,8 +85,16 @@ class Attention:
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> None:
         s = self.spec
         T = qkv.shape[0]
+        if batch.max_new > 1 and batch.tiles and K.attn_prefill_tc_supported(qkv.dtype, s.head_dim, kv.page_size):
+            # prompts, heads of 64: streaming softmax with both products on tcgen05 tensor cores,
+            # TMA loads straight from the paged cache, a block per 128 queries
+            tile_seq, tile_q0, n_tiles = batch.tiles[128]
+            K.attn_prefill_tc(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
+                              tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
+                              self.scale)
+            return
         if batch.max_new > 1 and batch.tiles and K.attn_prefill_supported(qkv.dtype, s.head_dim, kv.page_size):
-            # prompts: streaming-softmax kernel on the tensor cores, a block per tile of queries
+            # prompts, heads of 128: the same on mma.sync tensor cores, a block per tile of queries
             tile_seq, tile_q0, n_tiles = batch.tiles[K.attn_prefill_tile(s.head_dim)]
             K.attn_prefill(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
                            tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,

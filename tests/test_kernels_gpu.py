@@ -318,6 +318,26 @@ def test_attn_prefill(nh, nkv, hd, window):
     close(out, case.reference(window, scale), 1e-2, "attn_prefill")
 
 
+@pytest.mark.parametrize("nh,nkv", [(3, 3), (4, 2), (8, 1)])
+@pytest.mark.parametrize("window", [0, 24, 100])
+def test_attn_prefill_tc(nh, nkv, window):
+    hd = 64
+    case = PagedCase(lens=[300, 64, 1, 700, 65, 128, 129], new=[300, 64, 1, 200, 65, 1, 129], nh=nh, nkv=nkv, hd=hd,
+                     dtype=torch.bfloat16, seed=hd + nh + window)
+    T = case.q.shape[0]
+    buf = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    buf[:, :nh * hd] = case.q.reshape(T, nh * hd).to(DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    scale = 1.3 / math.sqrt(hd)
+    assert K().attn_prefill_tc_supported(torch.bfloat16, hd, 64)
+    tile_seq, tile_q0 = case.tiles(128)
+    K().attn_prefill_tc(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
+                        tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale)
+    torch.cuda.synchronize()
+    assert K().attn_prefill_tc_status() == 0
+    close(out, case.reference(window, scale), 1e-2, "attn_prefill_tc")
+
+
 def test_attn_prefill_is_refused_for_other_shapes():
     assert not K().attn_prefill_supported(torch.float32, 64, 64)
     assert not K().attn_prefill_supported(torch.bfloat16, 48, 64)
