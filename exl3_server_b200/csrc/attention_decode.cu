@@ -1,0 +1,630 @@
+// Attention of decoded tokens over the paged key/value cache: TMA into shared
+// memory, both products on the tensor cores (mma.sync), bfloat16, heads of 64,
+// pages of 64 keys.
+//
+//   s[j] = (q . K[j]) * scale,  j in [max(0, pos - window + 1), pos]
+//   out  = sum_j softmax(s)[j] * V[j]
+//
+// as in the reference's call of scaled-dot-product attention with an additive
+// causal mask (src/model.cpp:539-548, 576-578); query head h reads key/value
+// head h / (heads / kv_heads).
+//
+// A decoded token reads every key and value of its sequence once and does two
+// multiply-adds per element: the kernel is bound by memory, and on the CUDA
+// cores by the instructions that unpack and multiply the elements.  Here a
+// page of keys is the 16-row operand of the matrix instruction (keys x
+// features), the queries of the kv head's group are the 8 columns, and the
+// scores come out transposed: S^T = K Q^T, then O^T = V^T P^T with V read
+// through ldmatrix.trans and P^T made from the score registers by movmatrix.
+// One page costs a warp 32 matrix instructions instead of some 600 scalar ones.
+//
+// Work item: (token, kv head, chunk of split_keys keys), one warp each.  A
+// chunk is aligned to absolute positions, so for a given split_keys the way
+// keys are grouped, and therefore every rounding, depends only on the token's
+// own position: not on the batch, not on how the tokens were cut into steps.
+// The chunks that hold keys are counted at the start (a token's position gives
+// its chunks; shared memory holds the running sums), and the list of all of
+// them, ordered by token, kv head and chunk, is cut into equal shares for the
+// warps of a grid that fills the GPU once: sequences of unequal lengths are
+// balanced, and a warp's chunks are neighbours, so that their pages follow one
+// another in the block table.  Every warp has a ring of page buffers of its own,
+// filled by TMA (128-byte swizzle, so that ldmatrix meets no bank conflicts)
+// several pages ahead and across the ends of chunks; warps never wait for each
+// other.  The chunks of a (token, kv head) are merged in chunk order by the
+// warp that reports them last (a counter at the start of the scratch memory
+// tells it); the scratch must be zero when it is first used and is left with
+// zero counters by every launch.
+//
+// Scores, running maximum, running sum and the output accumulator are float32;
+// the probabilities are rounded to bfloat16 for the second product.
+//
+// Cache layout: pool[page][kv_head][slot][head_dim], page = block_table[row][pos / page_size].
+#include "api.h"
+#include "common.cuh"
+
+#include <cuda.h>
+#include <algorithm>
+#include <math.h>
+
+namespace exl3 {
+
+constexpr int AD_WARPS = 4;
+constexpr int AD_HD = 64, AD_PAGE = 64;
+constexpr int AD_MAX_GROUP = 8;                            // query heads per kv head: the columns of one instruction
+constexpr int AD_TILE_BYTES = AD_PAGE * AD_HD * 2;         // one page of one kv head: 8 KB
+constexpr int AD_STAGE_BYTES = 2 * AD_TILE_BYTES;          // keys, then values
+constexpr int AD_STAGES = 3;
+constexpr uint32_t AD_SMEM = AD_WARPS * AD_STAGES * AD_STAGE_BYTES + 1024;
+constexpr int AD_MAX_TOKENS = 1024;                        // positions, sequences and chunk counts kept in shared memory
+constexpr int AD_MAX_SPLITS = 256;                         // chunks of one (token, kv head)
+constexpr int AD_COUNTER_SLOTS = 65536;                    // ints at the start of scratch, as in attention_simt.cu
+constexpr uint32_t AD_WAIT_LIMIT = 1u << 24;               // polls of a few tens of cycles: a fraction of a second
+
+static __device__ int g_ad_error = 0;
+
+__device__ inline uint32_t ad_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ inline void ad_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ad_smem_u32(bar)), "r"(count));
+}
+__device__ inline void ad_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ad_smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded: false when the copy did not land within the limit.
+__device__ inline bool ad_mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = ad_smem_u32(bar);
+  for (uint32_t i = 0; i < AD_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ inline void ad_tma_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(ad_smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ inline void ad_ldsm(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ inline void ad_ldsm_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ inline void ad_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// An 8x8 matrix of 16-bit elements, one row of pairs per group of four lanes, transposed across the warp.
+__device__ inline uint32_t ad_transpose(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ inline float ad_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ inline uint32_t ad_pack(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Record layout in scratch: [64] accumulator, then max (base-2 units), then sum; as in attention_simt.cu.
+//
+// Under load every round trip to memory takes microseconds (the queues are full of pages on
+// their way), so a warp waits for none of them per chunk: positions and sequences of all tokens
+// are copied to shared memory at the start; page numbers are asked for 32 pages at a time, one
+// batch ahead; queries are asked for one (token, kv head) ahead; records are stored and left
+// behind, and one fence at the end of the warp's work covers them all before it draws tickets.
+__global__ void __launch_bounds__(AD_WARPS * 32, 1)
+attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
+                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
+                   const int* __restrict__ tok_seq, int T, int nh, int nkv, int window, float scale_log2,
+                   int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters) {
+  extern __shared__ unsigned char ad_smem_raw[];
+  __shared__ uint64_t full[AD_WARPS][AD_STAGES];
+  __shared__ int s_pos[AD_MAX_TOKENS], s_seq[AD_MAX_TOKENS];
+  __shared__ int s_cum[AD_MAX_TOKENS + 1];               // chunks of the tokens before this one (per kv head)
+  __shared__ float s_w[AD_WARPS][AD_MAX_SPLITS], s_l[AD_WARPS][AD_MAX_SPLITS];   // a merge's weights and sums
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gl = lane >> 2, tl = lane & 3;
+  const uint32_t ring = ((ad_smem_u32(ad_smem_raw) + 1023u) & ~1023u) + warp * (AD_STAGES * AD_STAGE_BYTES);
+  uint64_t* bars = full[warp];
+  if (lane == 0) {
+    for (int s = 0; s < AD_STAGES; ++s) ad_mbar_init(bars + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+  pdl_trigger();
+
+  // ---- every token's chunks, counted and summed ------------------------------------------------
+  // A token at position pos reads keys lo .. pos; its chunks are the aligned pieces of split_keys
+  // keys that this range touches, numbered from 0.
+  auto first_key = [&](int pos) { return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0; };
+  for (int i = threadIdx.x; i < T; i += blockDim.x) {
+    const int pos = __ldcg(tok_pos + i);
+    s_pos[i] = pos;
+    s_seq[i] = __ldcg(tok_seq + i);
+    s_cum[i + 1] = min(pos / split_keys - first_key(pos) / split_keys + 1, max_splits);
+  }
+  if (threadIdx.x == 0) s_cum[0] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (T + 31) / 32;                       // each lane sums a stretch of tokens, then the stretches are chained
+    const int a = min(lane * per, T), b = min(a + per, T);
+    int sum = 0;
+    for (int i = a; i < b; ++i) sum += s_cum[i + 1];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+    for (int i = a; i < b; ++i) { run += s_cum[i + 1]; s_cum[i + 1] = run; }
+  }
+  __syncthreads();
+
+  const int G = nh / nkv;
+  const int rec = AD_HD + 2;
+  // This warp's share: chunks i0 .. i1 - 1 of the list ordered by token, kv head, chunk.
+  const int n_chunks = nkv * s_cum[T];
+  const int n_warps = gridDim.x * AD_WARPS, gw = blockIdx.x * AD_WARPS + warp;
+  const int i0 = (int)((int64_t)gw * n_chunks / n_warps), i1 = (int)((int64_t)(gw + 1) * n_chunks / n_warps);
+
+  auto chunks_of = [&](int t) { return s_cum[t + 1] - s_cum[t]; };
+  auto base_of = [&](int t, int g) { return nkv * s_cum[t] + g * chunks_of(t); };   // index of chunk 0 of (t, g)
+  // the token whose chunks hold index i
+  auto token_of = [&](int i) {
+    int lo = 0, hi = T - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (nkv * s_cum[mid] <= i) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+  };
+  // keys of chunk sp of token t
+  auto chunk_keys = [&](int t, int sp, int& c_lo, int& c_hi) {
+    const int pos = s_pos[t], lo = first_key(pos);
+    const int c = lo / split_keys + sp;
+    c_lo = max(lo, c * split_keys);
+    c_hi = min(pos + 1, (c + 1) * split_keys);
+  };
+
+  // ldmatrix addresses inside a swizzled tile: row r at r * 128 bytes, its 16-byte piece c at c ^ (r & 7)
+  const uint32_t k_row = ((lane & 7) + ((lane >> 3) & 1) * 8) * 128;
+  const uint32_t v_row = ((lane & 7) + ((lane >> 4) & 1) * 8) * 128 + AD_TILE_BYTES;
+  uint32_t k_col[4], v_col[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    k_col[j] = (uint32_t)(((2 * j + (lane >> 4)) ^ (lane & 7)) << 4);
+    v_col[j] = (uint32_t)(((2 * j + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
+  }
+
+  // ---- the producer: pages in the order the chunks will want them -----------------------------
+  // The chunks of one (token, kv head) that this warp holds are neighbours, and so are their
+  // pages: a run.  Page numbers come 32 at a time (lane i holds page0 + i), one batch ahead.
+  struct Batch { int t, g, page0, run_last; bool some; };
+  auto run_of = [&](int t, int g, Batch& bt) {           // the pages of (t, g) inside i0 .. i1
+    const int base = base_of(t, g);
+    const int sp_a = max(i0 - base, 0), sp_b = min(i1 - base, chunks_of(t)) - 1;
+    int c_lo, c_hi;
+    chunk_keys(t, sp_a, c_lo, c_hi);
+    bt.page0 = c_lo / AD_PAGE;
+    chunk_keys(t, sp_b, c_lo, c_hi);
+    bt.run_last = (c_hi - 1) / AD_PAGE;
+    bt.t = t;
+    bt.g = g;
+    bt.some = true;
+  };
+  auto batch_after = [&](const Batch& cur, Batch& nx) {
+    nx = cur;
+    if (cur.page0 + 32 <= cur.run_last) { nx.page0 = cur.page0 + 32; return; }
+    int t = cur.t, g = cur.g + 1;
+    if (g == nkv) { g = 0; ++t; }
+    if (t >= T || base_of(t, g) >= i1) { nx.some = false; return; }
+    run_of(t, g, nx);
+  };
+  auto fetch = [&](const Batch& bt) {
+    const int idx = bt.page0 + lane;
+    return (bt.some && idx <= bt.run_last) ? __ldcg(block_table + (int64_t)s_seq[bt.t] * bt_stride + idx) : 0;
+  };
+  Batch cur_b, nxt_b;
+  cur_b.some = false;
+  int cur_pages = 0, nxt_pages = 0, p_pi = 1, p_end = 0;   // pages p_pi .. p_end of the current batch are still to ask for
+  int t0 = 0, g0 = 0, sp0 = 0;
+  nxt_b.some = false;
+  if (i0 < i1) {
+    t0 = token_of(i0);
+    const int r = i0 - nkv * s_cum[t0];
+    g0 = r / chunks_of(t0);
+    sp0 = r - g0 * chunks_of(t0);
+    run_of(t0, g0, nxt_b);
+  }
+  nxt_pages = fetch(nxt_b);
+  uint32_t pn = 0;                                       // pages asked for
+  auto produce = [&]() {
+    if (p_pi > p_end) {
+      if (!nxt_b.some) return;                           // no page left for this warp
+      cur_b = nxt_b;
+      cur_pages = nxt_pages;
+      p_pi = cur_b.page0;
+      p_end = min(cur_b.page0 + 31, cur_b.run_last);
+      batch_after(cur_b, nxt_b);
+      nxt_pages = fetch(nxt_b);
+    }
+    const int pg = __shfl_sync(0xffffffffu, cur_pages, p_pi - cur_b.page0);
+    if (lane == 0) {
+      const uint32_t s = pn % AD_STAGES;
+      const uint32_t dst = ring + s * AD_STAGE_BYTES;
+      const int row = (pg * nkv + cur_b.g) * AD_PAGE;
+      ad_mbar_expect_tx(bars + s, AD_STAGE_BYTES);
+      ad_tma_2d(dst, &map_k, bars + s, 0, row);
+      ad_tma_2d(dst + AD_TILE_BYTES, &map_v, bars + s, 0, row);
+    }
+    ++p_pi;
+    ++pn;
+  };
+#pragma unroll 1
+  for (int s = 0; s < AD_STAGES; ++s) produce();
+
+  // Q^T as the right operand: column gl is query head gl of the group, zero beyond the group
+  auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[4][2]) {
+    const unsigned* qrow = reinterpret_cast<const unsigned*>(q + (int64_t)t * q_row_stride +
+                                                             (int64_t)(g * G + gl) * AD_HD);
+    const bool live = some && gl < G;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      qq[j][0] = live ? __ldcg(qrow + 8 * j + tl) : 0u;
+      qq[j][1] = live ? __ldcg(qrow + 8 * j + tl + 4) : 0u;
+    }
+  };
+  // the (token, kv head) after (t, g), if this warp holds chunks of it
+  auto next_run = [&](int t, int g, int& nt, int& ng) {
+    nt = t;
+    ng = g + 1;
+    if (ng == nkv) { ng = 0; ++nt; }
+    return nt < T && base_of(nt, ng) < i1;
+  };
+
+  // ---- merging the chunks of a (token, kv head): the same sums in chunk order, whoever does it --
+  auto merge = [&](int mt, int mg) {
+    float* wv = s_w[warp];
+    float* lv = s_l[warp];
+    const int n_rec = chunks_of(mt);
+    for (int n = 0; n < G; ++n) {
+      const int head = mg * G + n;
+      const float* base = scratch + ((int64_t)mt * nh + head) * max_splits * rec;
+      // Lanes take the chunks' maxima and sums side by side, then their accumulators sixteen
+      // chunks at a time: a few round trips to memory, however many chunks there are.
+      float M = -INFINITY;
+      for (int s2 = lane; s2 < n_rec; s2 += 32) {
+        const float ms = __ldcg(base + (int64_t)s2 * rec + AD_HD);
+        lv[s2] = __ldcg(base + (int64_t)s2 * rec + AD_HD + 1);
+        wv[s2] = ms;
+        M = fmaxf(M, ms);
+      }
+      M = warp_max(M);
+      float ll = 0.0f;
+      for (int s2 = lane; s2 < n_rec; s2 += 32) {
+        const float w = ad_exp2(wv[s2] - M);
+        wv[s2] = w;
+        ll += lv[s2] * w;
+      }
+      ll = warp_sum(ll);
+      __syncwarp();
+      float a0 = 0.0f, a1 = 0.0f;
+      for (int s0 = 0; s0 < n_rec; s0 += 16) {
+        float v0[16], v1[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float* r = base + (int64_t)(s0 + u) * rec;
+          const bool in = s0 + u < n_rec;
+          v0[u] = in ? __ldcg(r + lane) : 0.0f;
+          v1[u] = in ? __ldcg(r + lane + 32) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float w = s0 + u < n_rec ? wv[s0 + u] : 0.0f;
+          a0 += v0[u] * w;
+          a1 += v1[u] * w;
+        }
+      }
+      __nv_bfloat16* dst = out + ((int64_t)mt * nh + head) * AD_HD;
+      dst[lane] = __float2bfloat16(a0 / ll);
+      dst[lane + 32] = __float2bfloat16(a1 / ll);
+      __syncwarp();                                      // before the next head's weights
+    }
+    if (lane == 0) counters[(int64_t)mt * nkv + mg] = 0;   // zero again for the next launch
+  };
+
+  // ---- the consumer: chunk after chunk ---------------------------------------------------------
+  uint32_t cn = 0;                                       // pages used
+  bool ok = true;
+  int t = t0, g = g0, sp = sp0;
+  uint32_t qb[4][2], qn[4][2];
+  int nt = 0, ng = 0;
+  bool nsome = false;
+  if (i0 < i1) {
+    load_q(t, g, true, qb);
+    nsome = next_run(t, g, nt, ng);
+    load_q(nt, ng, nsome, qn);                           // used when this warp gets to (nt, ng)
+  }
+#pragma unroll 1
+  for (int i = i0; i < i1 && ok; ++i) {
+    int c_lo, c_hi;
+    chunk_keys(t, sp, c_lo, c_hi);
+    const int first_page = c_lo / AD_PAGE, last_page = (c_hi - 1) / AD_PAGE;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[a][e] = 0.0f;
+    }
+#pragma unroll 1
+    for (int pi = first_page; pi <= last_page; ++pi) {
+      const uint32_t st = cn % AD_STAGES;
+      if (!ad_mbar_wait(bars + st, (cn / AD_STAGES) & 1)) { ok = false; break; }
+      const uint32_t kb = ring + st * AD_STAGE_BYTES;
+      // S^T = K Q^T: s[a] holds keys 16 a + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
+      float s[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[a][e] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t f[4];
+          ad_ldsm(f, kb + a * 2048 + k_row + k_col[j]);
+          ad_mma(s[a], f, qb[j][0], qb[j][1]);
+        }
+      }
+      const int key0 = pi * AD_PAGE;
+      if (key0 < c_lo || key0 + AD_PAGE > c_hi) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const int ka = key0 + 16 * a + gl, kb2 = ka + 8;
+          const bool da = (ka < c_lo) | (ka >= c_hi), db = (kb2 < c_lo) | (kb2 >= c_hi);
+          s[a][0] = da ? -INFINITY : s[a][0];
+          s[a][1] = da ? -INFINITY : s[a][1];
+          s[a][2] = db ? -INFINITY : s[a][2];
+          s[a][3] = db ? -INFINITY : s[a][3];
+        }
+      }
+      float mx[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        mx[c] = fmaxf(fmaxf(fmaxf(s[0][c], s[0][c + 2]), fmaxf(s[1][c], s[1][c + 2])),
+                      fmaxf(fmaxf(s[2][c], s[2][c + 2]), fmaxf(s[3][c], s[3][c + 2])));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
+      }
+      float corr[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float mn = fmaxf(m[c], mx[c] * scale_log2);   // a page in the chunk has a live key: finite
+        corr[c] = ad_exp2(m[c] - mn);                        // 0 on the first page
+        m[c] = mn;
+      }
+      // P^T as the right operand of the second product, by transposing 8x8 pieces across the warp
+      uint32_t pb[4][2];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float p0 = ad_exp2(fmaf(s[a][0], scale_log2, -m[0]));
+        const float p1 = ad_exp2(fmaf(s[a][1], scale_log2, -m[1]));
+        const float p2 = ad_exp2(fmaf(s[a][2], scale_log2, -m[0]));
+        const float p3 = ad_exp2(fmaf(s[a][3], scale_log2, -m[1]));
+        l[0] = l[0] * (a == 0 ? corr[0] : 1.0f) + (p0 + p2);
+        l[1] = l[1] * (a == 0 ? corr[1] : 1.0f) + (p1 + p3);
+        pb[a][0] = ad_transpose(ad_pack(p0, p1));
+        pb[a][1] = ad_transpose(ad_pack(p2, p3));
+      }
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        o[d][0] *= corr[0];
+        o[d][1] *= corr[1];
+        o[d][2] *= corr[0];
+        o[d][3] *= corr[1];
+      }
+      // O^T += V^T P^T: o[d] holds features 16 d + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          uint32_t f[4];
+          ad_ldsm_t(f, kb + a * 2048 + v_row + v_col[d]);
+          ad_mma(o[d], f, pb[a][0], pb[a][1]);
+        }
+      }
+      __syncwarp();                                      // every lane has read the stage
+      ++cn;
+      produce();                                         // refill it with the page AD_STAGES ahead
+    }
+    if (!ok) break;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 8);
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 16);
+    }
+    // ---- the chunk's result ------------------------------------------------------------------
+    const int n_rec = chunks_of(t);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int n = 2 * tl + c;
+      if (n >= G) continue;
+      const int head = g * G + n;
+      if (n_rec == 1) {
+        __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * AD_HD;
+        const float inv = 1.0f / l[c];
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          dst[16 * d + gl] = __float2bfloat16(o[d][c] * inv);
+          dst[16 * d + gl + 8] = __float2bfloat16(o[d][c + 2] * inv);
+        }
+      } else {
+        float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          sc[16 * d + gl] = o[d][c];
+          sc[16 * d + gl + 8] = o[d][c + 2];
+        }
+        if (gl == 0) { sc[AD_HD] = m[c]; sc[AD_HD + 1] = l[c]; }
+      }
+    }
+    // on to the next chunk; a new (token, kv head) brings its queries, asked for a run ago
+    if (++sp == n_rec) {
+      sp = 0;
+      t = nt;
+      g = ng;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { qb[j][0] = qn[j][0]; qb[j][1] = qn[j][1]; }
+      if (nsome) {
+        nsome = next_run(t, g, nt, ng);
+        load_q(nt, ng, nsome, qn);
+      }
+    }
+  }
+  if (ok) {
+    // All of this warp's records are written.  One fence for all of them, then a ticket per chunk,
+    // lanes side by side; the chunks of a (token, kv head) are merged by the warp that draws the
+    // last ticket.  Which warp that is varies; what it computes does not.
+    __threadfence();
+    __syncwarp();
+    for (int k0 = i0; k0 < i1; k0 += 32) {
+      int mt = 0, mg = 0;
+      bool last = false;
+      if (k0 + lane < i1) {
+        mt = token_of(k0 + lane);
+        const int n_rec = chunks_of(mt);
+        mg = (k0 + lane - nkv * s_cum[mt]) / n_rec;
+        if (n_rec > 1) last = atomicAdd(counters + (int64_t)mt * nkv + mg, 1) == n_rec - 1;
+      }
+      unsigned todo = __ballot_sync(0xffffffffu, last);
+      if (todo) __threadfence();
+      while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        merge(__shfl_sync(0xffffffffu, mt, src), __shfl_sync(0xffffffffu, mg, src));
+      }
+    }
+  } else {
+    // A copy did not land in time: say so, and give the copies still in flight a bounded time to
+    // land before the block's shared memory goes away.
+    if (lane == 0) atomicExch(&g_ad_error, 1);
+    for (; cn < pn; ++cn) {
+      if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
+    }
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+typedef CUresult (*AdEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static AdEncodeFn ad_encode_fn() {
+  static AdEncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<AdEncodeFn>(p);
+  }();
+  return fn;
+}
+// [rows, 64] bfloat16, rows packed; boxes of one page (64 rows), 128B swizzle.
+static int ad_make_map(CUtensorMap* map, const void* ptr, int64_t rows) {
+  AdEncodeFn fn = ad_encode_fn();
+  if (!fn) { set_error("attn_decode: the driver has no cuTensorMapEncodeTiled"); return ERR_UNSUPPORTED; }
+  const cuuint64_t dims[2] = {(cuuint64_t)AD_HD, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)AD_HD * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)AD_HD, (cuuint32_t)AD_PAGE};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("attn_decode: cuTensorMapEncodeTiled failed with %d", (int)r); return ERR_BAD_ARGUMENT; }
+  return 0;
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys,
+                                          int max_splits) {
+  return dtype == DT_BF16 && hd == AD_HD && page == AD_PAGE && T >= 0 && T <= AD_MAX_TOKENS && nkv >= 1 &&
+         nh % nkv == 0 && nh / nkv <= AD_MAX_GROUP && split_keys > 0 && split_keys % AD_PAGE == 0 &&
+         max_splits >= 1 && max_splits <= AD_MAX_SPLITS && (max_splits == 1 || (int64_t)T * nkv <= AD_COUNTER_SLOTS);
+}
+
+extern "C" int exl3_attn_decode_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_ad_error, sizeof(int));
+  if (v) { int z = 0; cudaMemcpyToSymbol(g_ad_error, &z, sizeof(int)); }
+  return v;
+}
+
+// Same arguments and the same scratch layout as exl3_attn_tokens; n_pool_rows = pages * kv_heads * 64.
+extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, const void* k_pool,
+                                const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
+                                const int* tok_pos, const int* tok_seq, int T, int nh, int nkv, int hd, int page,
+                                int window, float scale, int split_keys, int max_splits, float* scratch,
+                                size_t scratch_bytes, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
+      !exl3_attn_decode_supported(DT_BF16, T, nh, nkv, hd, page, split_keys, max_splits)) {
+    set_error("attn_decode: needs bfloat16, head_dim 64, pages of 64, at most %d tokens, %d query heads per kv "
+              "head and %d chunks of whole pages; got T=%d heads=%d kv_heads=%d head_dim=%d page=%d window=%d "
+              "split_keys=%d max_splits=%d", AD_MAX_TOKENS, AD_MAX_GROUP, AD_MAX_SPLITS, T, nh, nkv, hd, page,
+              window, split_keys, max_splits);
+    return ERR_UNSUPPORTED;
+  }
+  if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out) || q_row_stride % 8 != 0) {
+    set_error("attn_decode: q, k, v and out must be 16-byte aligned with a row stride in 16-byte units");
+    return ERR_ALIGNMENT;
+  }
+  if (exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits) > scratch_bytes) {
+    set_error("attn_decode: scratch of %zu bytes is too small, need %zu", scratch_bytes,
+              exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits));
+    return ERR_SCRATCH;
+  }
+  static int sms = 0;
+  if (!sms) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e != cudaSuccess) { set_error("attn_decode: cannot get %u bytes of shared memory: %s", AD_SMEM, cudaGetErrorString(e)); return (int)e; }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms < 1) sms = 1;
+  }
+  CUtensorMap map_k, map_v;
+  int rc = ad_make_map(&map_k, k_pool, n_pool_rows);
+  if (rc) return rc;
+  rc = ad_make_map(&map_v, v_pool, n_pool_rows);
+  if (rc) return rc;
+  const int blocks = (int)std::min<int64_t>(sms, ((int64_t)T * nkv * max_splits + AD_WARPS - 1) / AD_WARPS);
+  int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
+  float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
+  launch_pdl(attn_decode_kernel, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,
+             static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,
+             bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,
+             max_splits, records, counters);
+  return launch_status("attn_decode");
+}

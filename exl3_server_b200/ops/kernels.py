@@ -286,6 +286,38 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     return out
 
 
+def attn_decode_supported(dtype: torch.dtype, T: int, heads: int, kv_heads: int, head_dim: int, page: int,
+                          split_keys: int, max_splits: int) -> bool:
+    return bool(library().exl3_attn_decode_supported(
+        _c_int(dtype_code(dtype)), _c_int(T), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page),
+        _c_int(split_keys), _c_int(max_splits)))
+
+
+def attn_decode_status() -> int:
+    """0, or the code the decode attention kernel left when a bounded wait ran out (cleared by this call)."""
+    return int(library().exl3_attn_decode_status())
+
+
+def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, T: int, heads: int,
+                kv_heads: int, head_dim: int, page: int, window: int, scale: float, split_keys: int,
+                max_splits: int, scratch: Optional[torch.Tensor]) -> torch.Tensor:
+    """Attention of T query tokens over the paged cache on the tensor cores (see attention_decode.cu);
+    arguments and scratch as ``attn_tokens``."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
+    _contig(k_pool, "k_pool")
+    _contig(v_pool, "v_pool")
+    pool_rows = k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2]
+    nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
+    _check(library().exl3_attn_decode(
+        _ptr(q), _c_int64(q_row_stride), _ptr(out), _ptr(k_pool), _ptr(v_pool), _c_int64(pool_rows),
+        _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T), _c_int(heads),
+        _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
+        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _stream()), "attn_decode")
+    return out
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     R, V = logits.shape
     if logits.dtype != torch.float32:

@@ -103,20 +103,33 @@ class Attention:
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
             split = kv.page_size * (split // kv.page_size + 1)
+        n = self._chunks(batch.max_kv_len, split)
+        if K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
+            # decoded tokens, heads of 64: pages by TMA, both products on the tensor cores, a warp per chunk
+            scratch = None
+            if n > 1:
+                scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
+            K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
+                          s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+            return
         # bfloat16 with more work items than the GPU holds at once: chunks twice as long, so that a
         # block's fixed costs are spread over more keys.  float32 keeps one chunking for every
         # batch, so that its results do not depend on the batch at all.
         if qkv.dtype == torch.bfloat16 and T * s.kv_heads * ((batch.max_kv_len + split - 1) // split) > BUSY_ITEMS:
             split *= 2
-        n = (batch.max_kv_len + split - 1) // split
-        if s.window > 0:
-            n = min(n, (s.window + split - 2) // split + 1)
-        n = max(1, n)
+            n = self._chunks(batch.max_kv_len, split)
         scratch = None
         if n > 1:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
         K.attn_tokens(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+
+    def _chunks(self, max_kv_len: int, split: int) -> int:
+        """The most chunks of ``split`` keys that a token's keys can touch."""
+        n = (max_kv_len + split - 1) // split
+        if self.spec.window > 0:
+            n = min(n, (self.spec.window + split - 2) // split + 1)
+        return max(1, n)
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes()

@@ -299,6 +299,90 @@ def test_attn_tokens_finds_one_far_key_among_many():
     assert float((out.cpu() - case.v[0][far].reshape(1, -1)).abs().max()) > 0.1
 
 
+@pytest.mark.parametrize("nh,nkv", [(3, 3), (4, 2), (8, 1), (16, 2), (5, 5)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("split", [64, 256])
+def test_attn_decode(nh, nkv, window, split):
+    # single tokens and short prompts in one call, positions at both sides of page and chunk edges
+    hd = 64
+    lens = [300, 64, 1, 700, 65, 256, 257, 128, 513]
+    new = [1, 1, 1, 3, 1, 1, 1, 2, 1]
+    case = PagedCase(lens=lens, new=new, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    scale = 0.7 / math.sqrt(hd)
+    n = (max(lens) + split - 1) // split
+    if window > 0:
+        n = min(n, (window + split - 2) // split + 1)
+    assert K().attn_decode_supported(torch.bfloat16, T, nh, nkv, hd, 64, split, n)
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    for _ in range(2):                                  # the second call finds the counters as the first left them
+        out.fill_(7.0)
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, window, scale, split, n, scratch)
+        close(out, case.reference(window, scale), 1e-2, "attn_decode")
+    assert K().attn_decode_status() == 0
+
+
+def test_attn_decode_many_items_per_warp():
+    # more work items than the grid has warps: every warp's ring of pages runs across the ends of items,
+    # among them empty chunks of the shorter sequences
+    nh, nkv, hd = 8, 4, 64
+    g = torch.Generator().manual_seed(5)
+    lens = [int(x) for x in torch.randint(1, 1500, (48,), generator=g)]
+    case = PagedCase(lens=lens, new=[1] * len(lens), nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=11)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    split = 256
+    n = (max(lens) + split - 1) // split
+    assert T * nkv * n > 148 * 4
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                    nh, nkv, hd, 64, 0, 0.125, split, n, scratch)
+    close(out, case.reference(0, 0.125), 1e-2, "attn_decode, many items")
+    # one chunk for everything: no merge, results written directly
+    n1 = 1
+    K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                    nh, nkv, hd, 64, 0, 0.125, 2048, n1, None)
+    close(out, case.reference(0, 0.125), 1e-2, "attn_decode, one chunk")
+    assert K().attn_decode_status() == 0
+
+
+def test_attn_decode_finds_one_far_key_among_many():
+    nh = nkv = 2
+    hd = 64
+    case = PagedCase(lens=[900], new=[1], nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=3)
+    far = 37
+    kp, table = case.k_pool, case.table
+    pg = int(table[0, far // 64])
+    qv = case.q[0].float()
+    kp[pg, :, far % 64] = (qv * 40.0 / qv.norm(dim=-1, keepdim=True)).to(torch.bfloat16).to(DEV)
+    case.k[0][far] = kp[pg, :, far % 64].cpu()
+    q = case.q.reshape(1, nh * hd).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(1, nh, hd, 4) // 4, device=DEV)
+    K().attn_decode(q, q.stride(0), out, kp, case.v_pool, table, case.tok_pos, case.tok_seq, 1, nh, nkv, hd, 64, 0,
+                    1.0, 256, 4, scratch)
+    close(out, case.v[0][far].reshape(1, -1), 1e-2, "far key")
+    close(out, case.reference(0, 1.0), 1e-2, "far key vs reference")
+    K().attn_decode(q, q.stride(0), out, kp, case.v_pool, table, case.tok_pos, case.tok_seq, 1, nh, nkv, hd, 64, 800,
+                    1.0, 256, 4, scratch)
+    close(out, case.reference(800, 1.0), 1e-2, "window excludes the far key")
+    assert float((out.cpu().float() - case.v[0][far].reshape(1, -1).float()).abs().max()) > 0.1
+
+
+def test_attn_decode_is_refused_for_other_shapes():
+    assert K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.float32, 8, 4, 4, 64, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 128, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 16, 1, 64, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 100, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 5000, 4, 4, 64, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 1000)
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 2, 128), (4, 1, 128)])
 @pytest.mark.parametrize("window", [0, 24, 100])
 def test_attn_prefill(nh, nkv, hd, window):
