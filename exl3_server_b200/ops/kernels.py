@@ -286,6 +286,18 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     return out
 
 
+_SM_COUNT: dict = {}
+
+
+def sm_count(device: torch.device) -> int:
+    """Streaming multiprocessors of ``device`` (looked up once)."""
+    key = torch.device(device).index or 0
+    n = _SM_COUNT.get(key)
+    if n is None:
+        n = _SM_COUNT[key] = int(torch.cuda.get_device_properties(key).multi_processor_count)
+    return n
+
+
 def attn_decode_supported(dtype: torch.dtype, T: int, heads: int, kv_heads: int, head_dim: int, page: int,
                           split_keys: int, max_splits: int) -> bool:
     return bool(library().exl3_attn_decode_supported(

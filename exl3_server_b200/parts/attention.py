@@ -13,6 +13,7 @@ The three input projections are one fused matrix, so a step reads ``r`` once.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional
 
 import torch
@@ -100,11 +101,9 @@ class Attention:
                            tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
                            self.scale)
             return
-        split = max(SPLIT_KEYS, kv.page_size)
-        if split % kv.page_size:
-            split = kv.page_size * (split // kv.page_size + 1)
-        n = self._chunks(batch.max_kv_len, split)
-        if K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
+        split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device) if qkv.dtype == torch.bfloat16 else 0
+        n = self._chunks(batch.max_kv_len, split) if split else 0
+        if split and K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
             # decoded tokens, heads of 64: pages by TMA, both products on the tensor cores, a warp per chunk
             scratch = None
             if n > 1:
@@ -112,6 +111,10 @@ class Attention:
             K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                           s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
             return
+        split = max(SPLIT_KEYS, kv.page_size)
+        if split % kv.page_size:
+            split = kv.page_size * (split // kv.page_size + 1)
+        n = self._chunks(batch.max_kv_len, split)
         # bfloat16 with more work items than the GPU holds at once: chunks twice as long, so that a
         # block's fixed costs are spread over more keys.  float32 keeps one chunking for every
         # batch, so that its results do not depend on the batch at all.
@@ -123,6 +126,17 @@ class Attention:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
         K.attn_tokens(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+
+    def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device) -> int:
+        """Keys per chunk for the tensor-core decode kernel: about two chunks per SM's worth of warps, in whole
+        pages, 1 to 32 of them.  Every chunk costs its warp a record and a ticket, so few long chunks beat many
+        short ones once every warp has work (measured at batch 1 to 64).  The choice depends on the step's
+        size, not on a token's position: results differ between batch sizes by rounding."""
+        keys = min(max_kv_len, self.spec.window) if self.spec.window > 0 else max_kv_len
+        pages = T * self.spec.kv_heads * ((keys + page - 1) // page)
+        per = max(1.0, pages / (2.0 * K.sm_count(device)))
+        per = min(32, 1 << int(round(math.log2(per))))
+        return page * per
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
         """The most chunks of ``split`` keys that a token's keys can touch."""
