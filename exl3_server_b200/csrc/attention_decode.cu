@@ -130,7 +130,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, int T, int nh, int nkv, int window, float scale_log2,
-                   int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters) {
+                   int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
+                   const float* __restrict__ inv_freq, float pos_scale, int rotate, int write_new,
+                   __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
   extern __shared__ unsigned char ad_smem_raw[];
   __shared__ uint64_t full[AD_WARPS][AD_STAGES];
   __shared__ int s_pos[AD_MAX_TOKENS], s_seq[AD_MAX_TOKENS];
@@ -200,7 +202,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const int pos = s_pos[t], lo = first_key(pos);
     const int c = lo / split_keys + sp;
     c_lo = max(lo, c * split_keys);
-    c_hi = min(pos + 1, (c + 1) * split_keys);
+    c_hi = min(write_new ? pos : pos + 1, (c + 1) * split_keys);   // the new token's key is not in the cache yet
   };
 
   // ldmatrix addresses inside a swizzled tile: row r at r * 128 bytes, its 16-byte piece c at c ^ (r & 7)
@@ -224,7 +226,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     chunk_keys(t, sp_a, c_lo, c_hi);
     bt.page0 = c_lo / AD_PAGE;
     chunk_keys(t, sp_b, c_lo, c_hi);
-    bt.run_last = (c_hi - 1) / AD_PAGE;
+    bt.run_last = (c_hi + AD_PAGE - 1) / AD_PAGE - 1;    // below page0 when the run holds no cached key
     bt.t = t;
     bt.g = g;
     bt.some = true;
@@ -256,7 +258,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   nxt_pages = fetch(nxt_b);
   uint32_t pn = 0;                                       // pages asked for
   auto produce = [&]() {
-    if (p_pi > p_end) {
+    while (p_pi > p_end) {
       if (!nxt_b.some) return;                           // no page left for this warp
       cur_b = nxt_b;
       cur_pages = nxt_pages;
@@ -297,6 +299,35 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     ng = g + 1;
     if (ng == nkv) { ng = 0; ++nt; }
     return nt < T && base_of(nt, ng) < i1;
+  };
+
+  // ---- the position encoding, when it is this kernel's to apply -------------------------------
+  // Half-split rotary pairs (d, d + 32) with angle pos * pos_scale * inv_freq[d], as rope_kv_write does it
+  // (elementwise.cu).  A thread's fragment holds features 16 j + 2 tl + 8 h + e: a pair's two halves are its
+  // pieces j and j + 2.
+  auto angles = [&](int t, float (&cs)[8], float (&sn)[8]) {
+    const float p = (float)s_pos[t] * pos_scale;
+#pragma unroll
+    for (int idx = 0; idx < 8; ++idx) {
+      const int d = 16 * (idx >> 2) + 2 * tl + 8 * ((idx >> 1) & 1) + (idx & 1);
+      sincosf(p * __ldg(inv_freq + d), &sn[idx], &cs[idx]);
+    }
+  };
+  auto rotate_frag = [&](uint32_t (&f)[4][2], const float (&cs)[8], const float (&sn)[8]) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t x0 = f[j][h], x1 = f[j + 2][h];
+        const int idx = j * 4 + h * 2;
+        const float a0 = __uint_as_float(x0 << 16), a1 = __uint_as_float(x1 << 16);
+        const float b0 = __uint_as_float(x0 & 0xffff0000u), b1 = __uint_as_float(x1 & 0xffff0000u);
+        const float r0a = a0 * cs[idx] - a1 * sn[idx], r1a = a1 * cs[idx] + a0 * sn[idx];
+        const float r0b = b0 * cs[idx + 1] - b1 * sn[idx + 1], r1b = b1 * cs[idx + 1] + b0 * sn[idx + 1];
+        f[j][h] = ad_pack(r0a, r0b);
+        f[j + 2][h] = ad_pack(r1a, r1b);
+      }
+    }
   };
 
   // ---- merging the chunks of a (token, kv head): the same sums in chunk order, whoever does it --
@@ -357,16 +388,38 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   uint32_t qb[4][2], qn[4][2];
   int nt = 0, ng = 0;
   bool nsome = false;
+  float cs[8], sn[8];
   if (i0 < i1) {
     load_q(t, g, true, qb);
     nsome = next_run(t, g, nt, ng);
     load_q(nt, ng, nsome, qn);                           // used when this warp gets to (nt, ng)
+    if (rotate) { angles(t, cs, sn); rotate_frag(qb, cs, sn); }
   }
 #pragma unroll 1
   for (int i = i0; i < i1 && ok; ++i) {
     int c_lo, c_hi;
     chunk_keys(t, sp, c_lo, c_hi);
-    const int first_page = c_lo / AD_PAGE, last_page = (c_hi - 1) / AD_PAGE;
+    const int first_page = c_lo / AD_PAGE, last_page = c_lo < c_hi ? (c_hi - 1) / AD_PAGE : first_page - 1;
+    // The token's own key and value: the warp with the token's last chunk takes them from the projection's
+    // output (asked for now, used after the chunk's pages), rotates the key, adds the pair to the softmax as
+    // one more key and writes it to the cache.
+    const bool has_new = write_new && sp == chunks_of(t) - 1;
+    uint32_t kf[4][2];
+    unsigned short vf[8];
+    int new_page = 0;
+    if (has_new) {
+      const __nv_bfloat16* row = q + (int64_t)t * q_row_stride;
+      const unsigned* krow = reinterpret_cast<const unsigned*>(row + (int64_t)(nh + g) * AD_HD);
+      const unsigned short* vrow = reinterpret_cast<const unsigned short*>(row + (int64_t)(nh + nkv + g) * AD_HD);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[j][0] = __ldcg(krow + 8 * j + tl);
+        kf[j][1] = __ldcg(krow + 8 * j + tl + 4);
+        vf[2 * j] = __ldcg(vrow + 16 * j + gl);
+        vf[2 * j + 1] = __ldcg(vrow + 16 * j + gl + 8);
+      }
+      new_page = __ldcg(block_table + (int64_t)s_seq[t] * bt_stride + s_pos[t] / AD_PAGE);
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
     float o[4][4];
 #pragma unroll
@@ -455,6 +508,52 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       produce();                                         // refill it with the page AD_STAGES ahead
     }
     if (!ok) break;
+    if (has_new) {
+      if (rotate) rotate_frag(kf, cs, sn);
+      // to the cache, for the steps to come: the key from the lanes of query column 0, the value as it is
+      const int64_t at = (((int64_t)new_page * nkv + g) * AD_PAGE + (s_pos[t] % AD_PAGE)) * AD_HD;
+      if (new_page >= 0) {
+        if (gl == 0) {
+          unsigned* kdst = reinterpret_cast<unsigned*>(k_pool + at);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            kdst[8 * j + tl] = kf[j][0];
+            kdst[8 * j + tl + 4] = kf[j][1];
+          }
+        }
+        if (lane < 8) {
+          const uint4* vsrc = reinterpret_cast<const uint4*>(q + (int64_t)t * q_row_stride + (int64_t)(nh + nkv + g) * AD_HD);
+          reinterpret_cast<uint4*>(v_pool + at)[lane] = __ldcg(vsrc + lane);
+        }
+      }
+      // its score against this lane group's query (column gl), then to the lanes that hold that column's state
+      float dot = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          dot = fmaf(__uint_as_float(qb[j][h] << 16), __uint_as_float(kf[j][h] << 16), dot);
+          dot = fmaf(__uint_as_float(qb[j][h] & 0xffff0000u), __uint_as_float(kf[j][h] & 0xffff0000u), dot);
+        }
+      }
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float sc = __shfl_sync(0xffffffffu, dot, (2 * tl + c) * 4) * scale_log2;
+        const float mn = fmaxf(m[c], sc);
+        const float corr = ad_exp2(m[c] - mn);               // 0 when the cache held no key of this chunk
+        const uint32_t pp = ad_pack(ad_exp2(sc - mn), 0.0f);  // rounded as the other probabilities are
+        const float pr = __uint_as_float(pp << 16);
+        m[c] = mn;
+        l[c] = l[c] * corr + (gl == 0 ? pr : 0.0f);          // the sum over lane groups below counts it once
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+          o[d][c] = o[d][c] * corr + pr * __uint_as_float((uint32_t)vf[2 * d] << 16);
+          o[d][c + 2] = o[d][c + 2] * corr + pr * __uint_as_float((uint32_t)vf[2 * d + 1] << 16);
+        }
+      }
+    }
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
@@ -493,6 +592,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       g = ng;
 #pragma unroll
       for (int j = 0; j < 4; ++j) { qb[j][0] = qn[j][0]; qb[j][1] = qn[j][1]; }
+      if (rotate && i + 1 < i1) { angles(t, cs, sn); rotate_frag(qb, cs, sn); }
       if (nsome) {
         nsome = next_run(t, g, nt, ng);
         load_q(nt, ng, nsome, qn);
@@ -582,11 +682,16 @@ extern "C" int exl3_attn_decode_status() {
 }
 
 // Same arguments and the same scratch layout as exl3_attn_tokens; n_pool_rows = pages * kv_heads * 64.
-extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, const void* k_pool,
-                                const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
-                                const int* tok_pos, const int* tok_seq, int T, int nh, int nkv, int hd, int page,
-                                int window, float scale, int split_keys, int max_splits, float* scratch,
-                                size_t scratch_bytes, cudaStream_t stream) {
+// With write_new, q is the fused q|k|v output of the projection and every token is its sequence's only new one:
+// the kernel takes the token's key and value from there, adds them to its softmax and writes them to the cache
+// (which holds the positions before it).  With rot = 64 it also applies the half-split rotary encoding
+// (angle pos * pos_scale * inv_freq[d], 32 frequencies) to the queries and the new key; rot = 0: none.
+extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
+                                int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
+                                const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
+                                float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                const float* inv_freq, int rot, float pos_scale, int write_new,
+                                cudaStream_t stream) {
   if (T == 0) return 0;
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
       !exl3_attn_decode_supported(DT_BF16, T, nh, nkv, hd, page, split_keys, max_splits)) {
@@ -594,6 +699,10 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
               "head and %d chunks of whole pages; got T=%d heads=%d kv_heads=%d head_dim=%d page=%d window=%d "
               "split_keys=%d max_splits=%d", AD_MAX_TOKENS, AD_MAX_GROUP, AD_MAX_SPLITS, T, nh, nkv, hd, page,
               window, split_keys, max_splits);
+    return ERR_UNSUPPORTED;
+  }
+  if ((rot != 0 && rot != AD_HD) || (rot != 0 && inv_freq == nullptr)) {
+    set_error("attn_decode: the rotary encoding is applied to all %d features of a head or to none, got %d", AD_HD, rot);
     return ERR_UNSUPPORTED;
   }
   if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out) || q_row_stride % 8 != 0) {
@@ -625,6 +734,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   launch_pdl(attn_decode_kernel, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,
              bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,
-             max_splits, records, counters);
+             max_splits, records, counters, inv_freq, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,
+             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
   return launch_status("attn_decode");
 }

@@ -313,20 +313,30 @@ def attn_decode_status() -> int:
 def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, T: int, heads: int,
                 kv_heads: int, head_dim: int, page: int, window: int, scale: float, split_keys: int,
-                max_splits: int, scratch: Optional[torch.Tensor]) -> torch.Tensor:
+                max_splits: int, scratch: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor] = None,
+                rot: int = 0, pos_scale: float = 1.0, write_new: bool = False) -> torch.Tensor:
     """Attention of T query tokens over the paged cache on the tensor cores (see attention_decode.cu);
-    arguments and scratch as ``attn_tokens``."""
+    arguments and scratch as ``attn_tokens``.  With ``write_new``, ``q`` is the fused q|k|v output of the
+    projection, every token is its sequence's only new one and the cache holds the positions before it: the
+    kernel adds the token's own key and value to its softmax and writes them to the cache.  With ``rot`` equal to
+    ``head_dim`` it applies the half-split rotary encoding (``inv_freq``: head_dim / 2 float32 frequencies) to
+    the queries and the new key."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
     _contig(v_pool, "v_pool")
+    if rot:
+        if inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2:
+            raise KernelLibraryError("attn_decode: inv_freq must hold rot / 2 float32 frequencies")
+        _contig(inv_freq, "inv_freq")
     pool_rows = k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2]
     nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
     _check(library().exl3_attn_decode(
         _ptr(q), _c_int64(q_row_stride), _ptr(out), _ptr(k_pool), _ptr(v_pool), _c_int64(pool_rows),
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T), _c_int(heads),
         _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
-        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _stream()), "attn_decode")
+        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _ptr(inv_freq if rot else None), _c_int(rot),
+        _c_float(pos_scale), _c_int(1 if write_new else 0), _stream()), "attn_decode")
     return out
 
 

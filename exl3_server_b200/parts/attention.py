@@ -77,11 +77,37 @@ class Attention:
         if kv is None:
             raise RuntimeError("attention needs a cache view")
         qkv = self.qkv(x)
-        self.position.rotate_and_store(qkv, batch, kv, s.heads, s.kv_heads, s.head_dim)
         T = qkv.shape[0]
         out = torch.empty((T, s.heads * s.head_dim), dtype=qkv.dtype, device=qkv.device)
-        self.attend(qkv, out, batch, kv)
+        if not self._decode_fused(qkv, out, batch, kv):
+            self.position.rotate_and_store(qkv, batch, kv, s.heads, s.kv_heads, s.head_dim)
+            self.attend(qkv, out, batch, kv)
         return self.o(out)
+
+    def _decode_fused(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
+        """One token per sequence, bfloat16, heads of 64: the decode kernel rotates the queries and the new key
+        itself, takes the token's own key and value from ``qkv`` and writes them to the cache, so the position
+        step is no kernel of its own.  False when the step, the sizes or the position part do not allow it."""
+        s = self.spec
+        fused = getattr(self.position, "fused_rotation", None)
+        if batch.max_new != 1 or qkv.dtype != torch.bfloat16 or fused is None:
+            return False
+        rotation = fused(s.head_dim)
+        if rotation is None:
+            return False
+        inv_freq, rot, pos_scale = rotation
+        T = qkv.shape[0]
+        split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+        n = self._chunks(batch.max_kv_len, split)
+        if not K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
+            return False
+        scratch = None
+        if n > 1:
+            scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
+        K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
+                      s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
+                      inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns)
+        return True
 
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> None:
         s = self.spec

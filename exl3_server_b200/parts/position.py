@@ -10,6 +10,9 @@ kept as float32; angles and sin/cos are float32 in the kernel.  A scaled or
 extended variant only needs another table.
 
 ``none``: no rotation; keys and values are still written to the cache.
+
+A position part has ``rotate_and_store(qkv, batch, kv, heads, kv_heads, head_dim)``; it may also offer
+``fused_rotation(head_dim)`` (see below), which lets the decode attention kernel do both jobs itself.
 """
 from __future__ import annotations
 
@@ -39,6 +42,16 @@ class RotaryPosition:
         K.rope_kv_write(qkv, self.inv_freq, self.spec.dims, float(self.spec.scale), batch.tok_pos,
                         batch.tok_seq, kv.block_table, kv.k if write else None, kv.v if write else None,
                         heads, kv_heads, head_dim, kv.page_size, write)
+
+
+    def fused_rotation(self, head_dim: int):
+        """``(inv_freq, dims, scale)`` when an attention kernel can apply this encoding itself (all of a head's
+        features rotated, or none), else None: then ``rotate_and_store`` runs as a step of its own."""
+        if self.spec.dims == 0:
+            return None, 0, 1.0
+        if self.spec.dims == head_dim:
+            return self.inv_freq, self.spec.dims, float(self.spec.scale)
+        return None
 
 
 class NoPosition(RotaryPosition):

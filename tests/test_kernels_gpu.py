@@ -373,6 +373,59 @@ def test_attn_decode_finds_one_far_key_among_many():
     assert float((out.cpu().float() - case.v[0][far].reshape(1, -1).float()).abs().max()) > 0.1
 
 
+@pytest.mark.parametrize("nh,nkv", [(3, 3), (8, 1), (16, 2)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("rot", [64, 0])
+@pytest.mark.parametrize("split", [64, 256, 2048])
+def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, window, rot, split):
+    """The kernel takes each token's own key and value from the projection's output: the cache holds junk at
+    the token's place before the call and the rotated key and the value after it."""
+    hd = 64
+    lens = [300, 64, 1, 700, 65, 256, 257, 128, 513, 2]         # last positions at both sides of page and chunk edges
+    B = len(lens)
+    case = PagedCase(lens=lens, new=[1] * B, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split + rot)
+    g = torch.Generator().manual_seed(99)
+    q_raw = torch.randn(B, nh, hd, generator=g).to(torch.bfloat16)
+    k_raw = torch.randn(B, nkv, hd, generator=g).to(torch.bfloat16)
+    v_raw = torch.randn(B, nkv, hd, generator=g).to(torch.bfloat16)
+    theta, pos_scale = 10000.0, 1.0
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64),
+                         -2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd).to(torch.float32)
+
+    def rotated(x, pos):                                        # [heads, hd] at one position
+        if not rot:
+            return x
+        a = (torch.tensor(float(pos), dtype=torch.float32) * pos_scale * inv_freq).double()
+        x0, x1 = x[:, :hd // 2].double(), x[:, hd // 2:].double()
+        return torch.cat([x0 * a.cos() - x1 * a.sin(), x1 * a.cos() + x0 * a.sin()], dim=1).to(torch.bfloat16)
+
+    for b in range(B):
+        pos = lens[b] - 1
+        case.q[b] = rotated(q_raw[b], pos)
+        case.k[b][pos] = rotated(k_raw[b], pos)
+        case.v[b][pos] = v_raw[b]
+        pg = int(case.table[b, pos // 64])
+        case.k_pool[pg, :, pos % 64] = 100.0                   # not written yet: must not be read as a key
+        case.v_pool[pg, :, pos % 64] = -100.0
+    qkv = torch.cat([q_raw.reshape(B, -1), k_raw.reshape(B, -1), v_raw.reshape(B, -1)], dim=1).to(DEV).contiguous()
+    out = torch.empty((B, nh * hd), dtype=torch.bfloat16, device=DEV)
+    scale = 0.7 / math.sqrt(hd)
+    n = (max(lens) + split - 1) // split
+    if window > 0:
+        n = min(n, (window + split - 2) // split + 1)
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(B, nh, hd, n) // 4, device=DEV)
+    K().attn_decode(qkv, qkv.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, B,
+                    nh, nkv, hd, 64, window, scale, split, n, scratch, inv_freq=inv_freq.to(DEV), rot=rot,
+                    pos_scale=pos_scale, write_new=True)
+    close(out, case.reference(window, scale), 1e-2, "attn_decode, own key and value")
+    for b in range(B):
+        pos = lens[b] - 1
+        pg = int(case.table[b, pos // 64])
+        close(case.k_pool[pg, :, pos % 64], case.k[b][pos], 1e-2, "key written to the cache")
+        assert torch.equal(case.v_pool[pg, :, pos % 64].cpu(), v_raw[b])
+    assert K().attn_decode_status() == 0
+
+
 def test_attn_decode_is_refused_for_other_shapes():
     assert K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 16)
     assert not K().attn_decode_supported(torch.float32, 8, 4, 4, 64, 64, 256, 16)
