@@ -148,8 +148,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncwarp();
-  pdl_wait();
   pdl_trigger();
+  // Positions, sequences and page numbers are the step's inputs: no kernel of the step writes them.  When the
+  // token's own key and value come from the projection (write_new), the cache pages this kernel reads hold
+  // earlier steps' tokens only, so everything up to the first read of the queries, the first pages' copies
+  // included, may run while the projection before this kernel is still at work.  Otherwise the position step
+  // before this kernel has just written the newest page.
+  if (!write_new) pdl_wait();
 
   // ---- every token's chunks, counted and summed ------------------------------------------------
   // A token at position pos reads keys lo .. pos; its chunks are the aligned pieces of split_keys
@@ -389,6 +394,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   int nt = 0, ng = 0;
   bool nsome = false;
   float cs[8], sn[8];
+  if (write_new) pdl_wait();                             // from here on the projection's output is read
   if (i0 < i1) {
     load_q(t, g, true, qb);
     nsome = next_run(t, g, nt, ng);
