@@ -89,8 +89,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, _
   __nv_bfloat16* sK = sQ + BQ * HD;                                          // [STAGES][64][HD]
   __nv_bfloat16* sV = sK + STAGES * PF_BK * HD;                              // [STAGES][64][HD]
 
-  // tiles are listed by rising position; the ones with most keys to visit start first
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // the caller lists the tiles with the most keys to visit first
+  const int head = blockIdx.x, tile = blockIdx.y;   // blocks start in this order: all heads of tile 0, then tile 1, ...
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = row_start[b + 1] - row_start[b];
   const int pos0 = row_pos0[b];
@@ -293,7 +293,7 @@ static int launch_prefill(const void* q, int64_t q_row_stride, void* out, const 
     if (e != cudaSuccess) { set_error("attn_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return (int)e; }
     configured = true;
   }
-  dim3 grid(n_tiles, nh);
+  dim3 grid(nh, n_tiles);
   attn_prefill_kernel<HD, MT, STAGES, WARPS><<<grid, WARPS * 32, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out),
       static_cast<const __nv_bfloat16*>(k_pool), static_cast<const __nv_bfloat16*>(v_pool), block_table,
@@ -325,7 +325,7 @@ extern "C" int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out,
               dtype, hd, page);
     return ERR_UNSUPPORTED;
   }
-  if (n_tiles < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || nh > 65535 || window < 0) {
+  if (n_tiles < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0) {
     set_error("attn_prefill: bad sizes tiles=%d heads=%d kv_heads=%d window=%d", n_tiles, nh, nkv, window);
     return ERR_BAD_ARGUMENT;
   }

@@ -156,8 +156,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // tiles are listed by rising position; the ones with most keys to visit start first
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // the caller lists the tiles with the most keys to visit first
+  const int head = blockIdx.x, tile = blockIdx.y;   // blocks start in this order: all heads of tile 0, then tile 1, ...
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = row_start[b + 1] - row_start[b];
   const int pos0 = row_pos0[b];
@@ -440,7 +440,7 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
     set_error("attn_prefill_tc: needs bfloat16, head_dim 64 and pages of 64, got head_dim %d page %d", hd, page);
     return ERR_UNSUPPORTED;
   }
-  if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || nh > 65535 || window < 0 || q_row_stride % 8 != 0) {
+  if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || q_row_stride % 8 != 0) {
     set_error("attn_prefill_tc: bad sizes tiles=%d T=%d heads=%d kv_heads=%d window=%d", n_tiles, T, nh, nkv, window);
     return ERR_BAD_ARGUMENT;
   }
@@ -461,7 +461,7 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   if (rc) return rc;
   rc = fa_make_map(&map_v, v_pool, n_pool_rows, hd, hd, FA_BK);
   if (rc) return rc;
-  dim3 grid(n_tiles, nh);
+  dim3 grid(nh, n_tiles);
   attn_prefill_tc_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(
       map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
       tile_q0, nh, nkv, window, scale * 1.4426950408889634f);

@@ -275,6 +275,10 @@ rope_kv_write_vec_kernel(T* qkv, const float* __restrict__ inv_freq, int rot, fl
     cache_base = ((int64_t)pg * nkv * page + (pos % page)) * hd;
   }
   const float p = (float)pos * pos_scale;
+  // the token's sines and cosines, once for all its heads
+  extern __shared__ float rope_cs[];                  // [half] cosines, then [half] sines
+  for (int d = threadIdx.x; d < half; d += blockDim.x) sincosf(p * inv_freq[d], &rope_cs[half + d], &rope_cs[d]);
+  __syncthreads();
   const int cpr = half / VEC;                         // rotated pieces per head (first half)
   const int n_rot = (nh + nkv) * cpr;
   const int tail = (hd - rot) / VEC;                  // pass-through pieces per k head
@@ -289,8 +293,7 @@ rope_kv_write_vec_kernel(T* qkv, const float* __restrict__ inv_freq, int rot, fl
       load_vec_cg(src + half, x1);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        float s, c;
-        sincosf(p * inv_freq[d + e], &s, &c);
+        const float c = rope_cs[d + e], s = rope_cs[half + d + e];
         r0[e] = x0[e] * c - x1[e] * s;
         r1[e] = x1[e] * c + x0[e] * s;
       }
@@ -391,11 +394,11 @@ extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, i
   const int vec = dtype == DT_F32 ? 4 : 8;
   const bool fast = rot % (2 * vec) == 0 && hd % vec == 0 && aligned16(qkv) && aligned16(k_pool) && aligned16(v_pool);
   if (fast && dtype == DT_F32) {
-    launch_pdl(rope_kv_write_vec_kernel<float>, dim3(T), dim3(256), 0, stream, static_cast<float*>(qkv), inv_freq,
+    launch_pdl(rope_kv_write_vec_kernel<float>, dim3(T), dim3(256), (size_t)rot * sizeof(float), stream, static_cast<float*>(qkv), inv_freq,
                rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride, static_cast<float*>(k_pool),
                static_cast<float*>(v_pool), nh, nkv, hd, page, write_kv);
   } else if (fast) {
-    launch_pdl(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream,
+    launch_pdl(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t)rot * sizeof(float), stream,
                static_cast<__nv_bfloat16*>(qkv), inv_freq, rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride,
                static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), nh, nkv, hd, page, write_kv);
   } else {

@@ -81,8 +81,12 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
               np.asarray(wanted, np.int64)]
     tile_counts = []
     for size in QUERY_TILES:
-        tile_rows = [i for i in range(B) for _ in range(0, counts[i], size)]
-        tile_first = [a for i in range(B) for a in range(0, counts[i], size)]
+        # the tiles with the most keys to visit come first: the attention kernels start them first, so
+        # that the long ones do not run alone at the end
+        order = sorted(((starts[i] + min(a + size, counts[i]), i, a) for i in range(B) for a in range(0, counts[i], size)),
+                       key=lambda x: -x[0])
+        tile_rows = [i for _, i, _ in order]
+        tile_first = [a for _, _, a in order]
         pieces += [np.asarray(tile_rows, np.int64), np.asarray(tile_first, np.int64)]
         tile_counts.append(len(tile_rows))
     n_fixed = len(pieces)

@@ -12,6 +12,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Union
 
+import numpy as np
 import torch
 
 from ..cache.kv import SequenceCache
@@ -148,12 +149,14 @@ class Engine:
                 start = self.cache.length(e.slot)
             except CacheError as err:
                 raise StepError(str(err)) from None
-            t = [int(x) for x in e.tokens]
-            if not t:
+            t = np.asarray(e.tokens)
+            if t.ndim != 1 or t.dtype.kind not in "iu":
+                t = np.asarray([int(x) for x in e.tokens], dtype=np.int64)
+            if t.size == 0:
                 raise StepError(f"slot {e.slot}: a step entry needs at least one token")
-            bad = [x for x in t if not 0 <= x < vocab]
-            if bad:
-                raise StepError(f"slot {e.slot}: token id {bad[0]} is outside the vocabulary of {vocab}")
+            bad = t[(t < 0) | (t >= vocab)]
+            if bad.size:
+                raise StepError(f"slot {e.slot}: token id {int(bad[0])} is outside the vocabulary of {vocab}")
             if limit and start + len(t) > limit:
                 raise StepError(f"slot {e.slot}: {start + len(t)} positions exceed max_position_embeddings {limit}")
             if e.want is None:

@@ -226,9 +226,12 @@ class PagedCase:
         self.row_pos0 = torch.tensor([lens[b] - new[b] for b in range(B)], dtype=torch.int32, device=DEV)
 
     def tiles(self, size):
+        # any order is right; the engine lists the tiles with the most keys first
         B = len(self.new)
-        seq = torch.tensor([b for b in range(B) for _ in range(0, self.new[b], size)], dtype=torch.int32, device=DEV)
-        q0 = torch.tensor([a for b in range(B) for a in range(0, self.new[b], size)], dtype=torch.int32, device=DEV)
+        order = sorted(((self.lens[b] - self.new[b] + a, b, a) for b in range(B) for a in range(0, self.new[b], size)),
+                       reverse=True)
+        seq = torch.tensor([b for _, b, _ in order], dtype=torch.int32, device=DEV)
+        q0 = torch.tensor([a for _, _, a in order], dtype=torch.int32, device=DEV)
         return seq, q0
 
     def reference(self, window, scale):
