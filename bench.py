@@ -146,7 +146,7 @@ def main() -> int:
     model = Model(plan, tensors, torch.bfloat16, dev)
     del tensors
     B, C, Kst, W = args.batch, args.context, args.steps, args.warmup
-    big = 64 if not args.no_points else B
+    big = 64 if (not args.no_points and args.only == "all") else B
     cache_tokens = (max(big, B) + 1) * ((C + 63) // 64 * 64 + 64)
     engine = E.Engine(model, max_tokens=cache_tokens)
     print(f"[bench] model and cache ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)

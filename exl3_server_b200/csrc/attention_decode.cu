@@ -38,6 +38,16 @@
 // Scores, running maximum, running sum and the output accumulator are float32;
 // the probabilities are rounded to bfloat16 for the second product.
 //
+// Two jobs of the step before attention can be done here (write_new, rotate):
+// the half-split rotary encoding of the queries and of the token's own key
+// (src/model.cpp:566-567), and that key's and value's way into the cache
+// (src/model.cpp:569-574).  The warp that holds a token's last chunk takes its
+// key and value from the projection's output, rotates the key, adds the pair to
+// the softmax as one more key and writes it to the cache; the pages it reads
+// then hold earlier steps' tokens only, so the page stream may start before
+// the projection has finished (programmatic dependent launch).  This is for
+// steps in which every sequence brings one token.
+//
 // Cache layout: pool[page][kv_head][slot][head_dim], page = block_table[row][pos / page_size].
 #include "api.h"
 #include "common.cuh"
