@@ -19,6 +19,7 @@ from ..cache.kv import SequenceCache
 from ..cache.pages import CacheError
 from ..config.fields import ConfigError, read_config_json
 from ..config.registry import resolve_architecture
+from ..ops import kernels as K
 from ..ops.lib import KernelLibraryError, library
 from ..weights.loader import load_tensors
 from .batch import StepBatch, Workspace, pack_step
@@ -131,6 +132,11 @@ class Engine:
         return logits[torch.tensor(rows, device=logits.device)]
 
     # -- the step ------------------------------------------------------------
+    def check_kernels(self) -> None:
+        """Raises if a kernel with bounded waits gave up on one since the last call (see
+        ``ops.kernels.check_status``).  Waits for the work launched so far."""
+        K.check_status()
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the given tokens, as one batch, from the cache.  Returns the
         float32 logits ``[wanted, vocab]`` in the order of the entries and of

@@ -92,6 +92,9 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
     todo = [len(p) if opt.max_tokens > 0 else 0 for p in prompts]
     for batch in plan_batches(todo, opt.max_tokens, opt.max_batch, engine.cache_tokens):
         _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
+        check = getattr(engine, "check_kernels", None)
+        if check is not None:
+            check()                                       # the batch's tokens are on the host: no extra wait
     return results
 
 

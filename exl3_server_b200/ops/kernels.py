@@ -340,6 +340,17 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     return out
 
 
+def check_status() -> None:
+    """Raises if a kernel with bounded waits (the tcgen05 GEMM and attention, the TMA decode attention) gave up
+    on one since the last call: its results are then not to be trusted.  Reads three flags from the device, so
+    it waits for the work launched so far; call it where the host waits anyway."""
+    gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("attn_prefill_tc", attn_prefill_tc_status),
+                                     ("attn_decode", attn_decode_status)) if fn()]
+    if gave_up:
+        raise KernelLibraryError("a bounded wait ran out in " + ", ".join(gave_up) +
+                                 ": a copy or a tensor-core product did not complete in time")
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     R, V = logits.shape
     if logits.dtype != torch.float32:

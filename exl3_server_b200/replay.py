@@ -65,6 +65,7 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     print("trace_run: loading the model and the kernels ...", file=sys.stderr, flush=True)
     import torch
+
     from .engine import Engine
 
     engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device)
@@ -85,6 +86,7 @@ def main(argv=None) -> int:
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
+        engine.check_kernels()
         print(f"done {step}", flush=True)
     return 0
 

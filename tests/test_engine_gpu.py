@@ -276,3 +276,13 @@ def test_command_line(model_folders):
     bad = subprocess.run([sys.executable, "-m", "exl3_server_b200", "--model", folder, "--serve"], capture_output=True,
                          text=True, cwd=ROOT, timeout=120)
     assert bad.returncode == 2
+
+
+def test_kernels_report_no_bounded_wait_that_ran_out(model_folders):
+    """After real work through the tensor-core kernels (heads of 64) no kernel has given up on a wait."""
+    from exl3_server_b200 import Engine, GenerateOptions
+    eng = Engine.from_folder(model_folders["D"], dtype="bfloat16", max_tokens=1024)
+    toks = random_requests(TINY["D"]["cfg"].vocab_size, [300, 70], seed=2)
+    res = eng.generate(list(toks.values()), GenerateOptions(max_tokens=8, ignore_eos=True))
+    assert all(r.completion_tokens == 8 for r in res)
+    eng.check_kernels()
