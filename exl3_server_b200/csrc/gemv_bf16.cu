@@ -49,13 +49,35 @@ template <int N> __device__ inline void cp_async_wait_group() { asm volatile("cp
 // no registers, and keeps (GEMV_STAGES - 1) * 32 bytes of weights per thread in
 // flight.  Its pieces of the activations travel in the same ring.
 //
+// The norm between two projections, without a kernel of its own (GemvNorm):
+//   h += y * rho;   r = h * rsqrt(mean(h^2) + eps) * norm_w;   y2 = r . w2^T
+// is done in pieces.  The projection that produces y (EPI 2) keeps no y: each of its blocks adds its 16 features
+// to the float32 residual h, writes them times the norm weight as bfloat16 (x_raw) and writes the sums of their
+// squares per batch row (ss_part[block][16]).  The projection that consumes r (SCALE) reads x_raw as its input,
+// adds the blocks' sums in an order that depends on its thread count only, and multiplies its results by
+// rsqrt(sum / width + eps) before bias and gating: a factor per batch row commutes with the product.  Statistics and the residual stay float32.
+struct GemvNorm {
+  // EPI 2, the producing side
+  float* h;                      // [M, N] residual, updated in place
+  const void* norm_w;            // [N] weight of the norm that follows
+  __nv_bfloat16* x_raw;          // [M, N] out: h * norm_w
+  float* ss_out;                 // [blocks, 16] out: sums of squares of the block's features, per batch row
+  float rho;
+  int norm_w_f32;
+  // SCALE, the consuming side
+  const float* ss_in;            // [ss_blocks, 16] from the producer
+  int ss_blocks;
+  float eps, width;
+};
+
 // EPI 0: y[m, n] = acc (+ bias).  EPI 1 (gated feed-forward): the 16 rows of a
 // block are 8 gate rows followed by the 8 up rows of the same features;
 // y[m, block * 8 + r] = silu(gate_r) * up_r, so N / 2 features come out.
-template <int NT, typename TO, int EPI, int GEMV_STAGES>
+template <int NT, typename TO, int EPI, int GEMV_STAGES, bool SCALE = false>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
-                 const __nv_bfloat16* __restrict__ bias, TO* __restrict__ y, int M, int N, int K) {
+                 const __nv_bfloat16* __restrict__ bias, TO* __restrict__ y, int M, int N, int K, GemvNorm nrm) {
+  __shared__ float s_ss[GEMV_MAX_WARPS * 32];           // SCALE: every thread's share of its batch row's sum of squares
   extern __shared__ uint4 ring[];                     // [GEMV_STAGES][2 + NT][blockDim.x]: weights a, b, then x
   pdl_trigger();
   const int tid = threadIdx.x, nthreads = blockDim.x;
@@ -108,6 +130,30 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     if (i < n_my) issue_x(i);
     cp_async_commit_group();
   }
+  // SCALE: the producer's sums of squares [ss_blocks][16].  Thread t takes the values t, t + threads, ...: all of
+  // batch row t & 15 (the thread count is a multiple of 16).  The loads are asked for here, together with the
+  // activations, and added up after the loop; the 16-lane groups' sums meet in shared memory.
+  // EPI 2: the epilogue's own operands (a residual value and a norm weight per thread, when the block has at
+  // least 16 * 8 * NT threads) are asked for here too
+  float h_pre = 0.0f, wn_pre = 0.0f;
+  if constexpr (EPI == 2) {
+    const int m = tid >> 4, n = r0 + (tid & 15);
+    if (tid < 16 * 8 * NT && m < M && n < N) {
+      h_pre = __ldcg(nrm.h + (int64_t)m * N + n);
+      wn_pre = nrm.norm_w_f32 ? __ldg(static_cast<const float*>(nrm.norm_w) + n)
+                              : __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(nrm.norm_w) + n));
+    }
+  }
+  constexpr int SS_AHEAD = 8;
+  float ss_v[SS_AHEAD];
+  if constexpr (SCALE) {
+    const int n_ss = nrm.ss_blocks * 16;
+#pragma unroll
+    for (int j = 0; j < SS_AHEAD; ++j) {
+      const int idx = tid + j * nthreads;
+      ss_v[j] = idx < n_ss ? __ldcg(nrm.ss_in + idx) : 0.0f;
+    }
+  }
   // Groups complete in order: W0..W(S-2), X0..X(S-2), then one group per iteration.  Block i
   // needs the group at index S-1+i; at iteration i, 2(S-1)+i groups exist, so S-2 may pend.
   for (int i = 0; i < n_my; ++i) {
@@ -132,7 +178,20 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     part[warp][gid + 8][t * 8 + tig * 2] = c[t][2];
     part[warp][gid + 8][t * 8 + tig * 2 + 1] = c[t][3];
   }
+  if constexpr (SCALE) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < SS_AHEAD; ++j) ss += ss_v[j];
+    for (int idx = tid + SS_AHEAD * nthreads; idx < nrm.ss_blocks * 16; idx += nthreads) ss += __ldcg(nrm.ss_in + idx);
+    s_ss[tid] = ss;
+  }
   __syncthreads();
+  // the factor of batch row m: the shares of the threads t with t & 15 == m, added in thread order
+  auto row_factor = [&](int m) {
+    float ss = 0.0f;
+    for (int t = m; t < nthreads; t += 16) ss += s_ss[t];
+    return 1.0f / sqrtf(ss / nrm.width + nrm.eps);
+  };
   if (EPI == 0) {
     for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += blockDim.x) {
       const int m = idx >> 4, r = idx & 15;           // consecutive threads: consecutive features
@@ -140,10 +199,11 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       if (m >= M || n >= N) continue;
       float s = 0.0f;
       for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
+      if (SCALE) s *= row_factor(m);
       if (bias) s += __bfloat162float(bias[n]);
       Elem<TO>::store(y + (int64_t)m * N + n, s);
     }
-  } else {
+  } else if (EPI == 1) {
     const int n_out = N >> 1;
     for (int idx = threadIdx.x; idx < 8 * 8 * NT; idx += blockDim.x) {
       const int m = idx >> 3, r = idx & 7;
@@ -151,9 +211,40 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       if (m >= M || f >= n_out) continue;
       float g = 0.0f, u = 0.0f;
       for (int wi = 0; wi < nwarps; ++wi) { g += part[wi][r][m]; u += part[wi][r + 8][m]; }
+      if (SCALE) { const float f = row_factor(m); g *= f; u *= f; }
       if (bias) { g += __bfloat162float(bias[r0 + r]); u += __bfloat162float(bias[r0 + r + 8]); }
       Elem<TO>::store(y + (int64_t)m * n_out + f, g / (1.0f + expf(-g)) * u);
     }
+  } else {
+    // EPI 2: into the residual.  Whole warps take part (the limits are multiples of 32); the 16 lanes of a
+    // batch row add their squares.
+    for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += blockDim.x) {
+      const int m = idx >> 4, r = idx & 15;
+      const int n = r0 + r;
+      float sq = 0.0f;
+      if (m < M && n < N) {
+        float s = 0.0f;
+        for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
+        if (SCALE) s *= row_factor(m);
+        if (bias) s += __bfloat162float(bias[n]);
+        // the output is rounded to bfloat16 as it would be on its way through memory
+        const bool first = idx == (int)threadIdx.x;     // the first pass uses what was asked for before the loop
+        const float h_old = first ? h_pre : __ldcg(nrm.h + (int64_t)m * N + n);
+        const float hv = h_old + __bfloat162float(__float2bfloat16_rn(s)) * nrm.rho;
+        nrm.h[(int64_t)m * N + n] = hv;
+        const float wn = first ? wn_pre
+                       : nrm.norm_w_f32 ? static_cast<const float*>(nrm.norm_w)[n]
+                                        : __bfloat162float(static_cast<const __nv_bfloat16*>(nrm.norm_w)[n]);
+        nrm.x_raw[(int64_t)m * N + n] = __float2bfloat16_rn(hv * wn);
+        sq = hv * hv;
+      }
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      if (r == 0) nrm.ss_out[(int64_t)blockIdx.x * 16 + m] = sq;     // zero for rows beyond M
+    }
+    if (NT == 1 && threadIdx.x >= 8 && threadIdx.x < 16) nrm.ss_out[(int64_t)blockIdx.x * 16 + threadIdx.x] = 0.0f;
   }
 }
 
@@ -161,20 +252,37 @@ static size_t gemv_smem(int nt, int stages, int warps) {
   return (size_t)stages * (2 + nt) * warps * 32 * sizeof(uint4) + (size_t)warps * 16 * (8 * nt + 1) * sizeof(float);
 }
 
-template <int NT, typename TO, int EPI, int STAGES>
+template <int NT, typename TO, int EPI, int STAGES, bool SCALE = false>
 static int launch(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int warps,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const GemvNorm& nrm = GemvNorm()) {
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(gemv_bf16_kernel<NT, TO, EPI, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(gemv_bf16_kernel<NT, TO, EPI, STAGES, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)gemv_smem(NT, STAGES, GEMV_MAX_WARPS));
     configured = true;
   }
-  launch_pdl(gemv_bf16_kernel<NT, TO, EPI, STAGES>, dim3(ceil_div(N, 16)), dim3(warps * 32),
+  launch_pdl(gemv_bf16_kernel<NT, TO, EPI, STAGES, SCALE>, dim3(ceil_div(N, 16)), dim3(warps * 32),
              gemv_smem(NT, STAGES, warps), stream,
              static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-             static_cast<const __nv_bfloat16*>(bias), static_cast<TO*>(y), M, N, K);
+             static_cast<const __nv_bfloat16*>(bias), static_cast<TO*>(y), M, N, K, nrm);
   return launch_status("gemv_bf16");
+}
+
+// Few blocks: many warps per block, so that the ring covers most of K at
+// once.  Many blocks: fewer warps each, several blocks per SM.  The choice
+// depends on N and K only, never on M, so a row's result does not depend on
+// its batch.  (Measured: block shapes that make all blocks resident at once,
+// or deeper rings, change nothing; a dependent kernel costs about 2 us however
+// small, and mid-sized matrices stay near 3.5-4 TB/s for that reason.)
+static int gemv_sm_count();
+static int gemv_shape(int M, int N, int K, int& warps, int& stages) {
+  const int nt = M <= 8 ? 1 : 2;
+  const int nblocks = (K + 31) / 32;
+  const int ctas = ceil_div(N, 16);
+  warps = ctas >= 4 * gemv_sm_count() ? 4 : (ctas >= 2 * gemv_sm_count() ? 8 : 16);
+  while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
+  stages = (nt == 2 && warps == 16) ? 4 : 6;             // 16 warps x 6 stages x 4 slots would not fit
+  return nt;
 }
 
 static int gemv_sm_count() {
@@ -206,18 +314,8 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
   if (!aligned16(x) || !aligned16(w)) { set_error("gemv_bf16: x and w must be 16-byte aligned"); return ERR_ALIGNMENT; }
   const bool f32 = out_dtype == DT_F32;
   if (!f32 && out_dtype != DT_BF16) { set_error("gemv_bf16: unsupported output type %d", out_dtype); return ERR_UNSUPPORTED; }
-  // Few blocks: many warps per block, so that the ring covers most of K at
-  // once.  Many blocks: fewer warps each, several blocks per SM.  The choice
-  // depends on N and K only, never on M, so a row's result does not depend on
-  // its batch.  (Measured: block shapes that make all blocks resident at once,
-  // or deeper rings, change nothing; a dependent kernel costs about 2 us however
-  // small, and mid-sized matrices stay near 3.5-4 TB/s for that reason.)
-  const int nt = M <= 8 ? 1 : 2;
-  const int nblocks = (K + 31) / 32;
-  const int ctas = ceil_div(N, 16);
-  int warps = ctas >= 4 * gemv_sm_count() ? 4 : (ctas >= 2 * gemv_sm_count() ? 8 : 16);
-  while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
-  const int stages = (nt == 2 && warps == 16) ? 4 : 6;      // 16 warps x 6 stages x 4 slots would not fit
+  int warps, stages;
+  const int nt = gemv_shape(M, N, K, warps, stages);
 #define EXL3_GEMV(NT, EPI, ST)                                                                  \
   return f32 ? launch<NT, float, EPI, ST>(x, w, bias, y, M, N, K, warps, stream)                \
              : launch<NT, __nv_bfloat16, EPI, ST>(x, w, bias, y, M, N, K, warps, stream)
@@ -226,4 +324,60 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
   if (epilogue) { EXL3_GEMV_ST(2, 1) } else { EXL3_GEMV_ST(2, 0) }
 #undef EXL3_GEMV_ST
 #undef EXL3_GEMV
+}
+
+// The two sides of a norm that is no kernel of its own (see GemvNorm above).  Both take bfloat16 operands and
+// at most 16 batch rows, as exl3_gemv_bf16.
+//
+// ss_in / ss_blocks / eps / width: when ss_in is not null, x is the x_raw of a producing call and the results are
+// multiplied by rsqrt(sum of the blocks' sums / width + eps) per batch row before bias and gating.
+// epilogue 0 or 1: y as in exl3_gemv_bf16 (out_dtype).  epilogue 2: no y; h[M, N] += result * rho,
+// x_raw[M, N] = h * norm_w, ss_out[ceil(N / 16), 16] = the blocks' sums of squares.
+extern "C" int exl3_gemv_bf16_normed(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
+                                     int N, int K, int epilogue, const float* ss_in, int ss_blocks, float eps,
+                                     float width, float* h, float rho, const void* norm_w, int norm_w_dtype,
+                                     void* x_raw, float* ss_out, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < 0 || M > 16 || N < 0 || K < 8 || K % 8 != 0 || epilogue < 0 || epilogue > 2 ||
+      (epilogue == 1 && N % 16 != 0) || (ss_in != nullptr && (ss_blocks < 1 || !(width > 0.0f)))) {
+    set_error("gemv_bf16_normed: bad arguments M=%d N=%d K=%d epilogue=%d ss_blocks=%d", M, N, K, epilogue, ss_blocks);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (!aligned16(x) || !aligned16(w)) { set_error("gemv_bf16_normed: x and w must be 16-byte aligned"); return ERR_ALIGNMENT; }
+  GemvNorm nrm = {};
+  if (epilogue == 2) {
+    if (!h || !norm_w || !x_raw || !ss_out || (norm_w_dtype != DT_F32 && norm_w_dtype != DT_BF16)) {
+      set_error("gemv_bf16_normed: the residual epilogue needs h, a float32 or bfloat16 norm weight, x_raw and ss_out");
+      return ERR_BAD_ARGUMENT;
+    }
+    nrm.h = h;
+    nrm.norm_w = norm_w;
+    nrm.x_raw = static_cast<__nv_bfloat16*>(x_raw);
+    nrm.ss_out = ss_out;
+    nrm.rho = rho;
+    nrm.norm_w_f32 = norm_w_dtype == DT_F32;
+  } else if (out_dtype != DT_F32 && out_dtype != DT_BF16) {
+    set_error("gemv_bf16_normed: unsupported output type %d", out_dtype);
+    return ERR_UNSUPPORTED;
+  }
+  nrm.ss_in = ss_in;
+  nrm.ss_blocks = ss_blocks;
+  nrm.eps = eps;
+  nrm.width = width;
+  const bool f32 = out_dtype == DT_F32 && epilogue != 2;
+  const bool scale = ss_in != nullptr;
+  int warps, stages;
+  const int nt = gemv_shape(M, N, K, warps, stages);
+#define EXL3_GN4(NT, TO, EPI, ST)                                                                          \
+  return scale ? launch<NT, TO, EPI, ST, true>(x, w, bias, y, M, N, K, warps, stream, nrm)                  \
+               : launch<NT, TO, EPI, ST, false>(x, w, bias, y, M, N, K, warps, stream, nrm)
+#define EXL3_GN3(NT, TO, EPI) if (stages == 6) { EXL3_GN4(NT, TO, EPI, 6); } else { EXL3_GN4(NT, TO, EPI, 4); }
+#define EXL3_GN2(NT, EPI) if (f32) { EXL3_GN3(NT, float, EPI) } else { EXL3_GN3(NT, __nv_bfloat16, EPI) }
+#define EXL3_GN1(NT) if (epilogue == 0) { EXL3_GN2(NT, 0) } else if (epilogue == 1) { EXL3_GN2(NT, 1) } else { EXL3_GN3(NT, __nv_bfloat16, 2) }
+  if (nt == 1) { EXL3_GN1(1) }
+  EXL3_GN1(2)
+#undef EXL3_GN1
+#undef EXL3_GN2
+#undef EXL3_GN3
+#undef EXL3_GN4
 }

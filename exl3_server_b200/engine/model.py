@@ -70,8 +70,16 @@ class Model:
 
     def forward(self, batch: StepBatch, cache: SequenceCache) -> Optional[torch.Tensor]:
         stream = self.embedding.forward(batch.token_ids)
-        for i, e in enumerate(self.plan.schedule):
-            self.blocks[e.layer].forward(stream, batch, cache.view(i, batch.block_tables), cache.state_of(i))
+        sched = self.plan.schedule
+        for i, e in enumerate(sched):
+            block = self.blocks[e.layer]
+            kv, state = cache.view(i, batch.block_tables), cache.state_of(i)
+            if getattr(block, "takes_after", False):
+                # the norm that the next block applies first, so that this block's last projection may apply it
+                nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+                block.forward(stream, batch, kv, state, after=getattr(nxt, "mixer_norm", None))
+            else:
+                block.forward(stream, batch, kv, state)
         if batch.n_wanted == 0:
             return None
         return self.head.forward(stream, self.final_norm, batch.want_rows)

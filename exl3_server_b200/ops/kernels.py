@@ -183,6 +183,53 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
+def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                     gated: bool = False, scale=None, resid=None):
+    """``gemv_bf16`` as one or both sides of a norm that is no kernel of its own (see gemv_bf16.cu).
+
+    ``scale = (ss, eps, width)``: ``x`` is the ``x_raw`` of a producing call; results are multiplied per batch row
+    by ``rsqrt(ss.sum(0) / width + eps)`` before bias and gating.
+    ``resid = (h, rho, norm_w)``: nothing is returned as output; ``h += result * rho`` in place (float32), and
+    ``(x_raw, ss)`` is returned: ``h * norm_w`` as bfloat16 and the blocks' sums of squares ``[ceil(N/16), 16]``."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemv_bf16_normed: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemv_bf16_normed: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
+    if scale is not None:
+        ss_in, eps, width = scale
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[1] != 16:
+            raise KernelLibraryError("gemv_bf16_normed: ss must be float32 [blocks, 16]")
+        _contig(ss_in, "ss")
+        ss_blocks = ss_in.shape[0]
+    if resid is not None:
+        if gated:
+            raise KernelLibraryError("gemv_bf16_normed: the gated epilogue does not write into the residual")
+        h, rho, norm_w = resid
+        if h.dtype != torch.float32 or tuple(h.shape) != (M, N) or tuple(norm_w.shape) != (N,):
+            raise KernelLibraryError(f"gemv_bf16_normed: h {tuple(h.shape)} / norm weight {tuple(norm_w.shape)} "
+                                     f"do not fit an output of {(M, N)}")
+        _contig(h, "h")
+        _contig(norm_w, "norm_w")
+        x_raw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ss_out = torch.empty(((N + 15) // 16, 16), dtype=torch.float32, device=x.device)
+        _check(library().exl3_gemv_bf16_normed(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(None), _c_int(DT_BF16), _c_int(M), _c_int(N), _c_int(K), _c_int(2),
+            _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(h), _c_float(rho), _ptr(norm_w),
+            _c_int(dtype_code(norm_w.dtype)), _ptr(x_raw), _ptr(ss_out), _stream()), "gemv_bf16_normed")
+        return x_raw, ss_out
+    out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    _check(library().exl3_gemv_bf16_normed(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(M), _c_int(N), _c_int(K),
+        _c_int(1 if gated else 0), _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(None),
+        _c_float(0.0), _ptr(None), _c_int(DT_BF16), _ptr(None), _ptr(None), _stream()), "gemv_bf16_normed")
+    return out
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
             gated: bool = False) -> torch.Tensor:
     """``x @ w.T (+ bias)`` in bfloat16 on the tcgen05 tensor cores; with ``gated``

@@ -72,7 +72,10 @@ class Attention:
     def state_request(self) -> Optional[StateRequest]:
         return None
 
-    def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
+    takes_then = True       # the last projection may fold its output into the residual (NormAfter)
+    takes_raw = True        # the first projection takes a norm's output in two pieces (RawNormed)
+
+    def forward(self, x: torch.Tensor, batch, kv, state, then=None) -> torch.Tensor:
         s = self.spec
         if kv is None:
             raise RuntimeError("attention needs a cache view")
@@ -82,7 +85,7 @@ class Attention:
         if not self._decode_fused(qkv, out, batch, kv):
             self.position.rotate_and_store(qkv, batch, kv, s.heads, s.kv_heads, s.head_dim)
             self.attend(qkv, out, batch, kv)
-        return self.o(out)
+        return self.o(out, then=then)
 
     def _decode_fused(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
         """One token per sequence, bfloat16, heads of 64: the decode kernel rotates the queries and the new key

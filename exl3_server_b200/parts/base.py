@@ -59,14 +59,58 @@ class ResidualStream:
         self.h = h
         self.pending: Optional[torch.Tensor] = None
         self.pending_scale: float = 1.0
+        # (norm, RawNormed): what ``norm`` needs for its output over the residual as it stands, left by a
+        # projection that folded its output into the residual in its own kernel (see NormAfter)
+        self.normed = None
 
     def push(self, y: torch.Tensor, scale: float) -> None:
         if self.pending is not None:
             raise RuntimeError("residual stream already holds an output that was not folded in")
         self.pending = y
         self.pending_scale = scale
+        self.normed = None
+
+    def take_normed(self, norm):
+        """What a projection has left for ``norm`` over the residual as it stands (a ``RawNormed``), or None."""
+        got, self.normed = self.normed, None
+        if got is not None and self.pending is None and got[0] is norm:
+            return got[1]
+        return None
 
     def take(self):
         y, s = self.pending, self.pending_scale
         self.pending, self.pending_scale = None, 1.0
         return y, s
+
+
+class RawNormed:
+    """A norm's output in two pieces, as a projection kernel left it: ``x_raw = h * weight`` (bfloat16) and the
+    sums of squares of ``h`` per block of 16 features and batch row (``ss [blocks, 16]``); the output itself is
+    ``x_raw * rsqrt(ss.sum(0) / width + eps)`` per row.  A projection that takes it applies the factor to its
+    results (``Linear`` does); anyone else calls ``materialize()``."""
+
+    def __init__(self, x_raw: torch.Tensor, ss: torch.Tensor, eps: float, width: int):
+        self.x_raw, self.ss, self.eps, self.width = x_raw, ss, eps, width
+
+    @property
+    def shape(self):
+        return self.x_raw.shape
+
+    def materialize(self, out_scale: float = 1.0) -> torch.Tensor:
+        rows = self.x_raw.shape[0]
+        inv = torch.rsqrt(self.ss[:, :rows].sum(dim=0) / float(self.width) + self.eps)
+        return (self.x_raw.float() * (inv * out_scale)[:, None]).to(self.x_raw.dtype)
+
+
+class NormAfter:
+    """An offer to a part's last projection: instead of returning its output ``y`` to be added later, it may,
+    where its kernel can, add ``y * scale`` to the residual ``stream.h`` itself and leave what ``norm`` needs
+    for its output over the new residual in ``stream.normed`` (then ``done`` is set, the projection returns
+    None and the caller adds nothing).  A part that takes the offer declares ``takes_then = True`` and passes
+    ``then`` to its last ``Linear`` call; everything still works when the offer is ignored."""
+
+    def __init__(self, stream: ResidualStream, scale: float, norm):
+        self.stream = stream
+        self.scale = scale
+        self.norm = norm
+        self.done = False

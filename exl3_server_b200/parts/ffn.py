@@ -52,10 +52,13 @@ class SwiGLU:
         self.gate_up = Linear(w, b, ctx.dtype)
         self.down = Linear(tensors[prefix + "down_proj.weight"], tensors.get(prefix + "down_proj.bias"), ctx.dtype)
 
-    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+    takes_then = True       # the last projection may fold its output into the residual (NormAfter)
+    takes_raw = True        # the first projection takes a norm's output in two pieces (RawNormed)
+
+    def forward(self, x: torch.Tensor, batch, then=None) -> torch.Tensor:
         if self.interleave and self.gate_up.fuses_gate():
-            return self.down(self.gate_up.gated(x))
-        return self.down(K.silu_mul(self.gate_up(x), interleave=self.interleave))
+            return self.down(self.gate_up.gated(x), then=then)
+        return self.down(K.silu_mul(self.gate_up(x), interleave=self.interleave), then=then)
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()

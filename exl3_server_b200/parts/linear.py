@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 
 from ..ops import kernels as K
+from .base import RawNormed
 
 
 class Linear:
@@ -28,13 +29,35 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
         self.dtype = dtype
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: Optional[torch.dtype] = None, then=None) -> Optional[torch.Tensor]:
+        """``x``: a tensor, or a ``RawNormed`` (a norm's output in two pieces: the weight-streaming GEMV applies
+        the missing factor per row to its results; other paths materialise it first).
+        ``then``: a ``NormAfter`` offer; taken when the weight-streaming GEMV runs (at most 16 rows, bfloat16)
+        and the output is as wide as the residual: its blocks add the output to the residual and leave the
+        pieces of the next norm's output.  Returns None then."""
         out_dtype = out_dtype or self.dtype
         M = x.shape[0]
+        fast = self.in_features % 8 == 0
+        streams = self.dtype == torch.bfloat16 and fast and M <= K.GEMV_MAX_ROWS
+        scale = None
+        if isinstance(x, RawNormed):
+            if streams:
+                scale, x = (x.ss, x.eps, float(x.width)), x.x_raw
+            else:
+                x = x.materialize()
         if self.dtype == torch.float32:
             return K.gemm_simt(x, self.weight, self.bias, torch.float32)
-        fast = self.in_features % 8 == 0
-        if fast and M <= K.GEMV_MAX_ROWS:
+        if streams:
+            if (then is not None and out_dtype == torch.bfloat16 and hasattr(then.norm, "fuse_args")
+                    and then.stream.pending is None and tuple(then.stream.h.shape) == (M, self.out_features)):
+                norm_w, eps, width = then.norm.fuse_args()
+                x_raw, ss = K.gemv_bf16_normed(x, self.weight, self.bias, torch.bfloat16, scale=scale,
+                                               resid=(then.stream.h, then.scale, norm_w))
+                then.stream.normed = (then.norm, RawNormed(x_raw, ss, eps, width))
+                then.done = True
+                return None
+            if scale is not None:
+                return K.gemv_bf16_normed(x, self.weight, self.bias, out_dtype, scale=scale)
             return K.gemv_bf16(x, self.weight, self.bias, out_dtype)
         if out_dtype == torch.bfloat16 and fast:
             return torch.nn.functional.linear(x, self.weight, self.bias)
@@ -61,6 +84,11 @@ class Linear:
         of the same features, and so on: ``silu(gate) * up`` in the projection's
         own epilogue, so the gate/up product never goes to memory.  Up to 16 rows:
         the weight-streaming GEMV; more: the tcgen05 tensor-core GEMM."""
+        if isinstance(x, RawNormed):
+            if x.shape[0] <= K.GEMV_MAX_ROWS:
+                return K.gemv_bf16_normed(x.x_raw, self.weight, self.bias, self.dtype, gated=True,
+                                          scale=(x.ss, x.eps, float(x.width)))
+            x = x.materialize()
         if x.shape[0] <= K.GEMV_MAX_ROWS:
             return K.gemv_bf16(x, self.weight, self.bias, self.dtype, gated=True)
         return K.gemm_tc(x, self.weight, self.bias, gated=True)

@@ -30,11 +30,25 @@ class RMSNorm:
         self.weight = w.contiguous() if w.dtype == torch.float32 else w.to(ctx.dtype).contiguous()
         self.out_dtype = ctx.dtype
 
+    offers_raw = True
+
     def add_norm(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None,
-                 out_scale: float = 1.0) -> torch.Tensor:
+                 out_scale: float = 1.0, raw_ok: bool = False):
+        """``raw_ok``: the caller's next projection takes a ``RawNormed`` (the output in two pieces, left by the
+        projection before this norm) as well as a tensor."""
+        left = stream.take_normed(self)
+        if left is not None:
+            if rows is None and raw_ok and out_scale == 1.0:
+                return left
+            r = left.materialize(out_scale)
+            return r if rows is None else r.index_select(0, rows.long())
         y, s = stream.take()
         return K.add_rmsnorm(stream.h, y, s, self.weight, self.spec.eps, self.out_dtype,
                              out_scale=out_scale, rows=rows)
+
+    def fuse_args(self):
+        """``(weight, eps, width)`` for a projection kernel that prepares this norm (see ``NormAfter``)."""
+        return self.weight, self.spec.eps, self.spec.width
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -175,6 +175,46 @@ def test_gemm_tc_waits_are_bounded():
     close(K().gemm_tc(x, w, None), x.double() @ w.double().T, TOL[torch.bfloat16], "gemm_tc after a timed-out wait")
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("N,Kd", [(2304, 2304), (2304, 5760), (263, 96), (50, 40), (136, 208)])
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_gemv_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_dtype):
+    """The producing side of a norm that is no kernel of its own: h += y * rho, x_raw = h * w, sums of squares."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    nw = (1.0 + 0.2 * torch.randn(N, generator=g)).to(norm_dtype).to(DEV)
+    h0 = torch.randn(M, N, generator=g).to(DEV)
+    rho, eps = 0.37, 1e-5
+    for bias in (None, b):
+        h = h0.clone()
+        x_raw, ss = K().gemv_bf16_normed(x, w, bias, torch.bfloat16, resid=(h, rho, nw))
+        y = K().gemv_bf16(x, w, bias, torch.bfloat16)       # what the plain kernel stores
+        want_h = h0.double() + y.double() * rho
+        close(h, want_h, 2e-6, "residual")
+        close(x_raw, want_h * nw.double(), 6e-3, "residual times the norm weight")
+        assert ss.shape == ((N + 15) // 16, 16)
+        close(ss[:, :M].sum(0), (want_h * want_h).sum(1), 1e-5, "sums of squares")
+        if M < 16:
+            assert float(ss[:, M:].abs().max()) == 0.0
+        # the consuming side: a second projection over the norm's output, against the two kernels in turn
+        N2 = 176
+        w2 = (torch.randn(N2, N, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        b2 = torch.randn(N2, generator=g).to(torch.bfloat16).to(DEV)
+        if N % 8 == 0:
+            h2 = h0.clone()
+            r = K().add_rmsnorm(h2, y, rho, nw, eps, torch.bfloat16)
+            for bias2 in (None, b2):
+                want = r.double() @ w2.double().T + (0 if bias2 is None else bias2.double())
+                got = K().gemv_bf16_normed(x_raw, w2, bias2, torch.float32, scale=(ss, eps, float(N)))
+                close(got, want, 1e-2, "second projection")
+            wg = torch.stack([w2[:N2 // 2].view(-1, 8, N), w2[N2 // 2:].view(-1, 8, N)], dim=1).reshape(N2, N).contiguous()
+            got = K().gemv_bf16_normed(x_raw, wg, None, torch.bfloat16, gated=True, scale=(ss, eps, float(N)))
+            gate, up = r.double() @ w2[:N2 // 2].double().T, r.double() @ w2[N2 // 2:].double().T
+            close(got, torch.nn.functional.silu(gate) * up, 1.5e-2, "gated second projection")
+
+
 def test_gemv_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(17, 64, device=DEV).bfloat16()
