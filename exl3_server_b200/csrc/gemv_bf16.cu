@@ -53,7 +53,7 @@ template <int N> __device__ inline void cp_async_wait_group() { asm volatile("cp
 //   h += y * rho;   r = h * rsqrt(mean(h^2) + eps) * norm_w;   y2 = r . w2^T
 // is done in pieces.  The projection that produces y (EPI 2) keeps no y: each of its blocks adds its 16 features
 // to the float32 residual h, writes them times the norm weight as bfloat16 (x_raw) and writes the sums of their
-// squares per batch row (ss_part[block][16]).  The projection that consumes r (SCALE) reads x_raw as its input,
+// squares per batch row (ss_part[16][blocks]).  The projection that consumes r (SCALE) reads x_raw as its input,
 // adds the blocks' sums in an order that depends on its thread count only, and multiplies its results by
 // rsqrt(sum / width + eps) before bias and gating: a factor per batch row commutes with the product.  Statistics and the residual stay float32.
 struct GemvNorm {
@@ -61,11 +61,11 @@ struct GemvNorm {
   float* h;                      // [M, N] residual, updated in place
   const void* norm_w;            // [N] weight of the norm that follows
   __nv_bfloat16* x_raw;          // [M, N] out: h * norm_w
-  float* ss_out;                 // [blocks, 16] out: sums of squares of the block's features, per batch row
+  float* ss_out;                 // [16, blocks] out: sums of squares of the block's features, per batch row
   float rho;
   int norm_w_f32;
   // SCALE, the consuming side
-  const float* ss_in;            // [ss_blocks, 16] from the producer
+  const float* ss_in;            // [16, ss_blocks] from the producer
   int ss_blocks;
   float eps, width;
 };
@@ -77,7 +77,7 @@ template <int NT, typename TO, int EPI, int GEMV_STAGES, bool SCALE = false>
 __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
                  const __nv_bfloat16* __restrict__ bias, TO* __restrict__ y, int M, int N, int K, GemvNorm nrm) {
-  __shared__ float s_ss[GEMV_MAX_WARPS * 32];           // SCALE: every thread's share of its batch row's sum of squares
+  __shared__ float s_inv[16];                           // SCALE: rsqrt(mean square + eps) of each batch row
   extern __shared__ uint4 ring[];                     // [GEMV_STAGES][2 + NT][blockDim.x]: weights a, b, then x
   pdl_trigger();
   const int tid = threadIdx.x, nthreads = blockDim.x;
@@ -130,9 +130,6 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     if (i < n_my) issue_x(i);
     cp_async_commit_group();
   }
-  // SCALE: the producer's sums of squares [ss_blocks][16].  Thread t takes the values t, t + threads, ...: all of
-  // batch row t & 15 (the thread count is a multiple of 16).  The loads are asked for here, together with the
-  // activations, and added up after the loop; the 16-lane groups' sums meet in shared memory.
   // EPI 2: the epilogue's own operands (a residual value and a norm weight per thread, when the block has at
   // least 16 * 8 * NT threads) are asked for here too
   float h_pre = 0.0f, wn_pre = 0.0f;
@@ -144,14 +141,20 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
                               : __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(nrm.norm_w) + n));
     }
   }
-  constexpr int SS_AHEAD = 8;
-  float ss_v[SS_AHEAD];
+  // SCALE: the producer's sums of squares [16][ss_blocks].  Warp w adds up batch rows w, w + warps, ...: its lanes
+  // take a row's values side by side.  The loads are asked for here, together with the activations, and added
+  // up after the loop (an order that depends on the number of blocks only).
+  constexpr int SS_ROWS = 4, SS_AHEAD = 8;               // rows per warp and values per lane asked for ahead
+  float ss_v[SS_ROWS][SS_AHEAD];
   if constexpr (SCALE) {
-    const int n_ss = nrm.ss_blocks * 16;
 #pragma unroll
-    for (int j = 0; j < SS_AHEAD; ++j) {
-      const int idx = tid + j * nthreads;
-      ss_v[j] = idx < n_ss ? __ldcg(nrm.ss_in + idx) : 0.0f;
+    for (int rr = 0; rr < SS_ROWS; ++rr) {
+      const int m = warp + rr * nwarps;
+#pragma unroll
+      for (int j = 0; j < SS_AHEAD; ++j) {
+        const int p = lane + 32 * j;
+        ss_v[rr][j] = (m < M && p < nrm.ss_blocks) ? __ldcg(nrm.ss_in + (int64_t)m * nrm.ss_blocks + p) : 0.0f;
+      }
     }
   }
   // Groups complete in order: W0..W(S-2), X0..X(S-2), then one group per iteration.  Block i
@@ -179,19 +182,26 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     part[warp][gid + 8][t * 8 + tig * 2 + 1] = c[t][3];
   }
   if constexpr (SCALE) {
-    float ss = 0.0f;
+    for (int rr = 0; warp + rr * nwarps < M; ++rr) {
+      const int m = warp + rr * nwarps;
+      float ss = 0.0f;
+      if (rr < SS_ROWS) {
 #pragma unroll
-    for (int j = 0; j < SS_AHEAD; ++j) ss += ss_v[j];
-    for (int idx = tid + SS_AHEAD * nthreads; idx < nrm.ss_blocks * 16; idx += nthreads) ss += __ldcg(nrm.ss_in + idx);
-    s_ss[tid] = ss;
+        for (int q = 0; q < SS_ROWS; ++q) {
+          if (q == rr) {
+#pragma unroll
+            for (int j = 0; j < SS_AHEAD; ++j) ss += ss_v[q][j];
+          }
+        }
+        for (int p = lane + 32 * SS_AHEAD; p < nrm.ss_blocks; p += 32) ss += __ldcg(nrm.ss_in + (int64_t)m * nrm.ss_blocks + p);
+      } else {
+        for (int p = lane; p < nrm.ss_blocks; p += 32) ss += __ldcg(nrm.ss_in + (int64_t)m * nrm.ss_blocks + p);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) s_inv[m] = 1.0f / sqrtf(ss / nrm.width + nrm.eps);
+    }
   }
   __syncthreads();
-  // the factor of batch row m: the shares of the threads t with t & 15 == m, added in thread order
-  auto row_factor = [&](int m) {
-    float ss = 0.0f;
-    for (int t = m; t < nthreads; t += 16) ss += s_ss[t];
-    return 1.0f / sqrtf(ss / nrm.width + nrm.eps);
-  };
   if (EPI == 0) {
     for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += blockDim.x) {
       const int m = idx >> 4, r = idx & 15;           // consecutive threads: consecutive features
@@ -199,7 +209,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       if (m >= M || n >= N) continue;
       float s = 0.0f;
       for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
-      if (SCALE) s *= row_factor(m);
+      if (SCALE) s *= s_inv[m];
       if (bias) s += __bfloat162float(bias[n]);
       Elem<TO>::store(y + (int64_t)m * N + n, s);
     }
@@ -211,7 +221,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       if (m >= M || f >= n_out) continue;
       float g = 0.0f, u = 0.0f;
       for (int wi = 0; wi < nwarps; ++wi) { g += part[wi][r][m]; u += part[wi][r + 8][m]; }
-      if (SCALE) { const float f = row_factor(m); g *= f; u *= f; }
+      if (SCALE) { g *= s_inv[m]; u *= s_inv[m]; }
       if (bias) { g += __bfloat162float(bias[r0 + r]); u += __bfloat162float(bias[r0 + r + 8]); }
       Elem<TO>::store(y + (int64_t)m * n_out + f, g / (1.0f + expf(-g)) * u);
     }
@@ -225,7 +235,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       if (m < M && n < N) {
         float s = 0.0f;
         for (int wi = 0; wi < nwarps; ++wi) s += part[wi][r][m];
-        if (SCALE) s *= row_factor(m);
+        if (SCALE) s *= s_inv[m];
         if (bias) s += __bfloat162float(bias[n]);
         // the output is rounded to bfloat16 as it would be on its way through memory
         const bool first = idx == (int)threadIdx.x;     // the first pass uses what was asked for before the loop
@@ -242,9 +252,9 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
       sq += __shfl_xor_sync(0xffffffffu, sq, 4);
       sq += __shfl_xor_sync(0xffffffffu, sq, 2);
       sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-      if (r == 0) nrm.ss_out[(int64_t)blockIdx.x * 16 + m] = sq;     // zero for rows beyond M
+      if (r == 0) nrm.ss_out[(int64_t)m * gridDim.x + blockIdx.x] = sq;     // zero for rows beyond M
     }
-    if (NT == 1 && threadIdx.x >= 8 && threadIdx.x < 16) nrm.ss_out[(int64_t)blockIdx.x * 16 + threadIdx.x] = 0.0f;
+    if (NT == 1 && threadIdx.x >= 8 && threadIdx.x < 16) nrm.ss_out[(int64_t)threadIdx.x * gridDim.x + blockIdx.x] = 0.0f;
   }
 }
 
@@ -332,7 +342,7 @@ extern "C" int exl3_gemv_bf16(const void* x, const void* w, const void* bias, vo
 // ss_in / ss_blocks / eps / width: when ss_in is not null, x is the x_raw of a producing call and the results are
 // multiplied by rsqrt(sum of the blocks' sums / width + eps) per batch row before bias and gating.
 // epilogue 0 or 1: y as in exl3_gemv_bf16 (out_dtype).  epilogue 2: no y; h[M, N] += result * rho,
-// x_raw[M, N] = h * norm_w, ss_out[ceil(N / 16), 16] = the blocks' sums of squares.
+// x_raw[M, N] = h * norm_w, ss_out[16, ceil(N / 16)] = the blocks' sums of squares.
 extern "C" int exl3_gemv_bf16_normed(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
                                      int N, int K, int epilogue, const float* ss_in, int ss_blocks, float eps,
                                      float width, float* h, float rho, const void* norm_w, int norm_w_dtype,

@@ -188,9 +188,9 @@ def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     """``gemv_bf16`` as one or both sides of a norm that is no kernel of its own (see gemv_bf16.cu).
 
     ``scale = (ss, eps, width)``: ``x`` is the ``x_raw`` of a producing call; results are multiplied per batch row
-    by ``rsqrt(ss.sum(0) / width + eps)`` before bias and gating.
+    by ``rsqrt(ss.sum(1) / width + eps)`` before bias and gating.
     ``resid = (h, rho, norm_w)``: nothing is returned as output; ``h += result * rho`` in place (float32), and
-    ``(x_raw, ss)`` is returned: ``h * norm_w`` as bfloat16 and the blocks' sums of squares ``[ceil(N/16), 16]``."""
+    ``(x_raw, ss)`` is returned: ``h * norm_w`` as bfloat16 and the blocks' sums of squares ``[16, ceil(N/16)]``."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2:
@@ -202,10 +202,10 @@ def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
     if scale is not None:
         ss_in, eps, width = scale
-        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[1] != 16:
-            raise KernelLibraryError("gemv_bf16_normed: ss must be float32 [blocks, 16]")
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] != 16:
+            raise KernelLibraryError("gemv_bf16_normed: ss must be float32 [16, blocks]")
         _contig(ss_in, "ss")
-        ss_blocks = ss_in.shape[0]
+        ss_blocks = ss_in.shape[1]
     if resid is not None:
         if gated:
             raise KernelLibraryError("gemv_bf16_normed: the gated epilogue does not write into the residual")
@@ -216,7 +216,7 @@ def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
         _contig(h, "h")
         _contig(norm_w, "norm_w")
         x_raw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        ss_out = torch.empty(((N + 15) // 16, 16), dtype=torch.float32, device=x.device)
+        ss_out = torch.empty((16, (N + 15) // 16), dtype=torch.float32, device=x.device)
         _check(library().exl3_gemv_bf16_normed(
             _ptr(x), _ptr(w), _ptr(bias), _ptr(None), _c_int(DT_BF16), _c_int(M), _c_int(N), _c_int(K), _c_int(2),
             _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(h), _c_float(rho), _ptr(norm_w),

@@ -85,8 +85,8 @@ class ResidualStream:
 
 class RawNormed:
     """A norm's output in two pieces, as a projection kernel left it: ``x_raw = h * weight`` (bfloat16) and the
-    sums of squares of ``h`` per block of 16 features and batch row (``ss [blocks, 16]``); the output itself is
-    ``x_raw * rsqrt(ss.sum(0) / width + eps)`` per row.  A projection that takes it applies the factor to its
+    sums of squares of ``h`` per batch row and block of 16 features (``ss [16, blocks]``); the output itself is
+    ``x_raw * rsqrt(ss.sum(1) / width + eps)`` per row.  A projection that takes it applies the factor to its
     results (``Linear`` does); anyone else calls ``materialize()``."""
 
     def __init__(self, x_raw: torch.Tensor, ss: torch.Tensor, eps: float, width: int):
@@ -98,7 +98,7 @@ class RawNormed:
 
     def materialize(self, out_scale: float = 1.0) -> torch.Tensor:
         rows = self.x_raw.shape[0]
-        inv = torch.rsqrt(self.ss[:, :rows].sum(dim=0) / float(self.width) + self.eps)
+        inv = torch.rsqrt(self.ss[:rows].sum(dim=1) / float(self.width) + self.eps)
         return (self.x_raw.float() * (inv * out_scale)[:, None]).to(self.x_raw.dtype)
 
 

@@ -194,10 +194,10 @@ def test_gemv_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_dtype
         want_h = h0.double() + y.double() * rho
         close(h, want_h, 2e-6, "residual")
         close(x_raw, want_h * nw.double(), 6e-3, "residual times the norm weight")
-        assert ss.shape == ((N + 15) // 16, 16)
-        close(ss[:, :M].sum(0), (want_h * want_h).sum(1), 1e-5, "sums of squares")
+        assert ss.shape == (16, (N + 15) // 16)
+        close(ss[:M].sum(1), (want_h * want_h).sum(1), 1e-5, "sums of squares")
         if M < 16:
-            assert float(ss[:, M:].abs().max()) == 0.0
+            assert float(ss[M:].abs().max()) == 0.0
         # the consuming side: a second projection over the norm's output, against the two kernels in turn
         N2 = 176
         w2 = (torch.randn(N2, N, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
