@@ -169,14 +169,15 @@ class ToyConfig:
     vocab: int
     decay: float
     layout: List[str]                 # per layer: "ema" or "attn"
+    head_dim: int = 16                # of the attention layers (64: the tensor-core attention kernels' shape)
 
     @classmethod
     def from_dict(cls, d):
-        return cls(d["width"], d["vocab"], d["decay"], list(d["layout"]))
+        return cls(d["width"], d["vocab"], d["decay"], list(d["layout"]), int(d.get("head_dim", 16)))
 
     def to_dict(self):
         return {"architectures": ["ToyEmaLM"], "model_type": "toy_ema", "width": self.width, "vocab": self.vocab,
-                "decay": self.decay, "layout": self.layout}
+                "decay": self.decay, "layout": self.layout, "head_dim": self.head_dim}
 
 
 class EmaMixer:
@@ -229,8 +230,8 @@ def toy_plan(cfg: ToyConfig):
         if kind == "ema":
             mixer = MixerSpec("test_ema", width=cfg.width, params={"decay": cfg.decay})
         else:
-            mixer = MixerSpec("attention", width=cfg.width, heads=2, kv_heads=1, head_dim=16,
-                              position=PositionSpec("rope", dims=16, theta=100.0))
+            mixer = MixerSpec("attention", width=cfg.width, heads=2, kv_heads=1, head_dim=cfg.head_dim,
+                              position=PositionSpec("rope", dims=cfg.head_dim, theta=100.0))
         layers.append(LayerSpec("prenorm", mixer, FeedForwardSpec("swiglu", cfg.width, 2 * cfg.width),
                                 NormSpec("rms", cfg.width, 1e-5), NormSpec("rms", cfg.width, 1e-5), 0.5,
                                 names={"mixer": p + "mix.", "feed_forward": p + "ff.", "mixer_norm": p + "n1.",
@@ -264,9 +265,10 @@ def toy_plain_logits(w: Dict[str, torch.Tensor], cfg: ToyConfig, ids: List[int])
                 s = cfg.decay * s + (1 - cfg.decay) * r[t]
                 y[t] = s * w[p + "mix.scale"]
         else:
-            q = P.linear(r, w[p + "mix.q_proj.weight"]).view(L, 2, 16).transpose(0, 1)
-            k = P.linear(r, w[p + "mix.k_proj.weight"]).view(L, 1, 16).transpose(0, 1)
-            v = P.linear(r, w[p + "mix.v_proj.weight"]).view(L, 1, 16).transpose(0, 1)
+            hd = cfg.head_dim
+            q = P.linear(r, w[p + "mix.q_proj.weight"]).view(L, 2, hd).transpose(0, 1)
+            k = P.linear(r, w[p + "mix.k_proj.weight"]).view(L, 1, hd).transpose(0, 1)
+            v = P.linear(r, w[p + "mix.v_proj.weight"]).view(L, 1, hd).transpose(0, 1)
             pos = torch.arange(L)
             q, k = P.rope(q, pos, 100.0), P.rope(k, pos, 100.0)
             if si == n + 1:
@@ -280,15 +282,17 @@ def toy_plain_logits(w: Dict[str, torch.Tensor], cfg: ToyConfig, ids: List[int])
     return P.linear(P.rms_norm(h, w["toy.norm.weight"], 1e-5), w["toy.emb"])
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+@pytest.mark.parametrize("dtype,head_dim", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
+def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, dtype, head_dim):
     from exl3_server_b200 import Engine
     from exl3_server_b200.config import register_architecture, unregister_architecture
     from exl3_server_b200.engine.model import plan_manifest
     from exl3_server_b200.parts import register_mixer, unregister
     from exl3_server_b200.weights import write_safetensors
     from exl3_server_b200.weights.random_init import random_tensors
-    cfg = ToyConfig(width=32, vocab=50, decay=0.8, layout=["ema", "attn", "ema", "attn"])
+    # heads of 64 in bfloat16: the last schedule entry, which reads another entry's keys and values, then goes
+    # through the tensor-core decode kernel without a cache write of its own
+    cfg = ToyConfig(width=32, vocab=50, decay=0.8, layout=["ema", "attn", "ema", "attn"], head_dim=head_dim)
     register_mixer("test_ema", EmaMixer)
     register_architecture(["ToyEmaLM", "toy_ema"], ToyConfig, toy_plan)
     try:
