@@ -744,7 +744,9 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   if (rc) return rc;
   rc = ad_make_map(&map_v, v_pool, n_pool_rows);
   if (rc) return rc;
-  const int blocks = (int)std::min<int64_t>(sms, ((int64_t)T * nkv * max_splits + AD_WARPS - 1) / AD_WARPS);
+  // one block per SM as soon as there is a chunk for each: the warps' equal shares then spread few chunks over all
+  // SMs (and their memory pipes) instead of filling the warps of half of them
+  const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * nkv * max_splits);
   int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
   launch_pdl(attn_decode_kernel, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,
