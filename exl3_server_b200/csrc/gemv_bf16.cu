@@ -291,7 +291,7 @@ static int gemv_shape(int M, int N, int K, int& warps, int& stages) {
   const int ctas = ceil_div(N, 16);
   warps = ctas >= 4 * gemv_sm_count() ? 4 : (ctas >= 2 * gemv_sm_count() ? 8 : 16);
   while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
-  stages = (nt == 2 && warps == 16) ? 4 : 6;             // 16 warps x 6 stages x 4 slots would not fit
+  stages = nt == 2 ? 4 : 6;      // four slots per stage: six stages would not fit 16 warps, and with 8 warps only two blocks an SM
   return nt;
 }
 
