@@ -14,6 +14,8 @@
 #include "api.h"
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace exl3 {
 
 __device__ inline uint4 ldg_stream(const void* p) {
@@ -81,8 +83,10 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
   extern __shared__ uint4 ring[];                     // [GEMV_STAGES][2 + NT][blockDim.x]: weights a, b, then x
   pdl_trigger();
   const int tid = threadIdx.x, nthreads = blockDim.x;
-  // partial tiles of the warps, behind the ring: [warps][16][8 NT + 1]
-  float (*part)[16][8 * NT + 1] = reinterpret_cast<float (*)[16][8 * NT + 1]>(ring + GEMV_STAGES * (2 + NT) * nthreads);
+  // partial tiles of the warps, [warps][16][8 NT + 1]: in the ring's place, once every thread is done with the ring
+  // (kept apart they cost the q/k/v projection its third block per SM: 3 x 78 KB do not fit, and its 432 blocks
+  // then run as one and a half waves)
+  float (*part)[16][8 * NT + 1] = reinterpret_cast<float (*)[16][8 * NT + 1]>(ring);
   const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int r0 = blockIdx.x * 16;
@@ -174,6 +178,8 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
     if (i + GEMV_STAGES - 1 < n_my) { issue_w(i + GEMV_STAGES - 1); issue_x(i + GEMV_STAGES - 1); }
     cp_async_commit_group();
   }
+  cp_async_wait_group<0>();
+  __syncthreads();                                     // the ring is free: the partial tiles take its place
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     part[warp][gid][t * 8 + tig * 2] = c[t][0];
@@ -259,7 +265,7 @@ gemv_bf16_kernel(const __nv_bfloat16* x, const __nv_bfloat16* __restrict__ w,
 }
 
 static size_t gemv_smem(int nt, int stages, int warps) {
-  return (size_t)stages * (2 + nt) * warps * 32 * sizeof(uint4) + (size_t)warps * 16 * (8 * nt + 1) * sizeof(float);
+  return std::max((size_t)stages * (2 + nt) * warps * 32 * sizeof(uint4), (size_t)warps * 16 * (8 * nt + 1) * sizeof(float));
 }
 
 template <int NT, typename TO, int EPI, int STAGES, bool SCALE = false>
@@ -278,18 +284,17 @@ static int launch(const void* x, const void* w, const void* bias, void* y, int M
   return launch_status("gemv_bf16");
 }
 
-// Few blocks: many warps per block, so that the ring covers most of K at
-// once.  Many blocks: fewer warps each, several blocks per SM.  The choice
-// depends on N and K only, never on M, so a row's result does not depend on
-// its batch.  (Measured: block shapes that make all blocks resident at once,
-// or deeper rings, change nothing; a dependent kernel costs about 2 us however
-// small, and mid-sized matrices stay near 3.5-4 TB/s for that reason.)
+// The warps of a block share its 16 rows' K blocks; fewer warps mean a smaller ring, so more blocks per SM: one
+// block of 16 warps, three of 8, six of 4.  The largest block with which all blocks are on the GPU at once is
+// taken (a second, partly filled wave costs its full length: the q/k/v projection's 432 blocks took 8.6 us as
+// 296 + 136 and take 7.5 us as one wave); beyond 6 blocks per SM the smallest.  The choice depends on N and K
+// only, never on M, so a row's result does not depend on its batch.
 static int gemv_sm_count();
 static int gemv_shape(int M, int N, int K, int& warps, int& stages) {
   const int nt = M <= 8 ? 1 : 2;
   const int nblocks = (K + 31) / 32;
   const int ctas = ceil_div(N, 16);
-  warps = ctas >= 4 * gemv_sm_count() ? 4 : (ctas >= 2 * gemv_sm_count() ? 8 : 16);
+  warps = ctas <= gemv_sm_count() ? 16 : (ctas <= 3 * gemv_sm_count() ? 8 : 4);
   while (warps > 1 && (warps / 2) * 2 >= nblocks) warps >>= 1;
   stages = nt == 2 ? 4 : 6;      // four slots per stage: six stages would not fit 16 warps, and with 8 warps only two blocks an SM
   return nt;
