@@ -1,12 +1,13 @@
 // Decode-shaped projection: y[M,N] = x[M,K] . w[N,K]^T (+ bias) for M <= 16
 // rows of x, bfloat16 operands, float32 accumulation.
 //
-// The weight matrix is read exactly once, in 16-byte pieces, straight from
-// global memory into the A fragments of mma.m16n8k16 (weights are the 16-row
-// operand, the batch is the 8-column one).  No shared-memory staging is
-// needed because the order of the K index inside a 32-wide block is free: a
-// thread's 8 consecutive weights and its 8 consecutive activations are
-// assigned to the same logical k slots of two mma instructions.
+// The weight matrix is read exactly once, in 16-byte pieces that go as they
+// are into the A fragments of mma.m16n8k16 (weights are the 16-row operand,
+// the batch is the 8-column one).  No change of layout is needed because the
+// order of the K index inside a 32-wide block is free: a thread's 8
+// consecutive weights and its 8 consecutive activations are assigned to the
+// same logical k slots of two mma instructions.  Shared memory only holds the
+// pieces on their way (a ring per thread, filled by cp.async).
 //
 // A block owns 16 output features; its warps take 32-wide K blocks in turn and
 // their partial tiles are summed in warp order, so a result depends on K, N

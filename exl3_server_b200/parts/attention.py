@@ -10,6 +10,13 @@ head h reading kv head ``h // (heads / kv_heads)`` (src/model.cpp:576-578);
 query at position p to keys ``p - window + 1 .. p``.
 
 The three input projections are one fused matrix, so a step reads ``r`` once.
+
+Which kernels run: prompts in bfloat16 with heads of 64 go through the tcgen05 attention (heads of 128: the
+mma.sync one), after the position part's own step.  Steps in which every sequence brings one token (decode), in
+bfloat16 with heads of 64, are one kernel: it rotates the queries and the token's own key, takes that key and
+value from the projection's output, adds them to the softmax and writes them to the cache (``_decode_fused``;
+the position part must offer ``fused_rotation``).  Everything else (float32, other head sizes) takes the
+position step and the CUDA-core attention kernel.
 """
 from __future__ import annotations
 
@@ -25,7 +32,7 @@ from .linear import Linear
 from .registry import position_class, register_mixer
 from .spec import MixerSpec, PositionSpec
 
-# Keys per work item of the attention kernel; a multiple of the cache's page size.
+# Keys per work item of the CUDA-core attention kernel; a multiple of the cache's page size.
 SPLIT_KEYS = 256
 # Work items (token x kv head x chunk) beyond which the bfloat16 path doubles the chunk length.
 BUSY_ITEMS = 1776
