@@ -81,7 +81,7 @@ int exl3_gemv_bf16_normed(const void* x, const void* w, const void* bias, void* 
                           float rho, const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out,
                           cudaStream_t stream);
 
-// Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64, pages of 64, up
+// Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64 or 128, pages of 64, up
 // to 8 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing
 // them to the cache itself.  See attention_decode.cu.

@@ -1,6 +1,6 @@
 // Attention of decoded tokens over the paged key/value cache: TMA into shared
-// memory, both products on the tensor cores (mma.sync), bfloat16, heads of 64,
-// pages of 64 keys.
+// memory, both products on the tensor cores (mma.sync), bfloat16, heads of 64
+// or 128, pages of 64 keys.
 //
 //   s[j] = (q . K[j]) * scale,  j in [max(0, pos - window + 1), pos]
 //   out  = sum_j softmax(s)[j] * V[j]
@@ -55,14 +55,17 @@
 #include <cuda.h>
 #include <algorithm>
 #include <math.h>
+#include <type_traits>
 
 namespace exl3 {
 
 constexpr int AD_WARPS = 4;
-constexpr int AD_HD = 64, AD_PAGE = 64;
+constexpr int AD_PAGE = 64;
 constexpr int AD_MAX_GROUP = 8;                            // query heads per kv head: the columns of one instruction
-constexpr int AD_TILE_BYTES = AD_PAGE * AD_HD * 2;         // one page of one kv head: 8 KB
-constexpr int AD_STAGE_BYTES = 2 * AD_TILE_BYTES;          // keys, then values
+// A stage holds the keys, then the values, of one page of one kv head (heads of 64) or of half a page (heads of
+// 128): 8 KB each either way.
+constexpr int AD_TILE_BYTES = 8192;
+constexpr int AD_STAGE_BYTES = 2 * AD_TILE_BYTES;
 constexpr int AD_STAGES = 3;
 constexpr uint32_t AD_SMEM = AD_WARPS * AD_STAGES * AD_STAGE_BYTES + 1024;
 constexpr int AD_MAX_TOKENS = 1024;                        // positions, sequences and chunk counts kept in shared memory
@@ -128,13 +131,14 @@ __device__ inline uint32_t ad_pack(float lo, float hi) {
   return r;
 }
 
-// Record layout in scratch: [64] accumulator, then max (base-2 units), then sum; as in attention_simt.cu.
+// Record layout in scratch: [head_dim] accumulator, then max (base-2 units), then sum; as in attention_simt.cu.
 //
 // Under load every round trip to memory takes microseconds (the queues are full of pages on
 // their way), so a warp waits for none of them per chunk: positions and sequences of all tokens
 // are copied to shared memory at the start; page numbers are asked for 32 pages at a time, one
 // batch ahead; queries are asked for one (token, kv head) ahead; records are stored and left
 // behind, and one fence at the end of the warp's work covers them all before it draws tickets.
+template <int HD>
 __global__ void __launch_bounds__(AD_WARPS * 32, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
@@ -143,11 +147,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
                    const float* __restrict__ inv_freq, float pos_scale, int rotate, int write_new,
                    __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
+  constexpr int KS = HD == 64 ? 64 : 32;                 // keys of a stage
+  constexpr int SPP = AD_PAGE / KS;                      // stages of a page
+  constexpr int MT = KS / 16;                            // 16-key tiles of a stage
+  constexpr int NJ = HD / 16;                            // 16-feature pieces of a head
+  constexpr int NBOX = HD / 64;                          // 64-feature boxes (128-byte lines) of a row
+  constexpr int BOX_BYTES = KS * 128;
+  static_assert(KS * HD * 2 == AD_TILE_BYTES, "a stage is 8 KB of keys and 8 KB of values");
   extern __shared__ unsigned char ad_smem_raw[];
   __shared__ uint64_t full[AD_WARPS][AD_STAGES];
   __shared__ int s_pos[AD_MAX_TOKENS], s_seq[AD_MAX_TOKENS];
   __shared__ int s_cum[AD_MAX_TOKENS + 1];               // chunks of the tokens before this one (per kv head)
   __shared__ float s_w[AD_WARPS][AD_MAX_SPLITS], s_l[AD_WARPS][AD_MAX_SPLITS];   // a merge's weights and sums
+  __shared__ __align__(16) float2 s_rot[AD_WARPS][64];   // a token's rotary angles (cos, sin), one table per warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gl = lane >> 2, tl = lane & 3;
   const uint32_t ring = ((ad_smem_u32(ad_smem_raw) + 1023u) & ~1023u) + warp * (AD_STAGES * AD_STAGE_BYTES);
@@ -195,7 +207,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   __syncthreads();
 
   const int G = nh / nkv;
-  const int rec = AD_HD + 2;
+  const int rec = HD + 2;
   // This warp's share: chunks i0 .. i1 - 1 of the list ordered by token, kv head, chunk.
   const int n_chunks = nkv * s_cum[T];
   const int n_warps = gridDim.x * AD_WARPS, gw = blockIdx.x * AD_WARPS + warp;
@@ -222,7 +234,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
   // ldmatrix addresses inside a swizzled tile: row r at r * 128 bytes, its 16-byte piece c at c ^ (r & 7)
   const uint32_t k_row = ((lane & 7) + ((lane >> 3) & 1) * 8) * 128;
-  const uint32_t v_row = ((lane & 7) + ((lane >> 4) & 1) * 8) * 128 + AD_TILE_BYTES;
+  const uint32_t v_row = ((lane & 7) + ((lane >> 4) & 1) * 8) * 128 + AD_TILE_BYTES;   // values follow the keys
   uint32_t k_col[4], v_col[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -232,23 +244,25 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
   // ---- the producer: pages in the order the chunks will want them -----------------------------
   // The chunks of one (token, kv head) that this warp holds are neighbours, and so are their
-  // pages: a run.  Page numbers come 32 at a time (lane i holds page0 + i), one batch ahead.
-  struct Batch { int t, g, page0, run_last; bool some; };
+  // pages: a run.  Page numbers come 32 at a time (lane i holds page0 + i), one batch ahead.  The unit
+  // of copying is a stage's worth of keys (KS: a page, or half of one).
+  struct Batch { int t, g, page0, sub_a, sub_b; bool some; };   // stages sub_a .. sub_b of the run are still ahead
   auto run_of = [&](int t, int g, Batch& bt) {           // the pages of (t, g) inside i0 .. i1
     const int base = base_of(t, g);
     const int sp_a = max(i0 - base, 0), sp_b = min(i1 - base, chunks_of(t)) - 1;
     int c_lo, c_hi;
     chunk_keys(t, sp_a, c_lo, c_hi);
-    bt.page0 = c_lo / AD_PAGE;
+    bt.sub_a = c_lo / KS;
+    bt.page0 = bt.sub_a / SPP;
     chunk_keys(t, sp_b, c_lo, c_hi);
-    bt.run_last = (c_hi + AD_PAGE - 1) / AD_PAGE - 1;    // below page0 when the run holds no cached key
+    bt.sub_b = (c_hi + KS - 1) / KS - 1;                 // below sub_a when the run holds no cached key
     bt.t = t;
     bt.g = g;
     bt.some = true;
   };
   auto batch_after = [&](const Batch& cur, Batch& nx) {
     nx = cur;
-    if (cur.page0 + 32 <= cur.run_last) { nx.page0 = cur.page0 + 32; return; }
+    if ((cur.page0 + 32) * SPP <= cur.sub_b) { nx.page0 = cur.page0 + 32; nx.sub_a = nx.page0 * SPP; return; }
     int t = cur.t, g = cur.g + 1;
     if (g == nkv) { g = 0; ++t; }
     if (t >= T || base_of(t, g) >= i1) { nx.some = false; return; }
@@ -256,11 +270,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   };
   auto fetch = [&](const Batch& bt) {
     const int idx = bt.page0 + lane;
-    return (bt.some && idx <= bt.run_last) ? __ldcg(block_table + (int64_t)s_seq[bt.t] * bt_stride + idx) : 0;
+    return (bt.some && bt.sub_a <= bt.sub_b && idx <= bt.sub_b / SPP)
+               ? __ldcg(block_table + (int64_t)s_seq[bt.t] * bt_stride + idx) : 0;
   };
   Batch cur_b, nxt_b;
   cur_b.some = false;
-  int cur_pages = 0, nxt_pages = 0, p_pi = 1, p_end = 0;   // pages p_pi .. p_end of the current batch are still to ask for
+  int cur_pages = 0, nxt_pages = 0, p_pi = 1, p_end = 0;   // stages p_pi .. p_end of the current batch are still to ask for
   int t0 = 0, g0 = 0, sp0 = 0;
   nxt_b.some = false;
   if (i0 < i1) {
@@ -277,19 +292,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (!nxt_b.some) return;                           // no page left for this warp
       cur_b = nxt_b;
       cur_pages = nxt_pages;
-      p_pi = cur_b.page0;
-      p_end = min(cur_b.page0 + 31, cur_b.run_last);
+      p_pi = cur_b.sub_a;
+      p_end = min((cur_b.page0 + 32) * SPP - 1, cur_b.sub_b);
       batch_after(cur_b, nxt_b);
       nxt_pages = fetch(nxt_b);
     }
-    const int pg = __shfl_sync(0xffffffffu, cur_pages, p_pi - cur_b.page0);
+    const int pg = __shfl_sync(0xffffffffu, cur_pages, p_pi / SPP - cur_b.page0);
     if (lane == 0) {
       const uint32_t s = pn % AD_STAGES;
       const uint32_t dst = ring + s * AD_STAGE_BYTES;
-      const int row = (pg * nkv + cur_b.g) * AD_PAGE;
+      const int row = (pg * nkv + cur_b.g) * AD_PAGE + (p_pi % SPP) * KS;
       ad_mbar_expect_tx(bars + s, AD_STAGE_BYTES);
-      ad_tma_2d(dst, &map_k, bars + s, 0, row);
-      ad_tma_2d(dst + AD_TILE_BYTES, &map_v, bars + s, 0, row);
+#pragma unroll
+      for (int b = 0; b < NBOX; ++b) {
+        ad_tma_2d(dst + b * BOX_BYTES, &map_k, bars + s, 64 * b, row);
+        ad_tma_2d(dst + AD_TILE_BYTES + b * BOX_BYTES, &map_v, bars + s, 64 * b, row);
+      }
     }
     ++p_pi;
     ++pn;
@@ -298,12 +316,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   for (int s = 0; s < AD_STAGES; ++s) produce();
 
   // Q^T as the right operand: column gl is query head gl of the group, zero beyond the group
-  auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[4][2]) {
+  auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[NJ][2]) {
     const unsigned* qrow = reinterpret_cast<const unsigned*>(q + (int64_t)t * q_row_stride +
-                                                             (int64_t)(g * G + gl) * AD_HD);
+                                                             (int64_t)(g * G + gl) * HD);
     const bool live = some && gl < G;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NJ; ++j) {
       qq[j][0] = live ? __ldcg(qrow + 8 * j + tl) : 0u;
       qq[j][1] = live ? __ldcg(qrow + 8 * j + tl + 4) : 0u;
     }
@@ -317,81 +335,127 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   };
 
   // ---- the position encoding, when it is this kernel's to apply -------------------------------
-  // Half-split rotary pairs (d, d + 32) with angle pos * pos_scale * inv_freq[d], as rope_kv_write does it
+  // Half-split rotary pairs (d, d + HD / 2) with angle pos * pos_scale * inv_freq[d], as rope_kv_write does it
   // (elementwise.cu).  A thread's fragment holds features 16 j + 2 tl + 8 h + e: a pair's two halves are its
-  // pieces j and j + 2.
-  auto angles = [&](int t, float (&cs)[8], float (&sn)[8]) {
+  // pieces j and j + NJ / 2.
+  // A token's HD / 2 angles are computed once, two or so per lane, and kept in the warp's table (cos, sin):
+  // the token's query heads of every kv head and its own key all turn by them.
+  float2* rot_tab = s_rot[warp];
+  int rot_t = -1;                                        // the token whose angles the table holds
+  auto angles_of = [&](int t) {
+    if (t == rot_t) return;
+    __syncwarp();                                        // the table's last readers are done
     const float p = (float)s_pos[t] * pos_scale;
-#pragma unroll
-    for (int idx = 0; idx < 8; ++idx) {
-      const int d = 16 * (idx >> 2) + 2 * tl + 8 * ((idx >> 1) & 1) + (idx & 1);
-      sincosf(p * __ldg(inv_freq + d), &sn[idx], &cs[idx]);
+    for (int d = lane; d < HD / 2; d += 32) {
+      float sn, cs;
+      sincosf(p * __ldg(inv_freq + d), &sn, &cs);
+      rot_tab[d] = make_float2(cs, sn);
     }
+    __syncwarp();
+    rot_t = t;
   };
-  auto rotate_frag = [&](uint32_t (&f)[4][2], const float (&cs)[8], const float (&sn)[8]) {
+  auto rotate_at = [&](int t, uint32_t (&f)[NJ][2]) {
+    angles_of(t);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < NJ / 2; ++j) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const uint32_t x0 = f[j][h], x1 = f[j + 2][h];
-        const int idx = j * 4 + h * 2;
+        const float4 a = *reinterpret_cast<const float4*>(rot_tab + 16 * j + 2 * tl + 8 * h);   // pairs d, d + 1
+        const uint32_t x0 = f[j][h], x1 = f[j + NJ / 2][h];
         const float a0 = __uint_as_float(x0 << 16), a1 = __uint_as_float(x1 << 16);
         const float b0 = __uint_as_float(x0 & 0xffff0000u), b1 = __uint_as_float(x1 & 0xffff0000u);
-        const float r0a = a0 * cs[idx] - a1 * sn[idx], r1a = a1 * cs[idx] + a0 * sn[idx];
-        const float r0b = b0 * cs[idx + 1] - b1 * sn[idx + 1], r1b = b1 * cs[idx + 1] + b0 * sn[idx + 1];
+        const float r0a = a0 * a.x - a1 * a.y, r1a = a1 * a.x + a0 * a.y;
+        const float r0b = b0 * a.z - b1 * a.w, r1b = b1 * a.z + b0 * a.w;
         f[j][h] = ad_pack(r0a, r0b);
-        f[j + 2][h] = ad_pack(r1a, r1b);
+        f[j + NJ / 2][h] = ad_pack(r1a, r1b);
       }
     }
   };
 
   // ---- merging the chunks of a (token, kv head): the same sums in chunk order, whoever does it --
-  auto merge = [&](int mt, int mg) {
+  // HG query heads of the group side by side, 32 / HG lanes each: the warp waits for memory once for all the
+  // chunks' maxima and sums and once per MB chunks of accumulators, however many heads the group has.
+  auto merge_heads = [&](auto hg_c, int mt, int mg, int n0) {
+    constexpr int HG = decltype(hg_c)::value;
+    constexpr int LPH = 32 / HG;                         // lanes of a head
+    constexpr int DPL = HD / LPH;                        // features of a lane: the pairs i * LPH + lih of the head
+    constexpr int F2 = DPL / 2;
+    constexpr int MB = DPL <= 4 ? 16 : 64 / DPL;         // chunks asked for at once
     float* wv = s_w[warp];
     float* lv = s_l[warp];
     const int n_rec = chunks_of(mt);
-    for (int n = 0; n < G; ++n) {
-      const int head = mg * G + n;
-      const float* base = scratch + ((int64_t)mt * nh + head) * max_splits * rec;
-      // Lanes take the chunks' maxima and sums side by side, then their accumulators sixteen
-      // chunks at a time: a few round trips to memory, however many chunks there are.
-      float M = -INFINITY;
-      for (int s2 = lane; s2 < n_rec; s2 += 32) {
-        const float ms = __ldcg(base + (int64_t)s2 * rec + AD_HD);
-        lv[s2] = __ldcg(base + (int64_t)s2 * rec + AD_HD + 1);
-        wv[s2] = ms;
-        M = fmaxf(M, ms);
-      }
-      M = warp_max(M);
-      float ll = 0.0f;
-      for (int s2 = lane; s2 < n_rec; s2 += 32) {
-        const float w = ad_exp2(wv[s2] - M);
-        wv[s2] = w;
-        ll += lv[s2] * w;
-      }
-      ll = warp_sum(ll);
-      __syncwarp();
-      float a0 = 0.0f, a1 = 0.0f;
-      for (int s0 = 0; s0 < n_rec; s0 += 16) {
-        float v0[16], v1[16];
+    const int heads = min(HG, G - n0);
+    const float* base = scratch + ((int64_t)mt * nh + mg * G + n0) * max_splits * rec;   // a head's records: max_splits of them
+    const int n_pairs = heads * n_rec;
+    for (int p = lane; p < n_pairs; p += 32) {
+      const int n = p / n_rec, s2 = p - n * n_rec;
+      const float* r = base + ((int64_t)n * max_splits + s2) * rec + HD;
+      wv[p] = __ldcg(r);
+      lv[p] = __ldcg(r + 1);
+    }
+    __syncwarp();
+    const int nn = lane / LPH, lih = lane % LPH;
+    float my_ll = 1.0f;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float* r = base + (int64_t)(s0 + u) * rec;
+    for (int n = 0; n < HG; ++n) {
+      if (n < heads) {
+        float M = -INFINITY;
+        for (int s2 = lane; s2 < n_rec; s2 += 32) M = fmaxf(M, wv[n * n_rec + s2]);
+        M = warp_max(M);
+        float ll = 0.0f;
+        for (int s2 = lane; s2 < n_rec; s2 += 32) {
+          const float w = ad_exp2(wv[n * n_rec + s2] - M);
+          wv[n * n_rec + s2] = w;
+          ll += lv[n * n_rec + s2] * w;
+        }
+        ll = warp_sum(ll);
+        if (nn == n) my_ll = ll;
+      }
+    }
+    __syncwarp();
+    if (nn < heads) {
+      const float* hb = base + (int64_t)nn * max_splits * rec;
+      const float* wn = wv + nn * n_rec;
+      float acc[DPL];
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) acc[e] = 0.0f;
+      for (int s0 = 0; s0 < n_rec; s0 += MB) {
+        float2 v[MB][F2];
+#pragma unroll
+        for (int u = 0; u < MB; ++u) {
+          const float2* r = reinterpret_cast<const float2*>(hb + (int64_t)(s0 + u) * rec);
           const bool in = s0 + u < n_rec;
-          v0[u] = in ? __ldcg(r + lane) : 0.0f;
-          v1[u] = in ? __ldcg(r + lane + 32) : 0.0f;
+#pragma unroll
+          for (int i = 0; i < F2; ++i) v[u][i] = in ? __ldcg(r + i * LPH + lih) : make_float2(0.0f, 0.0f);
         }
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const float w = s0 + u < n_rec ? wv[s0 + u] : 0.0f;
-          a0 += v0[u] * w;
-          a1 += v1[u] * w;
+        for (int u = 0; u < MB; ++u) {
+          const float w = s0 + u < n_rec ? wn[s0 + u] : 0.0f;
+#pragma unroll
+          for (int i = 0; i < F2; ++i) {
+            acc[2 * i] += v[u][i].x * w;
+            acc[2 * i + 1] += v[u][i].y * w;
+          }
         }
       }
-      __nv_bfloat16* dst = out + ((int64_t)mt * nh + head) * AD_HD;
-      dst[lane] = __float2bfloat16(a0 / ll);
-      dst[lane + 32] = __float2bfloat16(a1 / ll);
-      __syncwarp();                                      // before the next head's weights
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + ((int64_t)mt * nh + mg * G + n0 + nn) * HD);
+#pragma unroll
+      for (int i = 0; i < F2; ++i)
+        dst[i * LPH + lih] = __floats2bfloat162_rn(acc[2 * i] / my_ll, acc[2 * i + 1] / my_ll);
+    }
+    __syncwarp();                                        // before the next heads' weights
+  };
+  auto merge = [&](int mt, int mg) {
+    const int n_rec = chunks_of(mt);
+    int hg = 1;                                          // as many heads at once as the weights' table takes
+    while (hg < G && 2 * hg * n_rec <= AD_MAX_SPLITS) hg *= 2;
+    for (int n0 = 0; n0 < G; n0 += hg) {
+      switch (hg) {
+        case 1: merge_heads(std::integral_constant<int, 1>{}, mt, mg, n0); break;
+        case 2: merge_heads(std::integral_constant<int, 2>{}, mt, mg, n0); break;
+        case 4: merge_heads(std::integral_constant<int, 4>{}, mt, mg, n0); break;
+        default: merge_heads(std::integral_constant<int, 8>{}, mt, mg, n0); break;
+      }
     }
     if (lane == 0) counters[(int64_t)mt * nkv + mg] = 0;   // zero again for the next launch
   };
@@ -400,35 +464,35 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   uint32_t cn = 0;                                       // pages used
   bool ok = true;
   int t = t0, g = g0, sp = sp0;
-  uint32_t qb[4][2], qn[4][2];
+  uint32_t qb[NJ][2], qn[NJ][2];
   int nt = 0, ng = 0;
   bool nsome = false;
-  float cs[8], sn[8];
+  if (rotate && i0 < i1) angles_of(t0);                  // positions are the step's inputs
   if (write_new) pdl_wait();                             // from here on the projection's output is read
   if (i0 < i1) {
     load_q(t, g, true, qb);
     nsome = next_run(t, g, nt, ng);
     load_q(nt, ng, nsome, qn);                           // used when this warp gets to (nt, ng)
-    if (rotate) { angles(t, cs, sn); rotate_frag(qb, cs, sn); }
+    if (rotate) rotate_at(t, qb);
   }
 #pragma unroll 1
   for (int i = i0; i < i1 && ok; ++i) {
     int c_lo, c_hi;
     chunk_keys(t, sp, c_lo, c_hi);
-    const int first_page = c_lo / AD_PAGE, last_page = c_lo < c_hi ? (c_hi - 1) / AD_PAGE : first_page - 1;
+    const int first_sub = c_lo / KS, last_sub = c_lo < c_hi ? (c_hi - 1) / KS : first_sub - 1;
     // The token's own key and value: the warp with the token's last chunk takes them from the projection's
     // output (asked for now, used after the chunk's pages), rotates the key, adds the pair to the softmax as
     // one more key and writes it to the cache.
     const bool has_new = write_new && sp == chunks_of(t) - 1;
-    uint32_t kf[4][2];
-    unsigned short vf[8];
+    uint32_t kf[NJ][2];
+    unsigned short vf[2 * NJ];
     int new_page = 0;
     if (has_new) {
       const __nv_bfloat16* row = q + (int64_t)t * q_row_stride;
-      const unsigned* krow = reinterpret_cast<const unsigned*>(row + (int64_t)(nh + g) * AD_HD);
-      const unsigned short* vrow = reinterpret_cast<const unsigned short*>(row + (int64_t)(nh + nkv + g) * AD_HD);
+      const unsigned* krow = reinterpret_cast<const unsigned*>(row + (int64_t)(nh + g) * HD);
+      const unsigned short* vrow = reinterpret_cast<const unsigned short*>(row + (int64_t)(nh + nkv + g) * HD);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         kf[j][0] = __ldcg(krow + 8 * j + tl);
         kf[j][1] = __ldcg(krow + 8 * j + tl + 4);
         vf[2 * j] = __ldcg(vrow + 16 * j + gl);
@@ -437,34 +501,40 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       new_page = __ldcg(block_table + (int64_t)s_seq[t] * bt_stride + s_pos[t] / AD_PAGE);
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[4][4];
+    float o[NJ][4];
 #pragma unroll
-    for (int a = 0; a < 4; ++a) {
+    for (int a = 0; a < NJ; ++a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[a][e] = 0.0f;
     }
 #pragma unroll 1
-    for (int pi = first_page; pi <= last_page; ++pi) {
+    for (int pi = first_sub; pi <= last_sub; ++pi) {
       const uint32_t st = cn % AD_STAGES;
       if (!ad_mbar_wait(bars + st, (cn / AD_STAGES) & 1)) { ok = false; break; }
       const uint32_t kb = ring + st * AD_STAGE_BYTES;
       // S^T = K Q^T: s[a] holds keys 16 a + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
-      float s[4][4];
+      float s[MT][4];
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
+      for (int a = 0; a < MT; ++a) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[a][e] = 0.0f;
+        float s_hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};         // features 64 .. of a head of 128: a chain of its own
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NJ; ++j) {                     // features 16 j ..: box j / 4, its piece j % 4
           uint32_t f[4];
-          ad_ldsm(f, kb + a * 2048 + k_row + k_col[j]);
-          ad_mma(s[a], f, qb[j][0], qb[j][1]);
+          ad_ldsm(f, kb + (j >> 2) * BOX_BYTES + a * 2048 + k_row + k_col[j & 3]);
+          if (j < 4) ad_mma(s[a], f, qb[j][0], qb[j][1]);
+          else ad_mma(s_hi, f, qb[j][0], qb[j][1]);
+        }
+        if (NJ > 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[a][e] += s_hi[e];
         }
       }
-      const int key0 = pi * AD_PAGE;
-      if (key0 < c_lo || key0 + AD_PAGE > c_hi) {
+      const int key0 = pi * KS;
+      if (key0 < c_lo || key0 + KS > c_hi) {
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
+        for (int a = 0; a < MT; ++a) {
           const int ka = key0 + 16 * a + gl, kb2 = ka + 8;
           const bool da = (ka < c_lo) | (ka >= c_hi), db = (kb2 < c_lo) | (kb2 >= c_hi);
           s[a][0] = da ? -INFINITY : s[a][0];
@@ -476,8 +546,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       float mx[2];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        mx[c] = fmaxf(fmaxf(fmaxf(s[0][c], s[0][c + 2]), fmaxf(s[1][c], s[1][c + 2])),
-                      fmaxf(fmaxf(s[2][c], s[2][c + 2]), fmaxf(s[3][c], s[3][c + 2])));
+        mx[c] = fmaxf(s[0][c], s[0][c + 2]);
+#pragma unroll
+        for (int a = 1; a < MT; ++a) mx[c] = fmaxf(mx[c], fmaxf(s[a][c], s[a][c + 2]));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
@@ -490,9 +561,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         m[c] = mn;
       }
       // P^T as the right operand of the second product, by transposing 8x8 pieces across the warp
-      uint32_t pb[4][2];
+      uint32_t pb[MT][2];
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
+      for (int a = 0; a < MT; ++a) {
         const float p0 = ad_exp2(fmaf(s[a][0], scale_log2, -m[0]));
         const float p1 = ad_exp2(fmaf(s[a][1], scale_log2, -m[1]));
         const float p2 = ad_exp2(fmaf(s[a][2], scale_log2, -m[0]));
@@ -503,7 +574,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         pb[a][1] = ad_transpose(ad_pack(p2, p3));
       }
 #pragma unroll
-      for (int d = 0; d < 4; ++d) {
+      for (int d = 0; d < NJ; ++d) {
         o[d][0] *= corr[0];
         o[d][1] *= corr[1];
         o[d][2] *= corr[0];
@@ -511,41 +582,41 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       }
       // O^T += V^T P^T: o[d] holds features 16 d + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
+      for (int a = 0; a < MT; ++a) {
 #pragma unroll
-        for (int d = 0; d < 4; ++d) {
+        for (int d = 0; d < NJ; ++d) {
           uint32_t f[4];
-          ad_ldsm_t(f, kb + a * 2048 + v_row + v_col[d]);
+          ad_ldsm_t(f, kb + (d >> 2) * BOX_BYTES + a * 2048 + v_row + v_col[d & 3]);
           ad_mma(o[d], f, pb[a][0], pb[a][1]);
         }
       }
       __syncwarp();                                      // every lane has read the stage
       ++cn;
-      produce();                                         // refill it with the page AD_STAGES ahead
+      produce();                                         // refill it with the stage AD_STAGES ahead
     }
     if (!ok) break;
     if (has_new) {
-      if (rotate) rotate_frag(kf, cs, sn);
+      if (rotate) rotate_at(t, kf);
       // to the cache, for the steps to come: the key from the lanes of query column 0, the value as it is
-      const int64_t at = (((int64_t)new_page * nkv + g) * AD_PAGE + (s_pos[t] % AD_PAGE)) * AD_HD;
+      const int64_t at = (((int64_t)new_page * nkv + g) * AD_PAGE + (s_pos[t] % AD_PAGE)) * HD;
       if (new_page >= 0) {
         if (gl == 0) {
           unsigned* kdst = reinterpret_cast<unsigned*>(k_pool + at);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < NJ; ++j) {
             kdst[8 * j + tl] = kf[j][0];
             kdst[8 * j + tl + 4] = kf[j][1];
           }
         }
-        if (lane < 8) {
-          const uint4* vsrc = reinterpret_cast<const uint4*>(q + (int64_t)t * q_row_stride + (int64_t)(nh + nkv + g) * AD_HD);
+        if (lane < HD / 8) {
+          const uint4* vsrc = reinterpret_cast<const uint4*>(q + (int64_t)t * q_row_stride + (int64_t)(nh + nkv + g) * HD);
           reinterpret_cast<uint4*>(v_pool + at)[lane] = __ldcg(vsrc + lane);
         }
       }
       // its score against this lane group's query (column gl), then to the lanes that hold that column's state
       float dot = 0.0f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < NJ; ++j) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           dot = fmaf(__uint_as_float(qb[j][h] << 16), __uint_as_float(kf[j][h] << 16), dot);
@@ -564,7 +635,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         m[c] = mn;
         l[c] = l[c] * corr + (gl == 0 ? pr : 0.0f);          // the sum over lane groups below counts it once
 #pragma unroll
-        for (int d = 0; d < 4; ++d) {
+        for (int d = 0; d < NJ; ++d) {
           o[d][c] = o[d][c] * corr + pr * __uint_as_float((uint32_t)vf[2 * d] << 16);
           o[d][c + 2] = o[d][c + 2] * corr + pr * __uint_as_float((uint32_t)vf[2 * d + 1] << 16);
         }
@@ -584,21 +655,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (n >= G) continue;
       const int head = g * G + n;
       if (n_rec == 1) {
-        __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * AD_HD;
+        __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * HD;
         const float inv = 1.0f / l[c];
 #pragma unroll
-        for (int d = 0; d < 4; ++d) {
+        for (int d = 0; d < NJ; ++d) {
           dst[16 * d + gl] = __float2bfloat16(o[d][c] * inv);
           dst[16 * d + gl + 8] = __float2bfloat16(o[d][c + 2] * inv);
         }
       } else {
         float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
 #pragma unroll
-        for (int d = 0; d < 4; ++d) {
+        for (int d = 0; d < NJ; ++d) {
           sc[16 * d + gl] = o[d][c];
           sc[16 * d + gl + 8] = o[d][c + 2];
         }
-        if (gl == 0) { sc[AD_HD] = m[c]; sc[AD_HD + 1] = l[c]; }
+        if (gl == 0) { sc[HD] = m[c]; sc[HD + 1] = l[c]; }
       }
     }
     // on to the next chunk; a new (token, kv head) brings its queries, asked for a run ago
@@ -607,8 +678,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       t = nt;
       g = ng;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { qb[j][0] = qn[j][0]; qb[j][1] = qn[j][1]; }
-      if (rotate && i + 1 < i1) { angles(t, cs, sn); rotate_frag(qb, cs, sn); }
+      for (int j = 0; j < NJ; ++j) { qb[j][0] = qn[j][0]; qb[j][1] = qn[j][1]; }
+      if (rotate && i + 1 < i1) rotate_at(t, qb);
       if (nsome) {
         nsome = next_run(t, g, nt, ng);
         load_q(nt, ng, nsome, qn);
@@ -664,13 +735,13 @@ static AdEncodeFn ad_encode_fn() {
   }();
   return fn;
 }
-// [rows, 64] bfloat16, rows packed; boxes of one page (64 rows), 128B swizzle.
-static int ad_make_map(CUtensorMap* map, const void* ptr, int64_t rows) {
+// [rows, hd] bfloat16, rows packed; boxes of 64 features x box_rows rows, 128B swizzle.
+static int ad_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int hd, int box_rows) {
   AdEncodeFn fn = ad_encode_fn();
   if (!fn) { set_error("attn_decode: the driver has no cuTensorMapEncodeTiled"); return ERR_UNSUPPORTED; }
-  const cuuint64_t dims[2] = {(cuuint64_t)AD_HD, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)AD_HD * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)AD_HD, (cuuint32_t)AD_PAGE};
+  const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -685,7 +756,7 @@ using namespace exl3;
 
 extern "C" int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys,
                                           int max_splits) {
-  return dtype == DT_BF16 && hd == AD_HD && page == AD_PAGE && T >= 0 && T <= AD_MAX_TOKENS && nkv >= 1 &&
+  return dtype == DT_BF16 && (hd == 64 || hd == 128) && page == AD_PAGE && T >= 0 && T <= AD_MAX_TOKENS && nkv >= 1 &&
          nh % nkv == 0 && nh / nkv <= AD_MAX_GROUP && split_keys > 0 && split_keys % AD_PAGE == 0 &&
          max_splits >= 1 && max_splits <= AD_MAX_SPLITS && (max_splits == 1 || (int64_t)T * nkv <= AD_COUNTER_SLOTS);
 }
@@ -700,8 +771,8 @@ extern "C" int exl3_attn_decode_status() {
 // Same arguments and the same scratch layout as exl3_attn_tokens; n_pool_rows = pages * kv_heads * 64.
 // With write_new, q is the fused q|k|v output of the projection and every token is its sequence's only new one:
 // the kernel takes the token's key and value from there, adds them to its softmax and writes them to the cache
-// (which holds the positions before it).  With rot = 64 it also applies the half-split rotary encoding
-// (angle pos * pos_scale * inv_freq[d], 32 frequencies) to the queries and the new key; rot = 0: none.
+// (which holds the positions before it).  With rot = hd it also applies the half-split rotary encoding
+// (angle pos * pos_scale * inv_freq[d], hd / 2 frequencies) to the queries and the new key; rot = 0: none.
 extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
                                 int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
                                 const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
@@ -711,14 +782,14 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   if (T == 0) return 0;
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
       !exl3_attn_decode_supported(DT_BF16, T, nh, nkv, hd, page, split_keys, max_splits)) {
-    set_error("attn_decode: needs bfloat16, head_dim 64, pages of 64, at most %d tokens, %d query heads per kv "
+    set_error("attn_decode: needs bfloat16, head_dim 64 or 128, pages of 64, at most %d tokens, %d query heads per kv "
               "head and %d chunks of whole pages; got T=%d heads=%d kv_heads=%d head_dim=%d page=%d window=%d "
               "split_keys=%d max_splits=%d", AD_MAX_TOKENS, AD_MAX_GROUP, AD_MAX_SPLITS, T, nh, nkv, hd, page,
               window, split_keys, max_splits);
     return ERR_UNSUPPORTED;
   }
-  if ((rot != 0 && rot != AD_HD) || (rot != 0 && inv_freq == nullptr)) {
-    set_error("attn_decode: the rotary encoding is applied to all %d features of a head or to none, got %d", AD_HD, rot);
+  if ((rot != 0 && rot != hd) || (rot != 0 && inv_freq == nullptr)) {
+    set_error("attn_decode: the rotary encoding is applied to all %d features of a head or to none, got %d", hd, rot);
     return ERR_UNSUPPORTED;
   }
   if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out) || q_row_stride % 8 != 0) {
@@ -732,27 +803,34 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   }
   static int sms = 0;
   if (!sms) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e != cudaSuccess) { set_error("attn_decode: cannot get %u bytes of shared memory: %s", AD_SMEM, cudaGetErrorString(e)); return (int)e; }
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 1;
   }
+  // a stage is a page (heads of 64) or half a page (heads of 128): the copy's box has as many rows
+  const int box_rows = hd == 64 ? 64 : 32;
   CUtensorMap map_k, map_v;
-  int rc = ad_make_map(&map_k, k_pool, n_pool_rows);
+  int rc = ad_make_map(&map_k, k_pool, n_pool_rows, hd, box_rows);
   if (rc) return rc;
-  rc = ad_make_map(&map_v, v_pool, n_pool_rows);
+  rc = ad_make_map(&map_v, v_pool, n_pool_rows, hd, box_rows);
   if (rc) return rc;
   // one block per SM as soon as there is a chunk for each: the warps' equal shares then spread few chunks over all
   // SMs (and their memory pipes) instead of filling the warps of half of them
   const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * nkv * max_splits);
   int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
-  launch_pdl(attn_decode_kernel, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,
-             static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,
-             bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,
-             max_splits, records, counters, inv_freq, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,
-             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
+#define EXL3_AD_LAUNCH(HD_)                                                                                       \
+  launch_pdl(attn_decode_kernel<HD_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
+             static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
+             bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,           \
+             max_splits, records, counters, inv_freq, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
+             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool))
+  if (hd == 64) EXL3_AD_LAUNCH(64); else EXL3_AD_LAUNCH(128);
+#undef EXL3_AD_LAUNCH
   return launch_status("attn_decode");
 }

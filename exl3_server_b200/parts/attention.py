@@ -13,7 +13,7 @@ The three input projections are one fused matrix, so a step reads ``r`` once.
 
 Which kernels run: prompts in bfloat16 with heads of 64 go through the tcgen05 attention (heads of 128: the
 mma.sync one), after the position part's own step.  Steps in which every sequence brings one token (decode), in
-bfloat16 with heads of 64, are one kernel: it rotates the queries and the token's own key, takes that key and
+bfloat16 with heads of 64 or 128, are one kernel: it rotates the queries and the token's own key, takes that key and
 value from the projection's output, adds them to the softmax and writes them to the cache (``_decode_fused``;
 the position part must offer ``fused_rotation``).  Everything else (float32, other head sizes) takes the
 position step and the CUDA-core attention kernel.
@@ -95,7 +95,7 @@ class Attention:
         return self.o(out, then=then)
 
     def _decode_fused(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
-        """One token per sequence, bfloat16, heads of 64: the decode kernel rotates the queries and the new key
+        """One token per sequence, bfloat16, heads of 64 or 128: the decode kernel rotates the queries and the new key
         itself, takes the token's own key and value from ``qkv`` and writes them to the cache, so the position
         step is no kernel of its own.  False when the step, the sizes or the position part do not allow it."""
         s = self.spec
@@ -140,7 +140,7 @@ class Attention:
         split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device) if qkv.dtype == torch.bfloat16 else 0
         n = self._chunks(batch.max_kv_len, split) if split else 0
         if split and K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
-            # decoded tokens, heads of 64: pages by TMA, both products on the tensor cores, a warp per chunk
+            # decoded tokens, heads of 64 or 128: pages by TMA, both products on the tensor cores, a warp per chunk
             scratch = None
             if n > 1:
                 scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
@@ -164,14 +164,18 @@ class Attention:
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device) -> int:
-        """Keys per chunk for the tensor-core decode kernel: about two chunks per SM's worth of warps, in whole
-        pages, 1 to 32 of them.  Every chunk costs its warp a record and a ticket, so few long chunks beat many
+        """Keys per chunk for the tensor-core decode kernel: about two chunks per SM, in whole pages, 1 to 32 of
+        them.  Every chunk costs its warp a record and a ticket, so few long chunks beat many
         short ones once every warp has work (measured at batch 1 to 64).  The choice depends on the step's
         size, not on a token's position: results differ between batch sizes by rounding."""
         keys = min(max_kv_len, self.spec.window) if self.spec.window > 0 else max_kv_len
         pages = T * self.spec.kv_heads * ((keys + page - 1) // page)
-        per = max(1.0, pages / (2.0 * K.sm_count(device)))
-        per = min(32, 1 << int(round(math.log2(per))))
+        # counted in 16 KB of keys and values (a page of a head of 64), which cost a warp about the same time
+        # whatever the head's size; at most 32 pages
+        wide = max(1, self.spec.head_dim // 64)
+        per = max(1.0, pages * wide / (2.0 * K.sm_count(device)))
+        per = min(32 * wide, 1 << int(round(math.log2(per))))
+        per = max(1, per // wide)
         return page * per
 
     def _chunks(self, max_kv_len: int, split: int) -> int:

@@ -342,12 +342,12 @@ def test_attn_tokens_finds_one_far_key_among_many():
     assert float((out.cpu() - case.v[0][far].reshape(1, -1)).abs().max()) > 0.1
 
 
-@pytest.mark.parametrize("nh,nkv", [(3, 3), (4, 2), (8, 1), (16, 2), (5, 5)])
+@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 1, 64), (16, 2, 64), (5, 5, 64), (6, 2, 64),
+                                       (5, 1, 64), (3, 3, 128), (8, 1, 128), (8, 2, 128), (6, 1, 128), (9, 3, 128)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("split", [64, 256])
-def test_attn_decode(nh, nkv, window, split):
+def test_attn_decode(nh, nkv, hd, window, split):
     # single tokens and short prompts in one call, positions at both sides of page and chunk edges
-    hd = 64
     lens = [300, 64, 1, 700, 65, 256, 257, 128, 513]
     new = [1, 1, 1, 3, 1, 1, 1, 2, 1]
     case = PagedCase(lens=lens, new=new, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split)
@@ -368,10 +368,11 @@ def test_attn_decode(nh, nkv, window, split):
     assert K().attn_decode_status() == 0
 
 
-def test_attn_decode_many_items_per_warp():
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attn_decode_many_items_per_warp(hd):
     # more work items than the grid has warps: every warp's ring of pages runs across the ends of items,
     # among them empty chunks of the shorter sequences
-    nh, nkv, hd = 8, 4, 64
+    nh, nkv = 8, 4
     g = torch.Generator().manual_seed(5)
     lens = [int(x) for x in torch.randint(1, 1500, (48,), generator=g)]
     case = PagedCase(lens=lens, new=[1] * len(lens), nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=11)
@@ -390,6 +391,26 @@ def test_attn_decode_many_items_per_warp():
     K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
                     nh, nkv, hd, 64, 0, 0.125, 2048, n1, None)
     close(out, case.reference(0, 0.125), 1e-2, "attn_decode, one chunk")
+    assert K().attn_decode_status() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 1, 64), (14, 2, 128), (4, 1, 128)])
+def test_attn_decode_merges_many_chunks_of_grouped_heads(nh, nkv, hd):
+    # so many chunks for each token that the heads of a group are merged in several passes
+    lens = [2100, 1, 2049, 640]
+    case = PagedCase(lens=lens, new=[1] * len(lens), nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=21)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    out = torch.empty_like(q)
+    split = 64
+    n = (max(lens) + split - 1) // split
+    assert (nh // nkv) * n > 256 or nh // nkv < 8
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    for _ in range(2):
+        out.fill_(7.0)
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, 0, 0.125, split, n, scratch)
+        close(out, case.reference(0, 0.125), 1e-2, "attn_decode, many chunks of grouped heads")
     assert K().attn_decode_status() == 0
 
 
@@ -416,14 +437,14 @@ def test_attn_decode_finds_one_far_key_among_many():
     assert float((out.cpu().float() - case.v[0][far].reshape(1, -1).float()).abs().max()) > 0.1
 
 
-@pytest.mark.parametrize("nh,nkv", [(3, 3), (8, 1), (16, 2)])
+@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (8, 1, 64), (16, 2, 64), (4, 2, 128), (8, 1, 128)])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("rot", [64, 0])
+@pytest.mark.parametrize("rotary", [True, False])
 @pytest.mark.parametrize("split", [64, 256, 2048])
-def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, window, rot, split):
+def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, hd, window, rotary, split):
     """The kernel takes each token's own key and value from the projection's output: the cache holds junk at
     the token's place before the call and the rotated key and the value after it."""
-    hd = 64
+    rot = hd if rotary else 0
     lens = [300, 64, 1, 700, 65, 256, 257, 128, 513, 2]         # last positions at both sides of page and chunk edges
     B = len(lens)
     case = PagedCase(lens=lens, new=[1] * B, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split + rot)
@@ -472,7 +493,8 @@ def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, window, rot, spli
 def test_attn_decode_is_refused_for_other_shapes():
     assert K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 16)
     assert not K().attn_decode_supported(torch.float32, 8, 4, 4, 64, 64, 256, 16)
-    assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 128, 64, 256, 16)
+    assert K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 128, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 96, 64, 256, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 8, 16, 1, 64, 64, 256, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 100, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 5000, 4, 4, 64, 64, 256, 16)

@@ -282,7 +282,7 @@ def toy_plain_logits(w: Dict[str, torch.Tensor], cfg: ToyConfig, ids: List[int])
     return P.linear(P.rms_norm(h, w["toy.norm.weight"], 1e-5), w["toy.emb"])
 
 
-@pytest.mark.parametrize("dtype,head_dim", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
+@pytest.mark.parametrize("dtype,head_dim", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64), ("bfloat16", 128)])
 def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, dtype, head_dim):
     from exl3_server_b200 import Engine
     from exl3_server_b200.config import register_architecture, unregister_architecture
@@ -290,7 +290,7 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(tmp_path, d
     from exl3_server_b200.parts import register_mixer, unregister
     from exl3_server_b200.weights import write_safetensors
     from exl3_server_b200.weights.random_init import random_tensors
-    # heads of 64 in bfloat16: the last schedule entry, which reads another entry's keys and values, then goes
+    # heads of 64 or 128 in bfloat16: the last schedule entry, which reads another entry's keys and values, then goes
     # through the tensor-core decode kernel without a cache write of its own
     cfg = ToyConfig(width=32, vocab=50, decay=0.8, layout=["ema", "attn", "ema", "attn"], head_dim=head_dim)
     register_mixer("test_ema", EmaMixer)
