@@ -54,16 +54,9 @@ int exl3_attn_tokens(const void* q, int64_t q_row_stride, void* out, int dtype, 
                      cudaStream_t stream);
 size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
 
-// Whole prompts on the tensor cores (bfloat16, head_dim 64 or 128, pages of 64); see attention_prefill.cu.
-int exl3_attn_prefill_supported(int dtype, int hd, int page);
-int exl3_attn_prefill_tile(int hd);
-int exl3_attn_prefill(const void* q, int64_t q_row_stride, void* out, int dtype, const void* k_pool,
-                      const void* v_pool, const int* block_table, int bt_stride, const int* row_start,
-                      const int* row_pos0, const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv,
-                      int hd, int page, int window, float scale, cudaStream_t stream);
-
 size_t exl3_argmax_scratch_bytes(int R, int V);
-// The same on tcgen05 tensor cores with TMA loads from the paged cache (heads of 64, tiles of 128 queries).
+// Whole prompts on tcgen05 tensor cores with TMA loads from the paged cache (bfloat16, heads of 64 or 128, pages
+// of 64, tiles of 128 queries); see attention_prefill_tc.cu.
 int exl3_attn_prefill_tc_supported(int dtype, int hd, int page);
 int exl3_attn_prefill_tc_status();
 int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,

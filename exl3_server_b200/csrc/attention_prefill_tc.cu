@@ -1,5 +1,5 @@
 // Causal grouped-query attention of whole prompts over the paged cache on the
-// 5th-generation tensor cores (heads of 64, bfloat16, pages of 64 keys).
+// 5th-generation tensor cores (heads of 64 or 128, bfloat16, pages of 64 keys).
 //
 // Same mathematics as attention_prefill.cu and attention_simt.cu (the
 // reference's masked scaled-dot-product attention, src/model.cpp:539-548,
@@ -9,7 +9,9 @@
 //   warp 4     issues everything asynchronous: TMA copies of the Q tile and of
 //              K and V pages (straight from the paged cache, 128B-swizzled),
 //              S = Q K^T and O += P V as tcgen05.mma with accumulators in tensor
-//              memory (two S buffers of 64 columns, O in 64, two P buffers of 32)
+//              memory (two S buffers of 64 columns, O in head_dim columns, two P buffers
+//              of 32); a head of 128 is two boxes of 64 features for every copy, two
+//              groups of four instructions for S and two halves of O
 //   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It reads its row
 //              of S with tcgen05.ld (no shuffles: the whole row is in its
 //              registers), masks, takes 2^(s * scale - m) with one multiply-add
@@ -31,12 +33,15 @@
 
 namespace exl3 {
 
-constexpr int FA_BQ = 128, FA_BK = 64, FA_HD = 64;
+constexpr int FA_BQ = 128, FA_BK = 64;
 constexpr int FA_THREADS = 160;
-constexpr int FA_TMEM_COLS = 256;                 // S0 (64) | S1 (64) | O (64) | P0 (32) | P1 (32)
-constexpr uint32_t FA_Q_BYTES = FA_BQ * FA_HD * 2, FA_KV_BYTES = FA_BK * FA_HD * 2;
 constexpr int FA_KV_STAGES = 5;
-constexpr uint32_t FA_SMEM = FA_Q_BYTES + 2 * FA_KV_STAGES * FA_KV_BYTES + 1024 + 256;
+// Tensor memory columns: S0 (64) | S1 (64) | O (head_dim) | P0 (32) | P1 (32); an allocation is a power of two.
+__host__ __device__ constexpr int fa_tmem_cols(int hd) { return hd == 64 ? 256 : 512; }
+__host__ __device__ constexpr uint32_t fa_q_bytes(int hd) { return FA_BQ * hd * 2; }
+__host__ __device__ constexpr uint32_t fa_kv_bytes(int hd) { return FA_BK * hd * 2; }
+__host__ __device__ constexpr uint32_t fa_smem(int hd) { return fa_q_bytes(hd) + 2 * FA_KV_STAGES * fa_kv_bytes(hd) + 1024 + 256; }
+constexpr uint32_t FA_QBOX_BYTES = FA_BQ * 128, FA_KVBOX_BYTES = FA_BK * 128;   // a box of 64 features
 constexpr uint32_t FA_WAIT_LIMIT = 1u << 24;   // polls of a few tens of cycles: a fraction of a second
 constexpr float FA_RESCALE_STEP = 8.0f;           // in base-2 units
 
@@ -134,7 +139,8 @@ __device__ inline uint32_t fa_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(FA_THREADS, 2)
+template <int FA_HD>
+__global__ void __launch_bounds__(FA_THREADS, FA_HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
@@ -142,9 +148,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* sQ = base;                                  // [128][64] bf16
-  unsigned char* sK = sQ + FA_Q_BYTES;                       // [stages][64][64]
-  unsigned char* sV = sK + FA_KV_STAGES * FA_KV_BYTES;       // [stages][64][64]
+  constexpr int NB = FA_HD / 64;                             // boxes of 64 features (128-byte lines) in a head
+  constexpr uint32_t FA_Q_BYTES = fa_q_bytes(FA_HD), FA_KV_BYTES = fa_kv_bytes(FA_HD);
+  constexpr int FA_TMEM_COLS = fa_tmem_cols(FA_HD);
+  unsigned char* sQ = base;                                  // [boxes][128][64] bf16
+  unsigned char* sK = sQ + FA_Q_BYTES;                       // [stages][boxes][64][64]
+  unsigned char* sV = sK + FA_KV_STAGES * FA_KV_BYTES;       // [stages][boxes][64][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + FA_KV_STAGES * FA_KV_BYTES);
   uint64_t* q_full = bars;                        // Q tile landed
   uint64_t* kv_full = bars + 1;                   // [stages] K and V page landed
@@ -192,31 +201,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   fa_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 128;                  // columns: S0 0..63, S1 64..127, O 128..191
-  const uint32_t tmem_p = tmem_base + 192;                  // P0 192..223, P1 224..255 (two bfloat16 per column)
+  const uint32_t tmem_o = tmem_base + 128;                  // columns: S0 0..63, S1 64..127, O from 128
+  const uint32_t tmem_p = tmem_base + 128 + FA_HD;          // P0, then P1: 32 columns each (two bfloat16 per column)
   bool ok = true;
 
   if (warp == 4) {
     // ---- issuer: TMA and MMA -----------------------------------------------------------
     if (lane == 0) {
       fa_mbar_expect_tx(q_full, FA_Q_BYTES);
-      fa_tma_2d(sQ, &map_q, q_full, head * FA_HD, row_start[b] + q0);
+#pragma unroll
+      for (int x = 0; x < NB; ++x)
+        fa_tma_2d(sQ + x * FA_QBOX_BYTES, &map_q, q_full, head * FA_HD + 64 * x, row_start[b] + q0);
     }
     auto load_kv = [&](int j) {                             // page j of this block's walk -> stage j % 3
       const int st = j % FA_KV_STAGES;
       const int pg = bt[page_lo + j];
       if (lane == 0) {
         fa_mbar_expect_tx(kv_full + st, 2 * FA_KV_BYTES);
-        fa_tma_2d(sK + st * FA_KV_BYTES, &map_k, kv_full + st, 0, (pg * nkv + g) * FA_BK);
-        fa_tma_2d(sV + st * FA_KV_BYTES, &map_v, kv_full + st, 0, (pg * nkv + g) * FA_BK);
+#pragma unroll
+        for (int x = 0; x < NB; ++x) {
+          fa_tma_2d(sK + st * FA_KV_BYTES + x * FA_KVBOX_BYTES, &map_k, kv_full + st, 64 * x, (pg * nkv + g) * FA_BK);
+          fa_tma_2d(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES, &map_v, kv_full + st, 64 * x, (pg * nkv + g) * FA_BK);
+        }
       }
     };
     auto issue_s = [&](int j) {                             // S[j & 1] = Q K_j^T
       const int sb = j & 1, st = j % FA_KV_STAGES;
       if (lane == 0) {
-        const uint64_t da = fa_desc(fa_smem_u32(sQ)), db = fa_desc(fa_smem_u32(sK + st * FA_KV_BYTES));
 #pragma unroll
-        for (int k = 0; k < FA_HD / 16; ++k) fa_umma(tmem_base + sb * 64, da + 2 * k, db + 2 * k, FA_IDESC_S, k > 0);
+        for (int x = 0; x < NB; ++x) {                       // 64 features of the sum at a time
+          const uint64_t da = fa_desc(fa_smem_u32(sQ + x * FA_QBOX_BYTES));
+          const uint64_t db = fa_desc(fa_smem_u32(sK + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) fa_umma(tmem_base + sb * 64, da + 2 * k, db + 2 * k, FA_IDESC_S, (x | k) > 0);
+        }
         fa_commit(s_full + sb);
       }
       __syncwarp();
@@ -240,10 +258,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fa_fence_after();
       if (lane == 0) {
         const int st = j % FA_KV_STAGES;
-        const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES));
 #pragma unroll
-        for (int k = 0; k < FA_BK / 16; ++k)                // 16 keys: 8 columns of P, 16 rows of V
-          fa_umma_ts(tmem_o, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        for (int x = 0; x < NB; ++x) {                       // 64 features of O at a time
+          const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
+#pragma unroll
+          for (int k = 0; k < FA_BK / 16; ++k)              // 16 keys: 8 columns of P, 16 rows of V
+            fa_umma_ts(tmem_o + 64 * x, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        }
         fa_commit(pv_done + sb);
         fa_commit(kv_free + st);
       }
@@ -312,16 +333,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // every earlier product must have landed in O before it is rewritten
           if (!fa_mbar_wait(pv_done + (st ^ 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
           fa_fence_after();
-          uint32_t o[2][32];
-          fa_ld32(tmem_o + lane_addr, o[0]);
-          fa_ld32(tmem_o + lane_addr + 32, o[1]);
-          fa_wait_ld();
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+          for (int h2 = 0; h2 < FA_HD / 64; ++h2) {          // 64 columns at a time
+            uint32_t o[2][32];
+            fa_ld32(tmem_o + lane_addr + 64 * h2, o[0]);
+            fa_ld32(tmem_o + lane_addr + 64 * h2 + 32, o[1]);
+            fa_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o[h][c] = __float_as_uint(__uint_as_float(o[h][c]) * corr);
-          fa_st32(tmem_o + lane_addr, o[0]);
-          fa_st32(tmem_o + lane_addr + 32, o[1]);
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[h][c] = __float_as_uint(__uint_as_float(o[h][c]) * corr);
+            fa_st32(tmem_o + lane_addr + 64 * h2, o[0]);
+            fa_st32(tmem_o + lane_addr + 64 * h2 + 32, o[1]);
+          }
           fa_wait_st();
           fa_fence_before();
         }
@@ -353,22 +377,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = fa_mbar_wait(pv_done + (jl & 1), (jl >> 1) & 1);
       if (ok) {
         fa_fence_after();
-        uint32_t o[2][32];
-        fa_ld32(tmem_o + lane_addr, o[0]);
-        fa_ld32(tmem_o + lane_addr + 32, o[1]);
-        fa_wait_ld();
-        if (r < rows) {
-          const float inv = 1.0f / l_run;
-          __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * FA_HD;
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * FA_HD;
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            uint4 w;
-            const int c = ch * 8;
-            w.x = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 0]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
-            w.y = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
-            w.z = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
-            w.w = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c) = w;
+        for (int h2 = 0; h2 < FA_HD / 64; ++h2) {            // 64 columns at a time (every thread reads: the load is the warp's)
+          uint32_t o[2][32];
+          fa_ld32(tmem_o + lane_addr + 64 * h2, o[0]);
+          fa_ld32(tmem_o + lane_addr + 64 * h2 + 32, o[1]);
+          fa_wait_ld();
+          if (r < rows) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              uint4 w;
+              const int c = ch * 8;
+              w.x = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 0]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
+              w.y = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
+              w.z = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
+              w.w = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 64 * h2 + c) = w;
+            }
           }
         }
       }
@@ -419,7 +446,7 @@ static int fa_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t 
 using namespace exl3;
 
 extern "C" int exl3_attn_prefill_tc_supported(int dtype, int hd, int page) {
-  return dtype == DT_BF16 && hd == FA_HD && page == FA_BK;
+  return dtype == DT_BF16 && (hd == 64 || hd == 128) && page == FA_BK;
 }
 extern "C" int exl3_attn_prefill_tc_status() {
   int v = 0;
@@ -437,7 +464,7 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
                                     float scale, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   if (!exl3_attn_prefill_tc_supported(DT_BF16, hd, page)) {
-    set_error("attn_prefill_tc: needs bfloat16, head_dim 64 and pages of 64, got head_dim %d page %d", hd, page);
+    set_error("attn_prefill_tc: needs bfloat16, head_dim 64 or 128 and pages of 64, got head_dim %d page %d", hd, page);
     return ERR_UNSUPPORTED;
   }
   if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || q_row_stride % 8 != 0) {
@@ -450,8 +477,10 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM);
-    if (e != cudaSuccess) { set_error("attn_prefill_tc: cannot get %u bytes of shared memory: %s", FA_SMEM, cudaGetErrorString(e)); return (int)e; }
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem(64));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem(128));
+    if (e != cudaSuccess) { set_error("attn_prefill_tc: cannot get %u bytes of shared memory: %s", fa_smem(128), cudaGetErrorString(e)); return (int)e; }
     configured = true;
   }
   CUtensorMap map_q, map_k, map_v;
@@ -462,8 +491,13 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   rc = fa_make_map(&map_v, v_pool, n_pool_rows, hd, hd, FA_BK);
   if (rc) return rc;
   dim3 grid(nh, n_tiles);
-  attn_prefill_tc_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(
-      map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
-      tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+  if (hd == 64)
+    attn_prefill_tc_kernel<64><<<grid, FA_THREADS, fa_smem(64), stream>>>(
+        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
+        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+  else
+    attn_prefill_tc_kernel<128><<<grid, FA_THREADS, fa_smem(128), stream>>>(
+        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
+        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
   return launch_status("attn_prefill_tc");
 }

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 
-QUERY_TILES = (64, 128)     # queries per block of the tensor-core prefill attention, by head size
+QUERY_TILES = (128,)        # queries per block of the tensor-core prefill attention
 
 
 class Workspace:
@@ -51,7 +51,7 @@ class StepBatch:
     max_kv_len: int                   # longest sequence after this step
     max_new: int                      # most tokens any row brings
     workspace: Workspace
-    # per tile size (64, 128 queries): (int32 [tiles] batch row, int32 [tiles] first new token, count)
+    # per tile size (128 queries): (int32 [tiles] batch row, int32 [tiles] first new token, count)
     tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     host_slots: List[int] = field(default_factory=list)
     host_new: List[int] = field(default_factory=list)

@@ -281,30 +281,6 @@ def attn_tokens(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     return out
 
 
-def attn_prefill_supported(dtype: torch.dtype, head_dim: int, page: int) -> bool:
-    return bool(library().exl3_attn_prefill_supported(_c_int(dtype_code(dtype)), _c_int(head_dim), _c_int(page)))
-
-
-def attn_prefill_tile(head_dim: int) -> int:
-    """Queries per block of the prefill attention for this head size."""
-    return int(library().exl3_attn_prefill_tile(_c_int(head_dim)))
-
-
-def attn_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                 block_table: torch.Tensor, row_start: torch.Tensor, row_pos0: torch.Tensor,
-                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, heads: int, kv_heads: int,
-                 head_dim: int, page: int, window: int, scale: float) -> torch.Tensor:
-    """Causal attention of whole prompts on the tensor cores (see attention_prefill.cu)."""
-    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
-        raise KernelLibraryError("attn_prefill: q, cache and out differ in element type")
-    _check(library().exl3_attn_prefill(
-        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
-        _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start), _ptr(row_pos0), _ptr(tile_seq),
-        _ptr(tile_q0), _c_int(n_tiles), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page),
-        _c_int(window), _c_float(scale), _stream()), "attn_prefill")
-    return out
-
-
 def attn_prefill_tc_supported(dtype: torch.dtype, head_dim: int, page: int) -> bool:
     return bool(library().exl3_attn_prefill_tc_supported(_c_int(dtype_code(dtype)), _c_int(head_dim), _c_int(page)))
 

@@ -11,8 +11,8 @@ query at position p to keys ``p - window + 1 .. p``.
 
 The three input projections are one fused matrix, so a step reads ``r`` once.
 
-Which kernels run: prompts in bfloat16 with heads of 64 go through the tcgen05 attention (heads of 128: the
-mma.sync one), after the position part's own step.  Steps in which every sequence brings one token (decode), in
+Which kernels run: prompts in bfloat16 with heads of 64 or 128 go through the tcgen05 attention, after the
+position part's own step.  Steps in which every sequence brings one token (decode), in
 bfloat16 with heads of 64 or 128, are one kernel: it rotates the queries and the token's own key, takes that key and
 value from the projection's output, adds them to the softmax and writes them to the cache (``_decode_fused``;
 the position part must offer ``fused_rotation``).  Everything else (float32, other head sizes) takes the
@@ -123,19 +123,12 @@ class Attention:
         s = self.spec
         T = qkv.shape[0]
         if batch.max_new > 1 and batch.tiles and K.attn_prefill_tc_supported(qkv.dtype, s.head_dim, kv.page_size):
-            # prompts, heads of 64: streaming softmax with both products on tcgen05 tensor cores,
+            # prompts, heads of 64 or 128: streaming softmax with both products on tcgen05 tensor cores,
             # TMA loads straight from the paged cache, a block per 128 queries
             tile_seq, tile_q0, n_tiles = batch.tiles[128]
             K.attn_prefill_tc(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
                               tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
                               self.scale)
-            return
-        if batch.max_new > 1 and batch.tiles and K.attn_prefill_supported(qkv.dtype, s.head_dim, kv.page_size):
-            # prompts, heads of 128: the same on mma.sync tensor cores, a block per tile of queries
-            tile_seq, tile_q0, n_tiles = batch.tiles[K.attn_prefill_tile(s.head_dim)]
-            K.attn_prefill(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
-                           tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
-                           self.scale)
             return
         split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device) if qkv.dtype == torch.bfloat16 else 0
         n = self._chunks(batch.max_kv_len, split) if split else 0

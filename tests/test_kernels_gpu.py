@@ -501,29 +501,9 @@ def test_attn_decode_is_refused_for_other_shapes():
     assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 1000)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 2, 128), (4, 1, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 1, 64), (3, 3, 128), (8, 2, 128), (5, 1, 128)])
 @pytest.mark.parametrize("window", [0, 24, 100])
-def test_attn_prefill(nh, nkv, hd, window):
-    # prompts from position 0, a prompt continued at position 500, single tokens, a full tile, one row more
-    case = PagedCase(lens=[300, 64, 1, 700, 65, 128], new=[300, 64, 1, 200, 65, 1], nh=nh, nkv=nkv, hd=hd,
-                     dtype=torch.bfloat16, seed=hd + nh + window)
-    T = case.q.shape[0]
-    # q lives inside a wider fused buffer, as in the engine
-    buf = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
-    buf[:, :nh * hd] = case.q.reshape(T, nh * hd).to(DEV)
-    out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
-    scale = 1.3 / math.sqrt(hd)
-    assert K().attn_prefill_supported(torch.bfloat16, hd, 64)
-    tile_seq, tile_q0 = case.tiles(K().attn_prefill_tile(hd))
-    K().attn_prefill(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
-                     tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale)
-    close(out, case.reference(window, scale), 1e-2, "attn_prefill")
-
-
-@pytest.mark.parametrize("nh,nkv", [(3, 3), (4, 2), (8, 1)])
-@pytest.mark.parametrize("window", [0, 24, 100])
-def test_attn_prefill_tc(nh, nkv, window):
-    hd = 64
+def test_attn_prefill_tc(nh, nkv, hd, window):
     case = PagedCase(lens=[300, 64, 1, 700, 65, 128, 129], new=[300, 64, 1, 200, 65, 1, 129], nh=nh, nkv=nkv, hd=hd,
                      dtype=torch.bfloat16, seed=hd + nh + window)
     T = case.q.shape[0]
@@ -540,10 +520,35 @@ def test_attn_prefill_tc(nh, nkv, window):
     close(out, case.reference(window, scale), 1e-2, "attn_prefill_tc")
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attn_prefill_tc_moves_its_reference_maximum(hd):
+    """Keys grow page by page, so every row's running maximum rises by far more than the kernel lets its
+    exponentials' reference lag behind: the accumulator in tensor memory is rescaled again and again."""
+    nh, nkv = 2, 1
+    case = PagedCase(lens=[700, 330], new=[700, 200], nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=41)
+    for b, n in enumerate(case.lens):
+        for pos in range(n):
+            f = 1.0 + 3.0 * (pos // 64)
+            case.k[b][pos] = (case.k[b][pos].float() * f).to(torch.bfloat16)
+            pg = int(case.table[b, pos // 64])
+            case.k_pool[pg, :, pos % 64] = case.k[b][pos].to(DEV)
+    T = case.q.shape[0]
+    buf = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    buf[:, :nh * hd] = case.q.reshape(T, nh * hd).to(DEV)
+    out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    tile_seq, tile_q0 = case.tiles(128)
+    K().attn_prefill_tc(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
+                        tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, 0, scale)
+    torch.cuda.synchronize()
+    assert K().attn_prefill_tc_status() == 0
+    close(out, case.reference(0, scale), 1e-2, "attn_prefill_tc, rising maximum")
+
+
 def test_attn_prefill_is_refused_for_other_shapes():
-    assert not K().attn_prefill_supported(torch.float32, 64, 64)
-    assert not K().attn_prefill_supported(torch.bfloat16, 48, 64)
-    assert not K().attn_prefill_supported(torch.bfloat16, 64, 32)
+    assert not K().attn_prefill_tc_supported(torch.float32, 64, 64)
+    assert not K().attn_prefill_tc_supported(torch.bfloat16, 48, 64)
+    assert not K().attn_prefill_tc_supported(torch.bfloat16, 64, 32)
 
 
 # -- rotary + cache write ------------------------------------------------------
