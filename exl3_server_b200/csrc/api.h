@@ -20,8 +20,9 @@ int exl3_add_rmsnorm(float* h, const void* y, int y_dtype, float y_scale, const 
                      int H, cudaStream_t stream);
 // interleave 0: gu = [gate (I) | up (I)]; 8: eight gate columns, then the eight up columns of the same features.
 int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, int interleave, cudaStream_t stream);
-int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, int rot, float pos_scale,
-                       const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+// inv_freq: rot / 2 frequencies; inv_freq_lo: what float32 lost of them, or null (see rope_sincos in common.cuh).
+int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const float* inv_freq_lo, int rot,
+                       float pos_scale, const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
                        void* k_pool, void* v_pool, int T, int nh, int nkv, int hd, int page, int write_kv,
                        cudaStream_t stream);
 
@@ -84,7 +85,7 @@ int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_poo
                      int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
                      const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, float scale,
                      int split_keys, int max_splits, float* scratch, size_t scratch_bytes, const float* inv_freq,
-                     int rot, float pos_scale, int write_new, cudaStream_t stream);
+                     const float* inv_freq_lo, int rot, float pos_scale, int write_new, cudaStream_t stream);
 
 int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,
                 cudaStream_t stream);

@@ -145,7 +145,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, int T, int nh, int nkv, int window, float scale_log2,
                    int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
-                   const float* __restrict__ inv_freq, float pos_scale, int rotate, int write_new,
+                   const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, float pos_scale,
+                   int rotate, int write_new,
                    __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
   constexpr int KS = HD == 64 ? 64 : 32;                 // keys of a stage
   constexpr int SPP = AD_PAGE / KS;                      // stages of a page
@@ -335,7 +336,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   };
 
   // ---- the position encoding, when it is this kernel's to apply -------------------------------
-  // Half-split rotary pairs (d, d + HD / 2) with angle pos * pos_scale * inv_freq[d], as rope_kv_write does it
+  // Half-split rotary pairs (d, d + HD / 2) with angle pos * pos_scale * (inv_freq[d] + inv_freq_lo[d]), as rope_kv_write does it
   // (elementwise.cu).  A thread's fragment holds features 16 j + 2 tl + 8 h + e: a pair's two halves are its
   // pieces j and j + NJ / 2.
   // A token's HD / 2 angles are computed once, two or so per lane, and kept in the warp's table (cos, sin):
@@ -348,7 +349,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const float p = (float)s_pos[t] * pos_scale;
     for (int d = lane; d < HD / 2; d += 32) {
       float sn, cs;
-      sincosf(p * __ldg(inv_freq + d), &sn, &cs);
+      rope_sincos(p, __ldg(inv_freq + d), inv_freq_lo ? __ldg(inv_freq_lo + d) : 0.0f, &sn, &cs);
       rot_tab[d] = make_float2(cs, sn);
     }
     __syncwarp();
@@ -772,13 +773,14 @@ extern "C" int exl3_attn_decode_status() {
 // With write_new, q is the fused q|k|v output of the projection and every token is its sequence's only new one:
 // the kernel takes the token's key and value from there, adds them to its softmax and writes them to the cache
 // (which holds the positions before it).  With rot = hd it also applies the half-split rotary encoding
-// (angle pos * pos_scale * inv_freq[d], hd / 2 frequencies) to the queries and the new key; rot = 0: none.
+// (angle pos * pos_scale * (inv_freq[d] + inv_freq_lo[d]), hd / 2 frequencies each, inv_freq_lo may be null) to the
+// queries and the new key; rot = 0: none.
 extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
                                 int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
                                 const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
                                 float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
-                                const float* inv_freq, int rot, float pos_scale, int write_new,
-                                cudaStream_t stream) {
+                                const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
+                                int write_new, cudaStream_t stream) {
   if (T == 0) return 0;
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
       !exl3_attn_decode_supported(DT_BF16, T, nh, nkv, hd, page, split_keys, max_splits)) {
@@ -828,7 +830,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   launch_pdl(attn_decode_kernel<HD_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,           \
-             max_splits, records, counters, inv_freq, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
+             max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
              static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool))
   if (hd == 64) EXL3_AD_LAUNCH(64); else EXL3_AD_LAUNCH(128);
 #undef EXL3_AD_LAUNCH

@@ -187,10 +187,10 @@ silu_mul_vec_kernel(const T* gu, T* out, int64_t total_vecs, int I, int interlea
 
 // One block per token.  qkv[t] = [q heads | k heads | v heads], each head_dim
 // wide.  q and k are rotated in place (half-split pairs d, d + rot/2 with
-// angle pos * pos_scale * inv_freq[d]); rotated k and plain v are written to
+// angle pos * pos_scale * (inv_freq[d] + inv_freq_lo[d])); rotated k and plain v are written to
 // the token's place in the paged cache.
 __global__ void rope_kv_write_kernel(void* __restrict__ qkv, int dtype, const float* __restrict__ inv_freq,
-                                     int rot, float pos_scale, const int* __restrict__ tok_pos,
+                                     const float* __restrict__ inv_freq_lo, int rot, float pos_scale, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                                      int bt_stride, void* __restrict__ k_pool, void* __restrict__ v_pool,
                                      int nh, int nkv, int hd, int page, int write_kv) {
@@ -214,7 +214,7 @@ __global__ void rope_kv_write_kernel(void* __restrict__ qkv, int dtype, const fl
   const int n_rot_heads = nh + nkv;
   auto rotate_heads = [&](int d, int first, int step) {
     float s, c;
-    sincosf(p * inv_freq[d], &s, &c);
+    rope_sincos(p, inv_freq[d], inv_freq_lo ? inv_freq_lo[d] : 0.0f, &s, &c);
     for (int head = first; head < n_rot_heads; head += step) {
       const int64_t a = base + (int64_t)head * hd + d;
       const float x0 = load_act(qkv, dtype, a), x1 = load_act(qkv, dtype, a + half);
@@ -256,7 +256,8 @@ __global__ void rope_kv_write_kernel(void* __restrict__ qkv, int dtype, const fl
 // rot % (2 VEC) == 0 and hd % VEC == 0.
 template <typename T>
 __global__ void __launch_bounds__(256)
-rope_kv_write_vec_kernel(T* qkv, const float* __restrict__ inv_freq, int rot, float pos_scale,
+rope_kv_write_vec_kernel(T* qkv, const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, int rot,
+                         float pos_scale,
                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                          const int* __restrict__ block_table, int bt_stride, T* k_pool, T* v_pool, int nh, int nkv,
                          int hd, int page, int write_kv) {
@@ -277,7 +278,8 @@ rope_kv_write_vec_kernel(T* qkv, const float* __restrict__ inv_freq, int rot, fl
   const float p = (float)pos * pos_scale;
   // the token's sines and cosines, once for all its heads
   extern __shared__ float rope_cs[];                  // [half] cosines, then [half] sines
-  for (int d = threadIdx.x; d < half; d += blockDim.x) sincosf(p * inv_freq[d], &rope_cs[half + d], &rope_cs[d]);
+  for (int d = threadIdx.x; d < half; d += blockDim.x)
+    rope_sincos(p, inv_freq[d], inv_freq_lo ? inv_freq_lo[d] : 0.0f, &rope_cs[half + d], &rope_cs[d]);
   __syncthreads();
   const int cpr = half / VEC;                         // rotated pieces per head (first half)
   const int n_rot = (nh + nkv) * cpr;
@@ -381,7 +383,8 @@ extern "C" int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I,
   return launch_status("silu_mul");
 }
 
-extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, int rot, float pos_scale,
+extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const float* inv_freq_lo, int rot,
+                                  float pos_scale,
                                   const int* tok_pos, const int* tok_seq, const int* block_table,
                                   int bt_stride, void* k_pool, void* v_pool, int T, int nh, int nkv, int hd,
                                   int page, int write_kv, cudaStream_t stream) {
@@ -395,14 +398,14 @@ extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, i
   const bool fast = rot % (2 * vec) == 0 && hd % vec == 0 && aligned16(qkv) && aligned16(k_pool) && aligned16(v_pool);
   if (fast && dtype == DT_F32) {
     launch_pdl(rope_kv_write_vec_kernel<float>, dim3(T), dim3(256), (size_t)rot * sizeof(float), stream, static_cast<float*>(qkv), inv_freq,
-               rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride, static_cast<float*>(k_pool),
+               inv_freq_lo, rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride, static_cast<float*>(k_pool),
                static_cast<float*>(v_pool), nh, nkv, hd, page, write_kv);
   } else if (fast) {
     launch_pdl(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t)rot * sizeof(float), stream,
-               static_cast<__nv_bfloat16*>(qkv), inv_freq, rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride,
+               static_cast<__nv_bfloat16*>(qkv), inv_freq, inv_freq_lo, rot, pos_scale, tok_pos, tok_seq, block_table, bt_stride,
                static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), nh, nkv, hd, page, write_kv);
   } else {
-    launch_pdl(rope_kv_write_kernel, dim3(T), dim3(256), 0, stream, qkv, dtype, inv_freq, rot, pos_scale, tok_pos,
+    launch_pdl(rope_kv_write_kernel, dim3(T), dim3(256), 0, stream, qkv, dtype, inv_freq, inv_freq_lo, rot, pos_scale, tok_pos,
                tok_seq, block_table, bt_stride, k_pool, v_pool, nh, nkv, hd, page, write_kv);
   }
   return launch_status("rope_kv_write");

@@ -119,6 +119,28 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interlea
     return out
 
 
+def rotary_table(frequencies: torch.Tensor) -> torch.Tensor:
+    """Float64 frequencies as the kernels take them: float32 ``[2, n]``, row 0 the frequencies rounded to
+    float32, row 1 what the rounding lost, so that the angle ``position * frequency`` keeps its accuracy at
+    large positions.  A plain float32 ``[n]`` table is taken too (no second term)."""
+    f = frequencies.to(torch.float64)
+    hi = f.to(torch.float32)
+    lo = (f - hi.to(torch.float64)).to(torch.float32)
+    return torch.stack([hi, lo]).contiguous()
+
+
+def _rotary_rows(inv_freq: torch.Tensor, rot: int, what: str):
+    """The frequency table's pointers: (frequencies, their float32 remainders or null)."""
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() not in (rot // 2, rot) or \
+            (inv_freq.numel() == rot and inv_freq.dim() != 2):
+        raise KernelLibraryError(f"{what}: inv_freq must be float32 with rot / 2 entries, or [2, rot / 2] "
+                                 "(see rotary_table)")
+    _contig(inv_freq, "inv_freq")
+    if inv_freq.dim() == 2 and inv_freq.shape[0] == 2:
+        return _ptr(inv_freq[0]), _ptr(inv_freq[1])
+    return _ptr(inv_freq), _c_void_p(0)
+
+
 def rope_kv_write(qkv: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos_scale: float,
                   tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                   k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], heads: int, kv_heads: int,
@@ -128,12 +150,11 @@ def rope_kv_write(qkv: torch.Tensor, inv_freq: torch.Tensor, rot: int, pos_scale
     _contig(qkv, "qkv")
     if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
         raise KernelLibraryError("rope_kv_write: qkv width does not match the head counts")
-    if inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rot:
-        raise KernelLibraryError("rope_kv_write: inv_freq must be float32 with rot/2 entries")
+    hi, lo = _rotary_rows(inv_freq, rot, "rope_kv_write") if rot else (_c_void_p(0), _c_void_p(0))
     if write_kv and (k_pool.dtype != qkv.dtype or v_pool.dtype != qkv.dtype):
         raise KernelLibraryError("rope_kv_write: cache and activations differ in element type")
     _check(library().exl3_rope_kv_write(
-        _ptr(qkv), _c_int(dtype_code(qkv.dtype)), _ptr(inv_freq), _c_int(rot), _c_float(pos_scale),
+        _ptr(qkv), _c_int(dtype_code(qkv.dtype)), hi, lo, _c_int(rot), _c_float(pos_scale),
         _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), _c_int(block_table.stride(0)),
         _ptr(k_pool) if write_kv else _c_void_p(0), _ptr(v_pool) if write_kv else _c_void_p(0), _c_int(T),
         _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(1 if write_kv else 0),
@@ -342,23 +363,24 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     arguments and scratch as ``attn_tokens``.  With ``write_new``, ``q`` is the fused q|k|v output of the
     projection, every token is its sequence's only new one and the cache holds the positions before it: the
     kernel adds the token's own key and value to its softmax and writes them to the cache.  With ``rot`` equal to
-    ``head_dim`` it applies the half-split rotary encoding (``inv_freq``: head_dim / 2 float32 frequencies) to
+    ``head_dim`` it applies the half-split rotary encoding (``inv_freq``: head_dim / 2 float32 frequencies, or a ``rotary_table``) to
     the queries and the new key."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
     _contig(v_pool, "v_pool")
+    hi = lo = _c_void_p(0)
     if rot:
-        if inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2:
-            raise KernelLibraryError("attn_decode: inv_freq must hold rot / 2 float32 frequencies")
-        _contig(inv_freq, "inv_freq")
+        if inv_freq is None:
+            raise KernelLibraryError("attn_decode: rot needs inv_freq")
+        hi, lo = _rotary_rows(inv_freq, rot, "attn_decode")
     pool_rows = k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2]
     nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
     _check(library().exl3_attn_decode(
         _ptr(q), _c_int64(q_row_stride), _ptr(out), _ptr(k_pool), _ptr(v_pool), _c_int64(pool_rows),
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T), _c_int(heads),
         _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
-        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _ptr(inv_freq if rot else None), _c_int(rot),
+        _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), hi, lo, _c_int(rot),
         _c_float(pos_scale), _c_int(1 if write_new else 0), _stream()), "attn_decode")
     return out
 

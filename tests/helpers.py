@@ -13,6 +13,7 @@ from exl3_server_b200 import LlamaConfig, write_random_model
 #  A: MiniCPM-style; grouped heads 4/2, head 16, tied head, all three scale constants.
 #  B: plain Llama; one kv head, head 32, untied, other theta and eps, no scaling.
 #  D: heads of 64 (the tensor-core attention's shape), width 136, vocabulary 301.
+#  E: grouped heads of 128 (see below).
 #  C: odd sizes: width 96, 6/3 heads of 48, vocabulary 263, a window of 24 keys on
 #     layers 0 and 2 (full attention on 1 and 3), biases on every projection.
 TINY: Dict[str, dict] = {
@@ -41,6 +42,14 @@ TINY: Dict[str, dict] = {
         rms_norm_eps=1e-5, scale_emb=2.0, scale_depth=1.0, dim_model_base=68, max_position_embeddings=4096,
         sliding_window=80, layer_types=["full_attention", "sliding_attention"]),
         norm_std=0.1, biases=False),
+    # E: grouped heads of 128 (6 query heads on 2), the tensor-core kernels' other shape; untied head, a window
+    # of 150 keys on the first layer.
+    "E": dict(cfg=LlamaConfig(
+        hidden_size=200, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+        intermediate_size=272, vocab_size=331, tie_word_embeddings=False, rope_theta=500000.0,
+        rms_norm_eps=2e-5, max_position_embeddings=4096,
+        sliding_window=150, layer_types=["sliding_attention", "full_attention"]),
+        norm_std=0.15, biases=False),
 }
 
 

@@ -23,7 +23,7 @@ def engine_for(folder, dtype, max_tokens=2048):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["C", "D"])
+@pytest.mark.parametrize("name", ["C", "D", "E"])
 def test_long_decoding(model_folders, name, dtype):
     """A 40-token prompt, then 1100 tokens one by one: across page boundaries
     (64), attention chunk boundaries (256), the decode graph's context bucket
@@ -128,7 +128,7 @@ def test_window_edge_in_the_engine(model_folders):
     assert rel_err(pm.logits(toks).numpy()[120:121], want[120:121]) > 1e-4
 
 
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_greedy_generation_through_the_entry_point(model_folders, name):
     from exl3_server_b200 import Engine, GenerateOptions
     folder = model_folders[name]

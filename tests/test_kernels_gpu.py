@@ -479,7 +479,8 @@ def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, hd, window, rotar
         n = min(n, (window + split - 2) // split + 1)
     scratch = torch.zeros(K().attn_tokens_scratch_bytes(B, nh, hd, n) // 4, device=DEV)
     K().attn_decode(qkv, qkv.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, B,
-                    nh, nkv, hd, 64, window, scale, split, n, scratch, inv_freq=inv_freq.to(DEV), rot=rot,
+                    nh, nkv, hd, 64, window, scale, split, n, scratch,
+                    inv_freq=(K().rotary_table(inv_freq) if split == 256 else inv_freq).to(DEV), rot=rot,
                     pos_scale=pos_scale, write_new=True)
     close(out, case.reference(window, scale), 1e-2, "attn_decode, own key and value")
     for b in range(B):
@@ -595,6 +596,34 @@ def test_rope_kv_write(dtype, nh, nkv, hd, rot):
         assert torch.equal(vp[pg, :, pos % page].cpu().double(), v), "v in cache"
     written = sum(new) * nkv * hd
     assert int((vp != 0).sum()) <= written               # nothing else was touched
+
+
+@pytest.mark.parametrize("hd", [64, 80])                        # the 16-byte kernel and the general one
+def test_rope_angles_stay_exact_at_large_positions(hd):
+    """At position 150,000 a frequency rounded to float32 puts the fastest pairs' angles off by up to 1e-2
+    radians; with the table's second row (what the rounding lost) the kernel's float32 angles stay right."""
+    nh, nkv = 2, 1
+    pos = [150001, 99999, 31337]
+    T = len(pos)
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g)
+    f64 = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)
+    ang = torch.tensor(pos, dtype=torch.float64)[:, None] * f64[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x = qkv.double().reshape(T, nh + 2 * nkv, hd)[:, :nh]
+    x0, x1 = x[..., :hd // 2], x[..., hd // 2:]
+    want = torch.cat([x0 * cos - x1 * sin, x1 * cos + x0 * sin], dim=-1)
+    tok_pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    errs = []
+    for tab in (K().rotary_table(f64).to(DEV), f64.float().to(DEV)):
+        buf = qkv.to(DEV).clone()
+        K().rope_kv_write(buf, tab, hd, 1.0, tok_pos, tok_seq, table, None, None, nh, nkv, hd, 64, False)
+        got = buf.cpu().double().reshape(T, nh + 2 * nkv, hd)[:, :nh]
+        errs.append(float((got - want).abs().max()))
+    assert errs[0] < 3e-6, errs          # float32 sine and cosine of an angle that is right
+    assert errs[1] > 1e-4, errs          # the plain table shows what the second row is for
 
 
 # -- sampling ------------------------------------------------------------------

@@ -12,7 +12,7 @@ from plain_llama import PlainModel
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 9, 13, 70, 131], "B": [1, 17, 40, 64, 97], "C": [3, 33, 64, 65, 150],
-           "D": [2, 64, 129, 200, 333]}
+           "D": [2, 64, 129, 200, 333], "E": [1, 63, 130, 257, 300]}
 _plain_cache = {}
 
 
