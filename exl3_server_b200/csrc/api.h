@@ -89,6 +89,13 @@ int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_poo
 
 int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,
                 cudaStream_t stream);
-int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature, int* out,
-                            int R, int V, cudaStream_t stream);
+// The reference's sampler on the device (see sampling_filtered.cu).  rows: float64 [R, 5] = temperature (<= 0:
+// greedy), top_k (0: off; at most exl3_sample_filtered_cap()), top_p, min_p, uniform number in [0, 1).
+int exl3_sample_filtered(const float* logits, const double* rows, int* out, int R, int V, cudaStream_t stream);
+int exl3_sample_filtered_cap();
+// counts: R device pointers (null: none) to int32 [V] token counts of the rows' contexts; params: float32 [R, 3] =
+// repetition, presence and frequency penalty.  Changes logits in place.  exl3_sample_count adds the chosen tokens.
+int exl3_sample_penalties(float* logits, int R, int V, const int* const* counts, const float* params,
+                          cudaStream_t stream);
+int exl3_sample_count(int* const* counts, const int* ids, int R, int V, cudaStream_t stream);
 }

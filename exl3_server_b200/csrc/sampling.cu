@@ -1,12 +1,8 @@
 // Picking the next token on the device.
 //
 // argmax: the first maximum wins, as in the reference's strict ">" scans
-// (src/model.cpp:604-613, 688-696).  sample_temperature: p[i] is proportional
-// to exp(logit[i] / T - max), the token is the first index whose running sum
-// reaches u * total: inverse-CDF sampling as in src/model.cpp:748-756, but
-// over all tokens in index order (the reference sorts its candidates first, so
-// the same u picks a different token there; the host sampler reproduces that
-// order).
+// (src/model.cpp:604-613, 688-696).  Sampling with temperature and filters
+// is in sampling_filtered.cu.
 #include "api.h"
 #include "common.cuh"
 
@@ -113,63 +109,6 @@ argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, in
   if (threadIdx.x == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_temperature_kernel(const float* __restrict__ logits, const float* __restrict__ uniform,
-                          float inv_t, int* __restrict__ out, int V) {
-  __shared__ float red[32];
-  __shared__ float part[SAMPLE_THREADS];
-  __shared__ int chosen;
-  const float* row = logits + (int64_t)blockIdx.x * V;
-  const int tid = threadIdx.x;
-  // each thread owns a contiguous range so that the running sum follows index order
-  const int per = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int b = min(V, tid * per), e = min(V, b + per);
-  float mx = -INFINITY;
-  for (int i = b; i < e; ++i) mx = fmaxf(mx, row[i] * inv_t);
-  mx = warp_max(mx);
-  if ((tid & 31) == 0) red[tid >> 5] = mx;
-  __syncthreads();
-  mx = red[tid & 31];
-  mx = warp_max(mx);
-  float s = 0.0f;
-  for (int i = b; i < e; ++i) s += expf(row[i] * inv_t - mx);
-  part[tid] = s;
-  if (tid == 0) chosen = -1;
-  __syncthreads();
-  if (tid == 0) {
-    // serial prefix over 1024 partial sums: cheap, and the order is fixed
-    float total = 0.0f;
-    for (int i = 0; i < SAMPLE_THREADS; ++i) total += part[i];
-    const float target = uniform[blockIdx.x] * total;
-    float run = 0.0f;
-    int owner = -1;
-    for (int i = 0; i < SAMPLE_THREADS; ++i) {
-      if (part[i] > 0.0f && run + part[i] >= target) { owner = i; break; }
-      run += part[i];
-    }
-    if (owner < 0) {                                // rounding left the target past the end
-      for (int i = SAMPLE_THREADS - 1; i >= 0; --i) if (part[i] > 0.0f) { owner = i; break; }
-      run = total;                                   // forces the last token of that range
-    }
-    part[0] = run;                                   // running sum before the owner's range
-    red[0] = target;
-    chosen = owner;
-  }
-  __syncthreads();
-  if (tid == chosen) {
-    float run = part[0];
-    const float target = red[0];
-    int pick = -1, last = -1;
-    for (int i = b; i < e; ++i) {
-      const float p = expf(row[i] * inv_t - mx);
-      if (p > 0.0f) last = i;
-      run += p;
-      if (p > 0.0f && run >= target) { pick = i; break; }
-    }
-    out[blockIdx.x] = pick >= 0 ? pick : (last >= 0 ? last : b);
-  }
-}
-
 }  // namespace exl3
 
 using namespace exl3;
@@ -203,17 +142,6 @@ extern "C" int exl3_argmax(const float* logits, int* out, int R, int V, void* sc
   launch_pdl(argmax_final_kernel, dim3(R), dim3(ARGMAX_THREADS), 0, stream, (const float*)pv, (const int*)pi, out,
              nchunks);
   return launch_status("argmax_final");
-}
-
-extern "C" int exl3_sample_temperature(const float* logits, const float* uniform, float inv_temperature,
-                                       int* out, int R, int V, cudaStream_t stream) {
-  if (R == 0) return 0;
-  if (R < 0 || V < 1 || !(inv_temperature > 0.0f)) {
-    set_error("sample_temperature: bad arguments rows=%d vocab=%d 1/T=%g", R, V, (double)inv_temperature);
-    return ERR_BAD_ARGUMENT;
-  }
-  sample_temperature_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, uniform, inv_temperature, out, V);
-  return launch_status("sample_temperature");
 }
 
 // ---------------------------------------------------------------------------

@@ -412,15 +412,42 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return out
 
 
-def sample_temperature(logits: torch.Tensor, uniform: torch.Tensor, temperature: float,
-                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def sample_filtered_cap() -> int:
+    """The most candidates the device sampler ranks (``top_k`` above it is the host sampler's)."""
+    return int(library().exl3_sample_filtered_cap())
+
+
+def sample_filtered(logits: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The reference's sampler on the device.  ``rows``: float64 ``[R, 5]`` on the device: temperature (<= 0:
+    greedy), top_k (0: off), top_p, min_p and the row's uniform number in [0, 1)."""
     R, V = logits.shape
-    if logits.dtype != torch.float32 or uniform.dtype != torch.float32 or uniform.numel() != R:
-        raise KernelLibraryError("sample_temperature: logits [R,V] and uniform [R] must be float32")
+    if logits.dtype != torch.float32 or rows.dtype != torch.float64 or tuple(rows.shape) != (R, 5):
+        raise KernelLibraryError("sample_filtered: logits [R, V] must be float32 and rows [R, 5] float64")
     _contig(logits, "logits")
+    _contig(rows, "rows")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _check(library().exl3_sample_temperature(_ptr(logits), _ptr(uniform), _c_float(1.0 / temperature),
-                                             _ptr(out), _c_int(R), _c_int(V), _stream()),
-           "sample_temperature")
+    _check(library().exl3_sample_filtered(_ptr(logits), _ptr(rows), _ptr(out), _c_int(R), _c_int(V), _stream()),
+           "sample_filtered")
     return out
+
+
+def sample_penalties(logits: torch.Tensor, counts: torch.Tensor, params: torch.Tensor) -> None:
+    """Repetition, presence and frequency penalties, in place.  ``counts``: int64 ``[R]`` on the device, the
+    addresses of the rows' int32 ``[V]`` token counts (0: the row has none); ``params``: float32 ``[R, 3]``."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or counts.dtype != torch.int64 or params.dtype != torch.float32 or \
+            counts.numel() != R or tuple(params.shape) != (R, 3):
+        raise KernelLibraryError("sample_penalties: logits float32 [R, V], counts int64 [R], params float32 [R, 3]")
+    _contig(logits, "logits")
+    _contig(params, "params")
+    _check(library().exl3_sample_penalties(_ptr(logits), _c_int(R), _c_int(V), _ptr(counts), _ptr(params),
+                                           _stream()), "sample_penalties")
+
+
+def sample_count(counts: torch.Tensor, ids: torch.Tensor, vocab: int) -> None:
+    """Adds each row's chosen token (``ids`` int32 ``[R]``) to its counts (``counts`` as in ``sample_penalties``)."""
+    if counts.dtype != torch.int64 or ids.dtype != torch.int32 or counts.numel() != ids.numel():
+        raise KernelLibraryError("sample_count: counts int64 [R] and ids int32 [R]")
+    _check(library().exl3_sample_count(_ptr(counts), _ptr(ids), _c_int(ids.numel()), _c_int(vocab), _stream()),
+           "sample_count")

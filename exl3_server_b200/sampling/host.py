@@ -40,8 +40,14 @@ def sample_token(logits: np.ndarray, opt: SampleOptions, context: Sequence[int],
     cap = max(opt.top_k if opt.top_k > 0 else 0, 2048)   # src/model.cpp:698
     m = min(n, cap)
     if m < n:
-        part = np.argpartition(-logits, m - 1)[:m]
-        idx = part[np.argsort(-logits[part], kind="stable")]
+        # equal logits rank by index, the smaller first (the reference's partial sort leaves their order open;
+        # the device sampler ranks them the same way)
+        neg = -logits
+        kth = np.partition(neg, m - 1)[m - 1]
+        above = np.nonzero(neg < kth)[0]
+        ties = np.nonzero(neg == kth)[0][:m - above.size]
+        part = np.sort(np.concatenate([above, ties]))
+        idx = part[np.argsort(neg[part], kind="stable")]
     else:
         idx = np.argsort(-logits, kind="stable")
     inv_t = np.float32(1.0) / np.float32(opt.temperature)

@@ -1,10 +1,13 @@
 """Choosing how a batch of logit rows is sampled.
 
-Rows that are all greedy, or all plain temperature without filters or
-penalties, are sampled on the device by the argmax / inverse-CDF kernels and
-only the chosen ids cross to the host.  Anything else (top-k, top-p, min-p,
-penalties, or a mixed batch) is sampled on the host by the reference's
-algorithm, which is where the reference always samples (src/model.cpp:667-757).
+Rows that are all greedy take the argmax kernel.  Everything else that the
+device sampler covers (temperature with top-k up to its cap, top-p, min-p and
+the penalties over the context) is sampled on the device by the reference's
+algorithm (``csrc/sampling_filtered.cu``): only the options, the uniform numbers
+and the chosen ids cross between host and device.  ``host.sample_token`` is the
+same algorithm on the host (src/model.cpp:667-757), for logits that are not on
+the device and for ``top_k`` above the cap; the tests hold the two against
+each other.
 """
 from __future__ import annotations
 
@@ -24,6 +27,51 @@ class RowSampler:
         self.opt = opt
         self.rng = SplitMix64(opt.seed + request_index)
         self.context: List[int] = list(prompt)
+        self._counts: Optional[torch.Tensor] = None      # int32 [vocab] on the device: how often each token occurs
+        self._counted = 0                                # tokens of the context that the counts hold
+
+    def device_counts(self, vocab: int, device) -> torch.Tensor:
+        """The context's token counts on the device, for the penalties: made from the whole context when first
+        asked for, then kept up by the sampler's own kernel (``counted``) or from the context's new tokens."""
+        if self._counts is None:
+            self._counts = torch.zeros(vocab, dtype=torch.int32, device=device)
+        if self._counted < len(self.context):
+            new = torch.tensor([t for t in self.context[self._counted:] if 0 <= t < vocab], dtype=torch.int64)
+            if new.numel():
+                self._counts.index_add_(0, new.to(device), torch.ones(new.numel(), dtype=torch.int32, device=device))
+            self._counted = len(self.context)
+        return self._counts
+
+    def counted(self, n: int = 1) -> None:
+        """The device has added the next ``n`` tokens of the context to the counts itself."""
+        self._counted += n
+
+
+def _on_device(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
+    from ..engine.decode import TRANSFERRED
+    from ..ops import kernels as K
+    R, V = logits.shape
+    counts = None
+    if any(r.opt.has_penalties for r in rows):
+        logits = logits.clone()                          # the step's own buffer stays as the model left it
+        counts = torch.tensor([r.device_counts(V, logits.device).data_ptr() if r.opt.has_penalties else 0
+                               for r in rows], dtype=torch.int64).to(logits.device)
+        params = torch.tensor([[r.opt.repetition_penalty, r.opt.presence_penalty, r.opt.frequency_penalty]
+                               for r in rows], dtype=torch.float32)
+        TRANSFERRED["h2d"] += counts.numel() * 8 + params.numel() * 4
+        K.sample_penalties(logits, counts, params.to(logits.device))
+    # a greedy row draws no number from its generator, as on the host
+    opts = torch.tensor([[r.opt.temperature, r.opt.top_k, r.opt.top_p, r.opt.min_p,
+                          0.0 if r.opt.greedy else r.rng.uniform01()] for r in rows], dtype=torch.float64)
+    ids = K.sample_filtered(logits, opts.to(logits.device))
+    if counts is not None:
+        K.sample_count(counts, ids, V)                   # the chosen tokens join the counts without a trip to the host
+        for r in rows:
+            if r.opt.has_penalties:
+                r.counted()
+    TRANSFERRED["h2d"] += opts.numel() * 8
+    TRANSFERRED["d2h"] += ids.numel() * 4
+    return ids.cpu().tolist()
 
 
 def sample_rows(logits: torch.Tensor, rows: Sequence[RowSampler],
@@ -33,27 +81,19 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[RowSampler],
     computed it on the device."""
     if logits.shape[0] != len(rows):
         raise ValueError(f"{logits.shape[0]} logit rows for {len(rows)} requests")
-    if logits.is_cuda and not any(r.opt.has_penalties for r in rows):
+    picked: Optional[List[int]] = None
+    if logits.is_cuda:
         from ..ops import kernels as K
-        if all(r.opt.greedy for r in rows):
+        if all(r.opt.greedy and not r.opt.has_penalties for r in rows):
             ids = device_argmax if device_argmax is not None else K.argmax(logits)
             picked = ids.cpu().tolist()
             from ..engine.decode import TRANSFERRED
             TRANSFERRED["d2h"] += ids.numel() * 4
-            for r, t in zip(rows, picked):
-                r.context.append(t)
-            return picked
-        temps = {r.opt.temperature for r in rows}
-        if len(temps) == 1 and not any(r.opt.greedy or r.opt.has_filters for r in rows):
-            u = torch.tensor([r.rng.uniform01() for r in rows], dtype=torch.float32).to(logits.device)
-            picked = K.sample_temperature(logits, u, temps.pop()).cpu().tolist()
-            for r, t in zip(rows, picked):
-                r.context.append(t)
-            return picked
-    host = logits.detach().to(torch.float32).cpu().numpy()
-    out = []
-    for i, r in enumerate(rows):
-        t = sample_token(host[i], r.opt, r.context, r.rng)
+        elif all(r.opt.top_k <= K.sample_filtered_cap() for r in rows):
+            picked = _on_device(logits.to(torch.float32), rows)
+    if picked is None:
+        host = logits.detach().to(torch.float32).cpu().numpy()
+        picked = [sample_token(host[i], r.opt, r.context, r.rng) for i, r in enumerate(rows)]
+    for r, t in zip(rows, picked):
         r.context.append(t)
-        out.append(t)
-    return out
+    return picked

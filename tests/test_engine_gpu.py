@@ -189,6 +189,29 @@ def test_temperature_sampling_is_seeded(model_folders):
     assert [r.tokens for r in other] != [r.tokens for r in a]
 
 
+def test_sampling_on_the_device_follows_the_host_sampler():
+    """The same requests sampled from logits on the device and from a copy on the host: filters, penalties over
+    the growing context, a greedy row among them, every request with its own generator."""
+    from exl3_server_b200.sampling import SampleOptions
+    from exl3_server_b200.sampling.sampler import RowSampler, sample_rows
+    opts = [SampleOptions(temperature=0.8, top_k=30, top_p=0.9, seed=3),
+            SampleOptions(temperature=1.2, min_p=0.03, repetition_penalty=1.2, presence_penalty=0.3,
+                          frequency_penalty=0.1, seed=4),
+            SampleOptions(temperature=0.0, repetition_penalty=1.5),
+            SampleOptions(temperature=1.0, seed=5)]
+    prompts = [[5, 6, 7], [8, 8, 8, 9], [1], [2, 3]]
+    V = 4000
+    g = torch.Generator().manual_seed(17)
+    dev_rows = [RowSampler(o, i, p) for i, (o, p) in enumerate(zip(opts, prompts))]
+    host_rows = [RowSampler(o, i, p) for i, (o, p) in enumerate(zip(opts, prompts))]
+    for _ in range(40):
+        logits = 3.0 * torch.randn(len(opts), V, generator=g)
+        on_device = sample_rows(logits.to("cuda:0"), dev_rows)
+        on_host = sample_rows(logits, host_rows)
+        assert on_device == on_host
+    assert [r.context for r in dev_rows] == [r.context for r in host_rows]
+
+
 def test_errors_come_before_any_kernel(model_folders):
     from exl3_server_b200 import Engine, StepEntry, StepError
     from exl3_server_b200.cache import CacheFull

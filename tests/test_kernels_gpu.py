@@ -4,6 +4,7 @@ vocabularies that are no power of two, head sizes in steps of 16, grouped
 heads, windows, ragged batches)."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -640,24 +641,116 @@ def test_argmax_first_maximum(V):
     assert got == [int(torch.argmax(x[0])), V // 2, 0, V - 1, int(torch.argmax(x[4]))]
 
 
-def test_sample_temperature_is_inverse_cdf_in_index_order():
-    torch.manual_seed(8)
+class _FixedU:
+    """A generator that hands out one given number."""
+    def __init__(self, u):
+        self.u = u
+
+    def uniform01(self):
+        return self.u
+
+
+def _host_ranking(logits, opt):
+    """The host sampler's candidates in its order, and the running sums of their probabilities (float64)."""
+    x = logits.astype(np.float32)
+    m = min(x.shape[0], 2048)
+    idx = np.argsort(-x, kind="stable")[:m]
+    inv_t = np.float32(1.0) / np.float32(opt.temperature)
+    probs = np.exp(x[idx] * inv_t - x[idx[0]] * inv_t).astype(np.float32)
+    return idx, np.cumsum(probs.astype(np.float64))
+
+
+@pytest.mark.parametrize("V", [300, 5000, 122753])
+def test_sample_filtered_agrees_with_the_host_sampler(V):
+    from exl3_server_b200.sampling import SampleOptions
+    from exl3_server_b200.sampling.host import sample_token
+    rng = np.random.default_rng(V)
+    option_sets = [SampleOptions(temperature=0.7), SampleOptions(temperature=1.3, top_k=5),
+                   SampleOptions(temperature=1.0, top_p=0.9), SampleOptions(temperature=2.0, top_p=0.5, top_k=50),
+                   SampleOptions(temperature=1.0, min_p=0.05),
+                   SampleOptions(temperature=0.9, min_p=0.02, top_p=0.8, top_k=40),
+                   SampleOptions(temperature=0.0), SampleOptions(temperature=30.0)]
+    R = len(option_sets)
+    logits = (3.0 * rng.normal(size=(R, V))).astype(np.float32)
+    dev_logits = torch.from_numpy(logits).to(DEV)
+    near = 0
+    for u in [0.0, 1e-9, 0.013, 0.25, 0.5, 0.77, 0.93, 0.999999] + rng.random(24).tolist():
+        rows = torch.tensor([[o.temperature, o.top_k, o.top_p, o.min_p, u] for o in option_sets], dtype=torch.float64)
+        got = K().sample_filtered(dev_logits, rows.to(DEV)).cpu().tolist()
+        for r, o in enumerate(option_sets):
+            want = sample_token(logits[r], o, [], _FixedU(u))
+            if got[r] == want:
+                continue
+            # float32 exponentials may differ in their last bit between host and device: the two may part only
+            # where u falls on the border between two neighbours of the ranking
+            idx, acc = _host_ranking(logits[r], o)
+            i, j = int(np.nonzero(idx == want)[0][0]), int(np.nonzero(idx == got[r])[0][0])
+            assert abs(i - j) == 1, (V, u, r, want, got[r])
+            near += 1
+    assert near <= 2, near
+
+
+def test_sample_filtered_ranks_equal_logits_by_index():
+    """Many tokens share each value (logits rounded to halves), also across the 2048th place: the ranking takes
+    the smaller index first, as the host's stable sort does."""
+    from exl3_server_b200.sampling import SampleOptions
+    from exl3_server_b200.sampling.host import sample_token
+    rng = np.random.default_rng(5)
+    V = 9000
+    logits = (np.round(2.0 * rng.normal(size=(3, V))) / 2.0).astype(np.float32)
+    logits[2, :] = 1.0                                   # one value only: the first 2048 indices are the candidates
+    dev_logits = torch.from_numpy(logits).to(DEV)
+    opts = [SampleOptions(temperature=1.0), SampleOptions(temperature=5.0, top_k=700), SampleOptions(temperature=1.0)]
+    for u in [0.0, 0.2, 0.41, 0.63, 0.87, 0.99]:
+        rows = torch.tensor([[o.temperature, o.top_k, o.top_p, o.min_p, u] for o in opts], dtype=torch.float64)
+        got = K().sample_filtered(dev_logits, rows.to(DEV)).cpu().tolist()
+        want = [sample_token(logits[r], o, [], _FixedU(u)) for r, o in enumerate(opts)]
+        assert got == want, (u, got, want)
+        assert want[2] < 2048
+
+
+def test_sample_filtered_keeps_to_the_2048_most_probable():
+    rng = np.random.default_rng(0)
     V = 5000
-    x = 3 * torch.randn(4, V, device=DEV)
-    temp = 0.8
-    p = torch.softmax(x.double() / temp, -1).cpu()
-    cdf = torch.cumsum(p, -1)
-    for u in (0.0, 0.013, 0.5, 0.77, 0.999999):
-        got = K().sample_temperature(x, torch.full((4,), u, device=DEV), temp).cpu().tolist()
-        for r in range(4):
-            want = int(torch.searchsorted(cdf[r], torch.tensor(u, dtype=torch.float64)))
-            # float32 running sums may move the boundary by one token of negligible mass
-            assert abs(got[r] - want) <= 1 or abs(float(cdf[r, got[r]]) - u) < 1e-4, (u, r, got[r], want)
+    logits = rng.normal(size=(1, V)).astype(np.float32)
+    allowed = set(np.argsort(-logits[0])[:2048].tolist())
+    dev_logits = torch.from_numpy(logits).to(DEV).repeat(512, 1).contiguous()
+    rows = torch.tensor([[50.0, 0, 1.0, 0.0, u] for u in rng.random(512)], dtype=torch.float64)
+    picks = set(K().sample_filtered(dev_logits, rows.to(DEV)).cpu().tolist())
+    assert picks <= allowed and len(picks) > 400
 
 
-def test_sample_temperature_distribution():
-    x = torch.log(torch.tensor([[0.6, 0.3, 0.1]], device=DEV)).repeat(4096, 1)
-    u = torch.rand(4096, device=DEV)
-    got = K().sample_temperature(x, u, 1.0)
+def test_sample_filtered_distribution():
+    x = torch.log(torch.tensor([[0.6, 0.3, 0.1]], device=DEV)).repeat(4096, 1).contiguous()
+    u = torch.rand(4096, dtype=torch.float64)
+    one, zero = torch.ones(4096, dtype=torch.float64), torch.zeros(4096, dtype=torch.float64)
+    rows = torch.stack([one, zero, one, zero, u], dim=1).contiguous()
+    got = K().sample_filtered(x, rows.to(DEV))
     freq = torch.bincount(got.long(), minlength=3).double().cpu() / 4096
     assert torch.allclose(freq, torch.tensor([0.6, 0.3, 0.1], dtype=torch.float64), atol=0.03)
+
+
+def test_sample_penalties_as_on_the_host():
+    from exl3_server_b200.sampling import SampleOptions, apply_penalties
+    rng = np.random.default_rng(9)
+    V, R = 1000, 3
+    logits = (2.0 * rng.normal(size=(R, V))).astype(np.float32)
+    opts = [SampleOptions(repetition_penalty=1.3, presence_penalty=0.4, frequency_penalty=0.15),
+            SampleOptions(), SampleOptions(repetition_penalty=0.8, frequency_penalty=0.3)]
+    contexts = [rng.integers(0, V, size=n).tolist() for n in (400, 50, 7)]
+    want = logits.copy()
+    counts = []
+    for r in range(R):
+        apply_penalties(want[r], opts[r], contexts[r])
+        counts.append(torch.bincount(torch.tensor(contexts[r]), minlength=V).to(torch.int32).to(DEV))
+    ptrs = torch.tensor([c.data_ptr() if o.has_penalties else 0 for c, o in zip(counts, opts)], dtype=torch.int64).to(DEV)
+    params = torch.tensor([[o.repetition_penalty, o.presence_penalty, o.frequency_penalty] for o in opts])
+    dev = torch.from_numpy(logits).to(DEV)
+    K().sample_penalties(dev, ptrs, params.to(DEV))
+    assert np.array_equal(dev.cpu().numpy(), want)
+    # the chosen tokens join the counts of the rows that keep counts
+    ids = torch.tensor([5, 6, 7], dtype=torch.int32, device=DEV)
+    before = [int(c[t]) for c, t in zip(counts, (5, 6, 7))]
+    K().sample_count(ptrs, ids, V)
+    after = [int(c[t]) for c, t in zip(counts, (5, 6, 7))]
+    assert after == [before[0] + 1, before[1], before[2] + 1]
