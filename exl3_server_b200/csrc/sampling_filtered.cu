@@ -43,20 +43,56 @@ struct SfRow {            // one row's options, as the host gives them (float64 
 
 __global__ void __launch_bounds__(SF_THREADS)
 sample_filtered_kernel(const float* __restrict__ logits, const SfRow* __restrict__ rows, int* __restrict__ out, int V) {
-  __shared__ unsigned long long cand[SF_CAP];    // (key << 32) | ~index, sorted descending
+  // cand and acc hold nothing while the select runs: its histograms, one per warp, lie in their place.  (Logits
+  // crowd into a few bins of the leading byte, and additions to one address of shared memory go one after the
+  // other: with one histogram for the block the first pass alone took some 60 us.)
+  __shared__ __align__(16) unsigned char raw[SF_CAP * 16];
+  unsigned long long* cand = reinterpret_cast<unsigned long long*>(raw);       // (key << 32) | ~index, sorted descending
+  double* acc = reinterpret_cast<double*>(raw + SF_CAP * 8);                   // running sums of probs
+  unsigned (*whist)[256] = reinterpret_cast<unsigned (*)[256]>(raw);           // [warps][256]
+  static_assert(sizeof(unsigned) * 256 * (SF_THREADS / 32) <= sizeof(raw), "the warps' histograms fit");
   __shared__ float probs[SF_CAP];
-  __shared__ double acc[SF_CAP];                 // running sums of probs
   __shared__ unsigned hist[256];
   __shared__ double warp_tot[SF_THREADS / 32];
   __shared__ unsigned long long sel_prefix;
-  __shared__ unsigned sel_remaining, n_cand;
+  __shared__ unsigned sel_remaining, n_cand, same;
   __shared__ int first_below, first_hit, first_draw;
   const float* row = logits + (int64_t)blockIdx.x * V;
   const SfRow o = rows[blockIdx.x];
   const int tid = threadIdx.x;
   const int M = V < SF_CAP ? V : SF_CAP;
 
-  auto composite = [&](int i) { return ((unsigned long long)sf_key(row[i]) << 32) | (unsigned)(~(unsigned)i); };
+  // Every token's (value, inverted index) key.  One block reads its whole row several times over and an SM has
+  // only so many loads on their way: 16-byte loads, four of a thread at a time, make a pass a few round trips
+  // to L2 (rows start at any multiple of 4 bytes: the pieces before and after the aligned part go one by one).
+  auto key_of = [&](float v, int i) { return ((unsigned long long)sf_key(v) << 32) | (unsigned)(~(unsigned)i); };
+  const int head = min(V, (int)((4 - ((reinterpret_cast<uintptr_t>(row) >> 2) & 3)) & 3));
+  const int n_vec = (V - head) / 4;
+  const float4* row4 = reinterpret_cast<const float4*>(row + head);
+  auto for_each = [&](auto&& f) {
+    constexpr int AHEAD = 4;
+    for (int i = tid; i < head; i += SF_THREADS) f(key_of(row[i], i));
+    for (int j0 = tid; j0 < n_vec; j0 += SF_THREADS * AHEAD) {
+      float4 v[AHEAD];
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a) {
+        const int j = j0 + a * SF_THREADS;
+        v[a] = j < n_vec ? row4[j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a) {
+        const int j = j0 + a * SF_THREADS;
+        if (j < n_vec) {
+          const int i = head + 4 * j;
+          f(key_of(v[a].x, i));
+          f(key_of(v[a].y, i + 1));
+          f(key_of(v[a].z, i + 2));
+          f(key_of(v[a].w, i + 3));
+        }
+      }
+    }
+    for (int i = head + 4 * n_vec + tid; i < V; i += SF_THREADS) f(key_of(row[i], i));
+  };
 
   // ---- the M largest (value, then smaller index): radix select on the composite key -------------
   unsigned long long thresh = 0;                 // everything passes when the row is no longer than the cap
@@ -65,13 +101,18 @@ sample_filtered_kernel(const float* __restrict__ logits, const SfRow* __restrict
     __syncthreads();
     // the value's four bytes; the index's four only when tokens with the threshold's value are too many
     for (int shift = 56; shift >= 0; shift -= 8) {
-      for (int b = tid; b < 256; b += SF_THREADS) hist[b] = 0;
+      for (int b = tid; b < 256 * (SF_THREADS / 32); b += SF_THREADS) whist[0][b] = 0;
       __syncthreads();
       const unsigned long long prefix = sel_prefix;
       const unsigned long long mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
-      for (int i = tid; i < V; i += SF_THREADS) {
-        const unsigned long long c = composite(i);
-        if ((c & mask) == prefix) atomicAdd(&hist[(unsigned)(c >> shift) & 255u], 1u);
+      for_each([&](unsigned long long c) {
+        if ((c & mask) == prefix) atomicAdd(&whist[tid >> 5][(unsigned)(c >> shift) & 255u], 1u);
+      });
+      __syncthreads();
+      if (tid < 256) {
+        unsigned n = 0;
+        for (int w = 0; w < SF_THREADS / 32; ++w) n += whist[w][tid];
+        hist[tid] = n;
       }
       __syncthreads();
       if (tid == 0) {
@@ -83,33 +124,23 @@ sample_filtered_kernel(const float* __restrict__ logits, const SfRow* __restrict
         }
         sel_remaining = rem - cum;               // how many of this digit's tokens still pass
         sel_prefix = prefix | ((unsigned long long)digit << shift);
+        same = hist[digit];                      // after the value's last byte: the tokens with the threshold's value
       }
       __syncthreads();
-      // after the value's bytes: if all tokens with this value pass, their indices need no select
-      if (shift == 32) {
-        const unsigned long long p = sel_prefix;
-        __shared__ unsigned same;
-        if (tid == 0) same = 0;
-        __syncthreads();
-        unsigned mine = 0;
-        for (int i = tid; i < V; i += SF_THREADS) mine += ((composite(i) >> 32) == (p >> 32)) ? 1u : 0u;
-        if (mine) atomicAdd(&same, mine);
-        __syncthreads();
-        if (same == sel_remaining) break;        // the threshold is (value, any index): sel_prefix has index bits 0
-      }
+      // if all tokens with this value pass, their indices need no select: the threshold is (value, any index)
+      if (shift == 32 && same == sel_remaining) break;
     }
     thresh = sel_prefix;
   }
   if (tid == 0) n_cand = 0;
   for (int i = tid; i < SF_CAP; i += SF_THREADS) cand[i] = 0ull;   // padding sorts last
   __syncthreads();
-  for (int i = tid; i < V; i += SF_THREADS) {
-    const unsigned long long c = composite(i);
+  for_each([&](unsigned long long c) {
     if (c >= thresh) {
       const unsigned at = atomicAdd(&n_cand, 1u);
       if (at < (unsigned)SF_CAP) cand[at] = c;
     }
-  }
+  });
   __syncthreads();
 
   // ---- sorted descending: bitonic over the 2048 slots --------------------------------------------

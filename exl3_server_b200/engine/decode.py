@@ -232,7 +232,7 @@ class DecodeSession:
     """A fixed set of sequences that advance one token per step.
 
     ``step(tokens)`` feeds the given token ids (host) or, with ``None``, the
-    argmax of the previous step, which never leaves the device.  Pages are
+    argmax of the previous step (or what ``feed`` left in its place), which never leaves the device.  Pages are
     reserved as sequences cross page boundaries and the cache's lengths are
     kept in step.  ``fetch_ids()`` starts the copy of the last step's argmax to
     the host, so that the next step can be launched before the host looks at
@@ -308,12 +308,21 @@ class DecodeSession:
         """The argmax of the last step's logits, on the device."""
         return self.runner.next_ids[:len(self.slots)]
 
-    def fetch_ids(self) -> FetchedIds:
-        """Starts copying the last step's argmax to pinned host memory (it must
+    def feed(self, ids: torch.Tensor) -> None:
+        """The next ``step(None)`` runs these token ids (int32 on the device, one per sequence) instead of the
+        last step's argmax: tokens sampled on the device go on without a trip to the host."""
+        n = len(self.slots)
+        self.runner.token_ids.dev[:n].copy_(ids[:n])
+
+    def fetch_ids(self, ids: Optional[torch.Tensor] = None) -> FetchedIds:
+        """Starts copying the last step's argmax (or the given ids of that step) to pinned host memory (it must
         be asked for before the next step is launched, which overwrites it)."""
         host = self._pinned[self._fetches % len(self._pinned)]
         self._fetches += 1
-        host.copy_(self.runner.next_ids, non_blocking=True)
+        if ids is None:
+            host.copy_(self.runner.next_ids, non_blocking=True)
+        else:
+            host[:ids.numel()].copy_(ids, non_blocking=True)
         TRANSFERRED["d2h"] += host.numel() * 4
         ev = torch.cuda.Event()
         ev.record()

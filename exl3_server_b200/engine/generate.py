@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
 from ..sampling.options import SampleOptions
-from ..sampling.sampler import RowSampler, sample_rows
+from ..sampling.sampler import RowSampler, launch_on_device, on_device, record, sample_rows
 from .engine import StepEntry
 
 PAGE = 64
@@ -35,7 +35,7 @@ class GenerateOptions:
     ignore_eos: bool = False
     stop_token_ids: Optional[Sequence[int]] = None   # None: the model's eos ids
     max_batch: int = 64                         # most requests that start together
-    run_ahead: bool = True                      # greedy: launch step k + 1 before reading step k's tokens
+    run_ahead: bool = True                      # launch step k + 1 before reading step k's tokens (sampling on the device)
 
 
 @dataclass
@@ -146,8 +146,12 @@ def _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
         remaining = opt.max_tokens - min(results[i].completion_tokens for i in live)
         session = engine.decode_session([slots[i] for i in live], max_new=remaining + 1)
         greedy = all(samplers[i].opt.greedy and not samplers[i].opt.has_penalties for i in live)
-        if greedy and opt.run_ahead and hasattr(session, "fetch_ids"):
+        ahead = opt.run_ahead and hasattr(session, "fetch_ids")
+        if greedy and ahead:
             _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state)
+        elif ahead and on_device(logits, [samplers[i] for i in live]):
+            _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state,
+                          samplers=[samplers[i] for i in live])
         else:
             session = _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, cancelled, state)
     finally:
@@ -187,15 +191,23 @@ def _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, c
     return session
 
 
-def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, cancelled, state) -> None:
-    """Greedy decoding one step ahead of the host.  The argmax of a step feeds
-    the next step on the device, so step k + 1 is launched before the host has
-    seen the tokens of step k; the host reads them (pinned copy) and decides
-    who has ended while the GPU works.  A row that ended has run one step too
-    many into its own pages, is turned into padding, and its slot is freed."""
+def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, cancelled, state, samplers=None) -> None:
+    """Decoding one step ahead of the host.  The tokens of a step (its argmax, or with ``samplers`` what the
+    device sampler draws from its logits) feed the next step on the device, so step k + 1 is launched before
+    the host has seen the tokens of step k; the host reads them (pinned copy) and decides who has ended while
+    the GPU works.  A row that ended has run one step too many into its own pages, is turned into padding,
+    and its slot is freed."""
     alive = [True] * len(rows)
-    session.step(first_tokens)
-    pending = session.fetch_ids()
+
+    def launch(tokens):
+        logits = session.step(tokens)
+        if samplers is None:
+            return session.fetch_ids()
+        ids = launch_on_device(logits, samplers)         # rows that ended draw too; nobody reads their tokens
+        session.feed(ids)
+        return session.fetch_ids(ids)
+
+    pending = launch(first_tokens)
     while True:
         if cancelled is not None and cancelled():
             for r, i in enumerate(rows):
@@ -203,9 +215,10 @@ def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, can
                     results[i].finish_reason = "cancelled"
                     results[i].decode_seconds = time.perf_counter() - state["d0"]
             return
-        session.step(None)                      # launched before the pending tokens are looked at
-        following = session.fetch_ids()
+        following = launch(None)                # launched before the pending tokens are looked at
         toks = pending.get()
+        if samplers is not None:
+            record(samplers, toks)
         ended = [r for r, i in enumerate(rows) if alive[r] and emit(i, toks[r])]
         if ended:
             session.park(ended)

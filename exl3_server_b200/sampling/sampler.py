@@ -47,7 +47,18 @@ class RowSampler:
         self._counted += n
 
 
-def _on_device(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
+def on_device(logits: torch.Tensor, rows: Sequence[RowSampler]) -> bool:
+    """Whether ``launch_on_device`` takes this batch."""
+    if not logits.is_cuda:
+        return False
+    from ..ops import kernels as K
+    return all(r.opt.top_k <= K.sample_filtered_cap() for r in rows)
+
+
+def launch_on_device(logits: torch.Tensor, rows: Sequence[RowSampler]) -> torch.Tensor:
+    """Starts the sampling of one token per row on the device and returns the ids (int32 on the device)
+    without waiting for them.  The generators advance now; the tokens join the rows' contexts when the caller
+    has read them (``record``).  The penalties' token counts are kept up on the device."""
     from ..engine.decode import TRANSFERRED
     from ..ops import kernels as K
     R, V = logits.shape
@@ -70,8 +81,13 @@ def _on_device(logits: torch.Tensor, rows: Sequence[RowSampler]) -> List[int]:
             if r.opt.has_penalties:
                 r.counted()
     TRANSFERRED["h2d"] += opts.numel() * 8
-    TRANSFERRED["d2h"] += ids.numel() * 4
-    return ids.cpu().tolist()
+    return ids
+
+
+def record(rows: Sequence[RowSampler], picked: Sequence[int]) -> None:
+    """The rows' sampled tokens, read by the host, join their contexts."""
+    for r, t in zip(rows, picked):
+        r.context.append(int(t))
 
 
 def sample_rows(logits: torch.Tensor, rows: Sequence[RowSampler],
@@ -89,11 +105,13 @@ def sample_rows(logits: torch.Tensor, rows: Sequence[RowSampler],
             picked = ids.cpu().tolist()
             from ..engine.decode import TRANSFERRED
             TRANSFERRED["d2h"] += ids.numel() * 4
-        elif all(r.opt.top_k <= K.sample_filtered_cap() for r in rows):
-            picked = _on_device(logits.to(torch.float32), rows)
+        elif on_device(logits, rows):
+            ids = launch_on_device(logits.to(torch.float32), rows)
+            picked = ids.cpu().tolist()
+            from ..engine.decode import TRANSFERRED
+            TRANSFERRED["d2h"] += ids.numel() * 4
     if picked is None:
         host = logits.detach().to(torch.float32).cpu().numpy()
         picked = [sample_token(host[i], r.opt, r.context, r.rng) for i, r in enumerate(rows)]
-    for r, t in zip(rows, picked):
-        r.context.append(t)
+    record(rows, picked)
     return picked

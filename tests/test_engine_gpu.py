@@ -189,6 +189,23 @@ def test_temperature_sampling_is_seeded(model_folders):
     assert [r.tokens for r in other] != [r.tokens for r in a]
 
 
+def test_sampled_generation_is_the_same_one_step_ahead_of_the_host(model_folders):
+    """Sampled tokens feed the next step on the device; the host reads them a step later.  Requests of unequal
+    lengths that end on a stop token at different times: the same tokens as with the host in every step."""
+    from exl3_server_b200 import Engine, GenerateOptions, SampleOptions
+    eng = Engine.from_folder(model_folders["D"], dtype="bfloat16", max_tokens=2048)
+    prompts = [[1, 2, 3], [4, 5, 6, 7, 8, 9], [10], [11, 12]]
+    so = SampleOptions(temperature=0.9, top_k=50, top_p=0.95, repetition_penalty=1.15, frequency_penalty=0.05, seed=21)
+    runs = []
+    for ahead in (True, False):
+        opt = GenerateOptions(max_tokens=40, stop_token_ids=[17, 33, 52, 80, 101], sample=so, run_ahead=ahead)
+        runs.append(eng.generate(prompts, opt))
+        assert eng.cache.tokens_held() == 0
+    assert [r.tokens for r in runs[0]] == [r.tokens for r in runs[1]]
+    assert [r.finish_reason for r in runs[0]] == [r.finish_reason for r in runs[1]]
+    assert len({len(r.tokens) for r in runs[0]}) > 1 or all(r.finish_reason == "length" for r in runs[0])
+
+
 def test_sampling_on_the_device_follows_the_host_sampler():
     """The same requests sampled from logits on the device and from a copy on the host: filters, penalties over
     the growing context, a greedy row among them, every request with its own generator."""
