@@ -38,6 +38,13 @@ BENCH_MODEL = dict(hidden_size=2304, num_hidden_layers=40, num_attention_heads=3
                    rope_theta=10000.0, rms_norm_eps=1e-5, scale_emb=12.0, scale_depth=1.4, dim_model_base=256,
                    max_position_embeddings=0, model_type="minicpm", architectures=["MiniCPMForCausalLM"])
 FULL_LAYERS = 40
+# Other layer sizes for looking at the kernels away from the headline configuration (--sizes); the default run and
+# its JSON line are the MiniCPM-2B ones above.
+OTHER_SIZES = {
+    "llama-8b-like": (dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                           head_dim=128, intermediate_size=14336, vocab_size=128256, tie_word_embeddings=False,
+                           rope_theta=500000.0, rms_norm_eps=1e-5, max_position_embeddings=0), 32),
+}
 
 
 def peaks():
@@ -110,6 +117,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (stated in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and batch 64 decode points")
+    ap.add_argument("--sizes", choices=["minicpm-2b"] + sorted(OTHER_SIZES), default="minicpm-2b",
+                    help="layer sizes; other than the default only with --only (a short JSON line)")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="run one part only (for profiling small cases); prints a short JSON line")
     args = ap.parse_args()
@@ -121,6 +130,9 @@ def main() -> int:
         return 0
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.sizes != "minicpm-2b" and args.only == "all":
+        print("bench.py: --sizes other than minicpm-2b needs --only decode or --only prefill")
         return 2
     if args.warmup < 3:
         args.warmup = 3
@@ -137,7 +149,12 @@ def main() -> int:
     torch.cuda.set_device(dev)
     hbm_gbs, bf16_tf, peak_src = peaks()
 
-    cfg = E.LlamaConfig(**{**BENCH_MODEL, "num_hidden_layers": args.layers})
+    if args.sizes != "minicpm-2b":
+        sizes, full = OTHER_SIZES[args.sizes]
+        cfg = E.LlamaConfig(**{**sizes, "num_hidden_layers": min(args.layers, full)})
+        args.layers = cfg.num_hidden_layers
+    else:
+        cfg = E.LlamaConfig(**{**BENCH_MODEL, "num_hidden_layers": args.layers})
     # the residual scale belongs to the 40-layer model whatever --layers says
     plan = build_plan(cfg)
     t0 = time.time()
@@ -189,7 +206,7 @@ def main() -> int:
 
     if args.only == "decode":
         ms, launches, _ = time_decode(B, C, Kst, W)
-        print(json.dumps({"only": "decode", "batch": B, "context": C, "layers": args.layers,
+        print(json.dumps({"only": "decode", "sizes": args.sizes, "batch": B, "context": C, "layers": args.layers,
                           "ms_per_step": ms / Kst, "tok_s": B * Kst / (ms / 1e3), "gpu_launches": int(launches)}))
         return 0
     if args.only == "prefill":
@@ -206,7 +223,8 @@ def main() -> int:
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / Kst
-        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "layers": args.layers, "ms": ms,
+        print(json.dumps({"only": "prefill", "sizes": args.sizes, "tokens": args.prefill_tokens, "layers": args.layers,
+                          "ms": ms,
                           "tok_s": args.prefill_tokens / (ms / 1e3)}))
         return 0
 

@@ -23,10 +23,7 @@ def _configs():
     from exl3_server_b200 import LlamaConfig
     return {
         "minicpm-2b": LlamaConfig(**{**bench.BENCH_MODEL, "num_hidden_layers": 2}),
-        "llama-8b-like": LlamaConfig(
-            hidden_size=4096, num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-            intermediate_size=14336, vocab_size=128256, tie_word_embeddings=False, rope_theta=500000.0,
-            rms_norm_eps=1e-5, max_position_embeddings=8192),
+        "llama-8b-like": LlamaConfig(**{**bench.OTHER_SIZES["llama-8b-like"][0], "num_hidden_layers": 2}),
     }
 
 
