@@ -59,3 +59,22 @@ def test_candidate_cap_of_2048():
     g = SplitMix64(3)
     picks = {sample_token(logits, SampleOptions(temperature=50.0), [], g) for _ in range(3000)}
     assert picks <= allowed and len(picks) > 1000
+
+
+def test_equal_logits_rank_by_index():
+    # 3000 tokens share the largest value: the candidates are the 2048 with the smallest indices, in index order
+    logits = np.zeros(5000, dtype=np.float32)
+    logits[1000:4000] = 1.0
+
+    class U:
+        def __init__(self, u):
+            self.u = u
+
+        def uniform01(self):
+            return self.u
+
+    opt = SampleOptions(temperature=1.0)
+    assert sample_token(logits, opt, [], U(0.0)) == 1000
+    assert sample_token(logits, opt, [], U(0.999999)) == 1000 + 2047
+    assert sample_token(logits, opt, [], U(0.5)) in (1000 + 1023, 1000 + 1024)
+    assert sample_token(logits, SampleOptions(temperature=1.0, top_k=3), [], U(0.99)) == 1002
