@@ -45,7 +45,8 @@ __global__ void __launch_bounds__(SF_THREADS)
 sample_filtered_kernel(const float* __restrict__ logits, const SfRow* __restrict__ rows, int* __restrict__ out, int V) {
   // cand and acc hold nothing while the select runs: its histograms, one per warp, lie in their place.  (Logits
   // crowd into a few bins of the leading byte, and additions to one address of shared memory go one after the
-  // other: with one histogram for the block the first pass alone took some 60 us.)
+  // other; a histogram per warp keeps the warps apart.  Measured, it made no difference to the kernel's time: the
+  // passes over the row through one SM's memory pipe are what it costs.)
   __shared__ __align__(16) unsigned char raw[SF_CAP * 16];
   unsigned long long* cand = reinterpret_cast<unsigned long long*>(raw);       // (key << 32) | ~index, sorted descending
   double* acc = reinterpret_cast<double*>(raw + SF_CAP * 8);                   // running sums of probs
