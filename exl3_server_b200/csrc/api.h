@@ -69,7 +69,7 @@ int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, 
 // exl3_gemv_bf16 as the two sides of a norm that is no kernel of its own.  With ss_in the input is the x_raw of a
 // producing call and the results are multiplied by rsqrt(sum of ss_in's blocks / width + eps) per batch row.
 // With epilogue 2 no y is written: h[M, N] += result * rho, x_raw = h * norm_w, ss_out[16, ceil(N / 16)] = sums of
-// squares per batch row and block.  See gemv_bf16.cu.
+// squares per batch row and block.  See gemv_bf16.cuh.
 int exl3_gemv_bf16_normed(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N,
                           int K, int epilogue, const float* ss_in, int ss_blocks, float eps, float width, float* h,
                           float rho, const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out,

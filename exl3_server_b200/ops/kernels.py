@@ -206,7 +206,7 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 
 def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
                      gated: bool = False, scale=None, resid=None):
-    """``gemv_bf16`` as one or both sides of a norm that is no kernel of its own (see gemv_bf16.cu).
+    """``gemv_bf16`` as one or both sides of a norm that is no kernel of its own (see gemv_bf16.cuh).
 
     ``scale = (ss, eps, width)``: ``x`` is the ``x_raw`` of a producing call; results are multiplied per batch row
     by ``rsqrt(ss.sum(1) / width + eps)`` before bias and gating.
