@@ -64,3 +64,18 @@ def test_forward_prefix_property(model_folders):
     ids = list(range(3, 60))
     full = pm.logits(ids)
     assert torch.allclose(pm.logits(ids[:31]), full[:31], atol=1e-12)
+
+
+def test_rotary_table_keeps_what_float32_loses():
+    """The kernels' frequency table: two float32 rows whose sum is the float64 frequency to about 1e-15 of it, so
+    that position * frequency keeps its accuracy at large positions."""
+    import torch
+    from exl3_server_b200.ops.kernels import rotary_table
+    f = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -2.0 * torch.arange(0, 64, dtype=torch.float64) / 128)
+    t = rotary_table(f)
+    assert t.dtype == torch.float32 and tuple(t.shape) == (2, 64) and t.is_contiguous()
+    back = t[0].double() + t[1].double()
+    assert float(((back - f).abs() / f).max()) < 1e-14
+    assert float(((t[0].double() - f).abs() / f).max()) > 1e-9          # the first row alone is float32
+    pos = 150001.0
+    assert float((pos * back - pos * f).abs().max()) < 1e-9
