@@ -101,6 +101,11 @@ class SequenceCache:
                     src_req = self.groups[self.entry_group[src][0]].request
                     if (kv.kv_heads, kv.head_dim) != (src_req.kv_heads, src_req.head_dim):
                         raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: head shapes differ")
+                    # the owner gives back the pages its own window no longer reaches: a reader that looks
+                    # further back would find them gone (the kernels skip pages that are not there)
+                    if src_req.window > 0 and not 0 < kv.window <= src_req.window:
+                        raise CacheError(f"schedule entry {i} (window {kv.window or 'none'}) cannot read entry "
+                                         f"{src}'s cache, which keeps only a window of {src_req.window}")
                 self.entry_group.append(self.entry_group[src])
                 self.entry_owns.append(False)
                 continue
@@ -191,6 +196,11 @@ class SequenceCache:
                     pages[i] = -1
                 any_gone = True
         return any_gone
+
+    def gives_back_at(self, length: int) -> bool:
+        """Whether a sequence that has just reached ``length`` has a page to give back that it still needed
+        at ``length - 1`` (only groups with a window ever do)."""
+        return any(g.first_needed_page(length) != g.first_needed_page(length - 1) for g in self.groups)
 
     def truncate(self, slot: int, new_len: int) -> None:
         """Forgets the positions from ``new_len`` on (the reference's

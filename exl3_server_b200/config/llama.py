@@ -13,7 +13,8 @@ read here: ``scale_emb`` multiplies the embedding, ``scale_depth / sqrt(layers)`
 multiplies every sublayer output before the residual add, and the normed hidden
 state is divided by ``hidden_size / dim_model_base`` before the head.  Absent
 keys give factors of one, which is the reference's arithmetic.  Also read:
-``tie_word_embeddings``, ``sliding_window`` with ``layer_types`` (a window of
+``tie_word_embeddings`` (absent: the head is tied exactly when the checkpoint has no ``lm_head.weight``),
+``sliding_window`` with ``layer_types`` (a window of
 keys for the layers marked ``"sliding_attention"``), ``hidden_act`` (must be
 ``"silu"``: the reference applies SiLU unconditionally, src/model.cpp:585).
 """
@@ -45,7 +46,7 @@ class LlamaConfig:
     scale_emb: float = 1.0
     scale_depth: Optional[float] = None   # None: sublayer outputs are not scaled
     dim_model_base: int = 0               # 0: hidden_size (divisor 1)
-    tie_word_embeddings: bool = False
+    tie_word_embeddings: Optional[bool] = None   # None: tied iff the checkpoint has no lm_head.weight
     sliding_window: Optional[int] = None
     layer_types: Optional[List[str]] = None
     model_type: str = "llama"
@@ -68,8 +69,9 @@ class LlamaConfig:
             raise ConfigError(
                 "config.json: num_attention_heads (%d) is not a multiple of num_key_value_heads (%d)"
                 % (self.num_attention_heads, self.num_key_value_heads))
-        if self.head_dim % 2 != 0:
-            raise ConfigError(f"config.json: head_dim must be even for rotary embedding, got {self.head_dim}")
+        if self.head_dim % 16 != 0:
+            # the rotation needs an even size; this engine's attention kernels take heads in steps of 16
+            raise ConfigError(f"config.json: key 'head_dim' must be a multiple of 16, got {self.head_dim}")
         if not self.rms_norm_eps > 0:
             raise ConfigError("config.json: key 'rms_norm_eps' must be > 0")
         if not self.rope_theta > 0:
@@ -138,7 +140,7 @@ class LlamaConfig:
             scale_emb=r.number("scale_emb", 1.0),
             scale_depth=r.number("scale_depth", None),
             dim_model_base=r.integer("dim_model_base", 0, minimum=0),
-            tie_word_embeddings=r.boolean("tie_word_embeddings", False),
+            tie_word_embeddings=r.boolean("tie_word_embeddings", None),
             sliding_window=r.integer("sliding_window", None),
             layer_types=layer_types,
             model_type=r.string("model_type", "llama"),
@@ -162,8 +164,9 @@ class LlamaConfig:
             "hidden_act": "silu",
             "scale_emb": self.scale_emb,
             "dim_model_base": self.dim_model_base,
-            "tie_word_embeddings": self.tie_word_embeddings,
         }
+        if self.tie_word_embeddings is not None:
+            d["tie_word_embeddings"] = self.tie_word_embeddings
         if self.scale_depth is not None:
             d["scale_depth"] = self.scale_depth
         if self.bos_token_id is not None:

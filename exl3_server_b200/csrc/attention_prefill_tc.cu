@@ -1,7 +1,7 @@
 // Causal grouped-query attention of whole prompts over the paged cache on the
 // 5th-generation tensor cores (heads of 64 or 128, bfloat16, pages of 64 keys).
 //
-// Same mathematics as attention_prefill.cu and attention_simt.cu (the
+// Same mathematics as attention_simt.cu (the
 // reference's masked scaled-dot-product attention, src/model.cpp:539-548,
 // 576-578).  A block owns 128 consecutive queries of one sequence and one head
 // and walks the key pages its queries may see:

@@ -18,16 +18,25 @@ QUERY_TILES = (128,)        # queries per block of the tensor-core prefill atten
 
 
 class Workspace:
-    """Scratch memory for kernels, owned by the engine and grown on demand."""
+    """Scratch memory for kernels, owned by the engine and grown on demand.
 
-    def __init__(self, device):
+    ``keep_outgrown``: a buffer that became too small stays alive beside its larger successor.  Recorded CUDA
+    graphs hold the address of the buffer they were recorded with, so a workspace that graphs use must never
+    free one (a decode runner records a graph per context bucket, and a later bucket may need more scratch
+    than an earlier one)."""
+
+    def __init__(self, device, keep_outgrown: bool = False):
         self.device = device
+        self.keep_outgrown = keep_outgrown
         self._buf: Optional[torch.Tensor] = None
+        self._outgrown: List[torch.Tensor] = []
 
     def floats(self, n: int) -> torch.Tensor:
         # zeroed when made: the attention kernel keeps counters in it that must start at zero
         # (and returns them to zero itself)
         if self._buf is None or self._buf.numel() < n:
+            if self._buf is not None and self.keep_outgrown:
+                self._outgrown.append(self._buf)
             self._buf = torch.zeros(max(n, 1 << 16), dtype=torch.float32, device=self.device)
         return self._buf
 

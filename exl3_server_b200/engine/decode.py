@@ -81,12 +81,13 @@ class DecodeRunner:
         self.tok_seq = torch.arange(rows, dtype=torch.int32, device=dev)
         self.row_start = torch.arange(rows + 1, dtype=torch.int32, device=dev)
         self.next_ids = torch.zeros(rows, dtype=torch.int32, device=dev)
-        self.workspace = Workspace(dev)
+        self.workspace = Workspace(dev, keep_outgrown=True)   # graphs keep the addresses they were recorded with
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_logits: Dict[int, torch.Tensor] = {}
         self.launches: Dict[int, int] = {}
         self.last_bucket = 0
         self.pool = None
+        self.holder = None                     # weak reference to the decode session that owns the buffers' contents
         # an all-padding batch of the same shape, for the eager pass before recording
         self.pad_pos = torch.zeros(rows, dtype=torch.int32, device=dev)
         self.pad_slots = torch.full((rows,), cache.pad_slot, dtype=torch.int32, device=dev)
@@ -205,16 +206,24 @@ class DecodeRunner:
             self.tables[gi].upload()
 
 
-def runner_for(engine, n_rows: int, max_len: int) -> DecodeRunner:
-    """The engine's runner for at least ``n_rows`` rows and contexts of up to
-    ``max_len`` tokens (made on first use, kept for later steps)."""
+def runner_for(engine, n_rows: int, max_len: int, holder=None) -> DecodeRunner:
+    """One of the engine's runners for at least ``n_rows`` rows and contexts of up to ``max_len`` tokens
+    (made on first use, kept for later steps).  A runner's device buffers (positions, slots, page tables,
+    tokens) belong to one user at a time: a decode session passes itself as ``holder`` and keeps the runner
+    until it is closed or dropped; anyone else gets a runner that no live session holds (a second one of the
+    same shape is made when needed) and must be done with it before control returns to the caller."""
     rows = _pow2(max(1, n_rows))
     page = engine.cache.page_size
     width = _pow2(max(16, (max_len + page - 1) // page))
-    key = (rows, width)
-    if key not in engine.decode_runners:
-        engine.decode_runners[key] = DecodeRunner(engine, rows, width)
-    return engine.decode_runners[key]
+    pool = engine.decode_runners.setdefault((rows, width), [])
+    for runner in pool:
+        if runner.holder is None or runner.holder() is None or runner.holder() is holder:
+            break
+    else:
+        runner = DecodeRunner(engine, rows, width)
+        pool.append(runner)
+    runner.holder = weakref.ref(holder) if holder is not None else None
+    return runner
 
 
 class FetchedIds:
@@ -245,10 +254,11 @@ class DecodeSession:
         cache = engine.cache
         self.lens = [cache.length(s) for s in self.slots]
         horizon = max(self.lens) + (max_new if max_new > 0 else 4 * SPLIT_BUCKET)
-        self.runner = runner_for(engine, len(self.slots), horizon)
+        self.runner = runner_for(engine, len(self.slots), horizon, holder=self)
         self._reserve()
         self.runner.load(self.slots, self.lens, first_tokens)
         self.launches_per_step = 0
+        self.closed = False
         self._pinned = [torch.zeros(self.runner.rows, dtype=torch.int32).pin_memory() for _ in range(4)]
         self._fetches = 0
 
@@ -270,14 +280,21 @@ class DecodeSession:
     def step(self, tokens: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Runs one token per sequence; returns the logits ``[n, vocab]`` of
         the sequences (valid until the next step)."""
+        if self.closed:
+            raise RuntimeError("decode session: step after close")
         cache = self.engine.cache
         page = cache.page_size
         longest = max([n for n, s in zip(self.lens, self.slots) if s is not None] + [0])
+        limit = self.engine.model.plan.max_positions
+        if limit and longest + 1 > limit:
+            from .engine import StepError
+            raise StepError(f"decode session: {longest + 1} positions exceed max_position_embeddings {limit}")
         if longest + 1 > self.runner.width * page:
             if tokens is None:
                 raise RuntimeError("decode session: contexts outgrew the page table while tokens are fed "
                                    "on the device; give max_new when the session is made")
-            self.runner = runner_for(self.engine, len(self.slots), longest + 4 * SPLIT_BUCKET)
+            self.runner.holder = None
+            self.runner = runner_for(self.engine, len(self.slots), longest + 4 * SPLIT_BUCKET, holder=self)
             self._reserve()
             self.runner.load(self.slots, self.lens, None)
         else:
@@ -293,8 +310,8 @@ class DecodeSession:
             if s is None:
                 continue
             self.lens[r] += 1
-            if self.lens[r] % page == 0:
-                if cache.commit(s, self.lens[r]):          # a windowed group gave pages back
+            if cache.gives_back_at(self.lens[r]):
+                if cache.commit(s, self.lens[r]):          # a windowed group gave a page back
                     shrunk[r] = s
             else:
                 cache.lengths[s] = self.lens[r]
@@ -342,7 +359,11 @@ class DecodeSession:
         self.runner.load(self.slots, self.lens, None)
 
     def close(self) -> None:
+        """Records the sequences' lengths in the cache and lets go of the runner."""
         cache = self.engine.cache
         for s, n in zip(self.slots, self.lens):
             if s is not None and cache.slots.is_live(s):
                 cache.commit(s, n)
+        if self.runner.holder is not None and self.runner.holder() is self:
+            self.runner.holder = None
+        self.closed = True

@@ -59,7 +59,7 @@ def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", devi
     arch = resolve_architecture(obj)
     cfg = arch.config_class.from_dict(obj)
     plan = arch.build_plan(cfg)
-    tensors = load_tensors(model_dir, plan_manifest(plan), dt, device)
+    tensors = load_tensors(model_dir, plan_manifest(plan), dt, device, ignorable=plan.ignorable)
     model = Model(plan, tensors, dt, device)
     model.config = cfg
     return model
@@ -93,6 +93,11 @@ class Engine:
     def cache_tokens(self) -> int:
         return self.cache.max_tokens
 
+    @property
+    def max_positions(self) -> int:
+        """The most positions a sequence may have (0: no limit given by the configuration)."""
+        return int(self.model.plan.max_positions or 0)
+
     def generate(self, prompts, options=None, cancelled=None, on_token=None):
         """See ``engine.generate.generate``."""
         from .generate import generate
@@ -113,6 +118,13 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def truncate(self, slot: int, new_len: int) -> None:
+        """Forgets the sequence's positions from ``new_len`` on; the next step of the slot feeds the token at
+        that position (the reference rewinds a cache this way to reuse a prompt's prefix,
+        src/engine.cpp:244-262, src/model.cpp:630-650).  Refused for sequences with fixed-size state and for
+        windowed groups that already gave back pages needed at that length."""
+        self.cache.truncate(slot, new_len)
 
     def _decode_step(self, slots, starts, toks, wants) -> Optional[torch.Tensor]:
         """One token per entry: the recorded decode graph runs it (the same
@@ -178,6 +190,8 @@ class Engine:
                 w = [int(x) for x in e.want]
                 if any(not 0 <= x < len(t) for x in w):
                     raise StepError(f"slot {e.slot}: wanted place outside the {len(t)} tokens of this step")
+                if len(set(w)) != len(w):
+                    raise StepError(f"slot {e.slot}: a place is wanted twice in one step")
             slots.append(e.slot)
             starts.append(start)
             toks.append(t)

@@ -48,10 +48,12 @@ class GenerateResult:
     decode_seconds: float = 0.0
 
 
-def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, cache_tokens: int) -> List[List[int]]:
+def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, cache_tokens: int,
+                 max_positions: int = 0) -> List[List[int]]:
     """Splits request indices, in order, into batches that fit the cache: a
     request may grow to its prompt plus ``max_tokens`` tokens, counted in whole
-    pages."""
+    pages.  With ``max_positions`` a request that could grow beyond the model's positions is refused here,
+    before anything runs, as the step function would refuse it later."""
     def need(n: int) -> int:
         # one token more than asked for: greedy decoding runs one step ahead of the host
         return (n + max_tokens + 1 + PAGE - 1) // PAGE * PAGE
@@ -62,6 +64,8 @@ def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, ca
     for i, n in enumerate(prompt_lens):
         if n == 0:
             continue                              # answered without a forward pass
+        if max_positions and n + max_tokens > max_positions:
+            raise ValueError(f"request {i}: {n + max_tokens} positions exceed max_position_embeddings {max_positions}")
         if need(n) > cache_tokens:
             raise ValueError(f"request {i}: {n} prompt + {max_tokens} new tokens do not fit a cache of "
                              f"{cache_tokens} tokens")
@@ -90,7 +94,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
         if len(p) == 0 or opt.max_tokens == 0:
             results[i].finish_reason = "stop" if len(p) == 0 else "length"   # src/engine.cpp:227-230
     todo = [len(p) if opt.max_tokens > 0 else 0 for p in prompts]
-    for batch in plan_batches(todo, opt.max_tokens, opt.max_batch, engine.cache_tokens):
+    for batch in plan_batches(todo, opt.max_tokens, opt.max_batch, engine.cache_tokens,
+                              getattr(engine, "max_positions", 0)):
         _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
         check = getattr(engine, "check_kernels", None)
         if check is not None:
@@ -148,10 +153,11 @@ def _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
         greedy = all(samplers[i].opt.greedy and not samplers[i].opt.has_penalties for i in live)
         ahead = opt.run_ahead and hasattr(session, "fetch_ids")
         if greedy and ahead:
-            _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state)
+            _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state,
+                          opt.max_tokens)
         elif ahead and on_device(logits, [samplers[i] for i in live]):
             _decode_ahead(engine, session, live, [t for _, t in nxt], slots, results, emit, cancelled, state,
-                          samplers=[samplers[i] for i in live])
+                          opt.max_tokens, samplers=[samplers[i] for i in live])
         else:
             session = _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, cancelled, state)
     finally:
@@ -191,12 +197,14 @@ def _decode_in_step(engine, session, nxt, slots, samplers, results, opt, emit, c
     return session
 
 
-def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, cancelled, state, samplers=None) -> None:
+def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, cancelled, state, max_tokens,
+                  samplers=None) -> None:
     """Decoding one step ahead of the host.  The tokens of a step (its argmax, or with ``samplers`` what the
     device sampler draws from its logits) feed the next step on the device, so step k + 1 is launched before
     the host has seen the tokens of step k; the host reads them (pinned copy) and decides who has ended while
-    the GPU works.  A row that ended has run one step too many into its own pages, is turned into padding,
-    and its slot is freed."""
+    the GPU works.  A row that ended on a stop token has run one step too many into its own pages, is turned
+    into padding, and its slot is freed.  When the tokens on their way are the last that ``max_tokens`` allows
+    to every live row, no step is launched ahead of them: only an unforeseen stop token costs a step."""
     alive = [True] * len(rows)
 
     def launch(tokens):
@@ -215,16 +223,18 @@ def _decode_ahead(engine, session, rows, first_tokens, slots, results, emit, can
                     results[i].finish_reason = "cancelled"
                     results[i].decode_seconds = time.perf_counter() - state["d0"]
             return
-        following = launch(None)                # launched before the pending tokens are looked at
+        last = all(results[i].completion_tokens + 1 >= max_tokens for r, i in enumerate(rows) if alive[r])
+        following = None if last else launch(None)    # launched before the pending tokens are looked at
         toks = pending.get()
         if samplers is not None:
             record(samplers, toks)
         ended = [r for r, i in enumerate(rows) if alive[r] and emit(i, toks[r])]
-        if ended:
-            session.park(ended)
-            for r in ended:
-                alive[r] = False
-                engine.close(slots.pop(rows[r]))
+        for r in ended:
+            alive[r] = False
+        if ended and any(alive):
+            session.park(ended)                       # the others go on; nothing to re-arrange when all have ended
+        for r in ended:
+            engine.close(slots.pop(rows[r]))
         if not any(alive):
             return
         pending = following

@@ -14,8 +14,8 @@ import torch
 
 from ..cache.kv import SequenceCache
 from ..parts.base import BuildContext, KVRequest, StateRequest
-from ..parts.embedding import Embedding, Head
-from ..parts.registry import arrangement_class, feed_forward_class, mixer_class, norm_class
+from ..parts.registry import (arrangement_class, embedding_class, feed_forward_class, head_class, mixer_class,
+                              norm_class)
 from ..parts.spec import ModelPlan
 from ..weights.loader import TensorSpec
 from .batch import StepBatch
@@ -23,7 +23,7 @@ from .batch import StepBatch
 
 def plan_manifest(plan: ModelPlan) -> List[TensorSpec]:
     """Every tensor the plan's parts will ask for, by checkpoint name."""
-    specs: List[TensorSpec] = list(Embedding.tensor_specs(plan.embedding))
+    specs: List[TensorSpec] = list(embedding_class(plan.embedding.kind).tensor_specs(plan.embedding))
     for layer in plan.layers:
         specs += mixer_class(layer.mixer.kind).tensor_specs(layer.mixer, layer.names["mixer"])
         specs += feed_forward_class(layer.feed_forward.kind).tensor_specs(layer.feed_forward,
@@ -32,7 +32,7 @@ def plan_manifest(plan: ModelPlan) -> List[TensorSpec]:
         specs += norm_class(layer.feed_forward_norm.kind).tensor_specs(layer.feed_forward_norm,
                                                                       layer.names["feed_forward_norm"])
     specs += norm_class(plan.final_norm.kind).tensor_specs(plan.final_norm, plan.final_norm_name)
-    specs += Head.tensor_specs(plan.head)
+    specs += head_class(plan.head.kind).tensor_specs(plan.head)
     return specs
 
 
@@ -43,7 +43,7 @@ class Model:
         self.dtype = dtype
         self.device = torch.device(device)
         ctx = BuildContext(dtype=dtype, device=self.device)
-        self.embedding = Embedding(plan.embedding, tensors, ctx)
+        self.embedding = embedding_class(plan.embedding.kind)(plan.embedding, tensors, ctx)
         self.blocks = []
         for layer in plan.layers:
             mixer = mixer_class(layer.mixer.kind)(layer.mixer, tensors, layer.names["mixer"], ctx)
@@ -54,7 +54,7 @@ class Model:
                                                           layer.names["feed_forward_norm"], ctx)
             self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2))
         self.final_norm = norm_class(plan.final_norm.kind)(plan.final_norm, tensors, plan.final_norm_name, ctx)
-        self.head = Head(plan.head, tensors, self.embedding, ctx)
+        self.head = head_class(plan.head.kind)(plan.head, tensors, self.embedding, ctx)
         self.vocab = plan.head.vocab
 
     def cache_requests(self) -> List[Tuple[Optional[KVRequest], Optional[StateRequest], Optional[int]]]:
@@ -89,5 +89,5 @@ class Model:
         reads the embedding table)."""
         n = sum(self.blocks[e.layer].weight_bytes() for e in self.plan.schedule)
         n += self.final_norm.weight_bytes()
-        n += self.head.linear.weight_bytes()
+        n += self.head.read_bytes()
         return n

@@ -48,6 +48,7 @@ def build_plan(cfg: LlamaConfig) -> ModelPlan:
         max_positions=cfg.max_position_embeddings,
         stop_token_ids=list(cfg.eos_token_id),
         bos_token_id=cfg.bos_token_id,
+        ignorable=["*.rotary_emb.inv_freq"],      # stored by older exporters; the angles are computed here
     )
     plan.validate()
     return plan

@@ -5,6 +5,11 @@ scale is MiniCPM's ``scale_emb``).  Head: ``logits = (norm(h) / divisor) W^T``
 in float32, computed only for the rows that were asked for (the reference
 computes every row, src/model.cpp:589-592); ``W`` is the embedding table when
 the head is tied.
+
+Both are registered part kinds like the others (``"table"`` and ``"linear"``).  An embedding of another kind has
+``tensor_specs(spec)``, ``__init__(spec, tensors, ctx)`` and ``forward(token_ids) -> ResidualStream``; a head has
+``tensor_specs(spec)``, ``__init__(spec, tensors, embedding, ctx)``, ``forward(stream, final_norm, rows) ->
+float32 logits [rows, vocab]`` and ``read_bytes()``, the weight bytes a step reads.
 """
 from __future__ import annotations
 
@@ -16,6 +21,7 @@ from ..ops import kernels as K
 from ..weights.loader import TensorSpec
 from .base import BuildContext, ResidualStream
 from .linear import Linear
+from .registry import register_embedding, register_head
 from .spec import EmbeddingSpec, HeadSpec
 
 
@@ -38,13 +44,17 @@ class Embedding:
 class Head:
     @staticmethod
     def tensor_specs(spec: HeadSpec) -> List[TensorSpec]:
-        return [] if spec.tied else [TensorSpec(spec.name, (spec.vocab, spec.width))]
+        if spec.tied:
+            return []
+        # tied None: the configuration does not say; a head of its own is used when the checkpoint has one
+        return [TensorSpec(spec.name, (spec.vocab, spec.width), optional=spec.tied is None)]
 
     def __init__(self, spec: HeadSpec, tensors: Dict[str, torch.Tensor], embedding: Embedding, ctx: BuildContext):
         self.spec = spec
-        weight = embedding.table if spec.tied else tensors[spec.name]
+        self.tied = spec.tied if spec.tied is not None else spec.name not in tensors
+        weight = embedding.table if self.tied else tensors[spec.name]
         self.linear = Linear(weight, None, ctx.dtype)
-        if spec.tied:
+        if self.tied:
             self.linear.weight = embedding.table          # one copy in memory
 
     def forward(self, stream: ResidualStream, final_norm, rows: Optional[torch.Tensor]) -> torch.Tensor:
@@ -52,4 +62,13 @@ class Head:
         return self.linear(r, out_dtype=torch.float32)
 
     def weight_bytes(self) -> int:
-        return 0 if self.spec.tied else self.linear.weight_bytes()
+        """Bytes this part holds beyond the embedding's."""
+        return 0 if self.tied else self.linear.weight_bytes()
+
+    def read_bytes(self) -> int:
+        """Weight bytes a step reads for the logits (a tied head reads the embedding table)."""
+        return self.linear.weight_bytes()
+
+
+register_embedding("table", Embedding)
+register_head("linear", Head)

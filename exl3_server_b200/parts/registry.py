@@ -2,7 +2,7 @@
 
 A part is looked up by the ``kind`` string of its spec.  The framework's own
 parts register themselves on import; a caller adds another mixer,
-feed-forward, norm, position encoding or block arrangement with the matching
+feed-forward, norm, position encoding, block arrangement, embedding or head with the matching
 ``register_*`` function and names it in a plan.  No framework file has to
 change for that.
 """
@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Any, Callable, Dict
 
-_KINDS = ("norm", "position", "mixer", "feed_forward", "arrangement")
+_KINDS = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
 _TABLES: Dict[str, Dict[str, Any]] = {k: {} for k in _KINDS}
 
 
@@ -31,6 +31,8 @@ def register_position(kind: str, cls: Any) -> Any: return _register("position", 
 def register_mixer(kind: str, cls: Any) -> Any: return _register("mixer", kind, cls)
 def register_feed_forward(kind: str, cls: Any) -> Any: return _register("feed_forward", kind, cls)
 def register_arrangement(kind: str, cls: Any) -> Any: return _register("arrangement", kind, cls)
+def register_embedding(kind: str, cls: Any) -> Any: return _register("embedding", kind, cls)
+def register_head(kind: str, cls: Any) -> Any: return _register("head", kind, cls)
 
 
 def norm_class(kind: str) -> Any: return _lookup("norm", kind)
@@ -38,6 +40,8 @@ def position_class(kind: str) -> Any: return _lookup("position", kind)
 def mixer_class(kind: str) -> Any: return _lookup("mixer", kind)
 def feed_forward_class(kind: str) -> Any: return _lookup("feed_forward", kind)
 def arrangement_class(kind: str) -> Any: return _lookup("arrangement", kind)
+def embedding_class(kind: str) -> Any: return _lookup("embedding", kind)
+def head_class(kind: str) -> Any: return _lookup("head", kind)
 
 
 def unregister(table: str, kind: str) -> None:

@@ -81,6 +81,8 @@ class EmbeddingSpec:
     width: int
     scale: float
     name: str
+    kind: str = "table"           # registered embedding name
+    params: Dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
@@ -88,8 +90,11 @@ class HeadSpec:
     vocab: int
     width: int
     input_divisor: float          # the normed hidden state is divided by this
-    tied: bool                    # True: the embedding table is the head's weight
+    tied: Optional[bool]          # True: the embedding table is the head's weight; None: it is when the
+                                  # checkpoint has no tensor called ``name``
     name: str
+    kind: str = "linear"          # registered head name
+    params: Dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass
@@ -104,6 +109,9 @@ class ModelPlan:
     max_positions: int            # 0: not limited by the configuration
     stop_token_ids: List[int] = field(default_factory=list)
     bos_token_id: Optional[int] = None
+    # patterns (``fnmatch``) of tensor names that a checkpoint of this architecture may carry and the model
+    # does not read; any other tensor the parts did not ask for is an error
+    ignorable: List[str] = field(default_factory=list)
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -17,6 +17,7 @@ tensor stored in 32-bit floats stays 32-bit, integer tables become int32.  The
 from __future__ import annotations
 
 from dataclasses import dataclass
+from fnmatch import fnmatchcase
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
@@ -52,9 +53,12 @@ def stored_dtype(on_disk: torch.dtype, kind: str, float_dtype: torch.dtype) -> t
     return torch.bfloat16
 
 
-def check_manifest(manifest: Sequence[TensorSpec], found: Dict[str, Tuple[int, ...]]) -> None:
+def check_manifest(manifest: Sequence[TensorSpec], found: Dict[str, Tuple[int, ...]],
+                   ignorable: Sequence[str] = ()) -> None:
     """Raises one error naming every mismatch between ``manifest`` and the
-    shapes ``found`` in a checkpoint."""
+    shapes ``found`` in a checkpoint.  Names that match one of the ``ignorable`` patterns may be there without
+    being asked for (tables that some exporters store and the model recomputes, such as
+    ``*.rotary_emb.inv_freq``; the reference reads by name and never looks at the rest, src/model.cpp:378-416)."""
     wanted = {s.name: s for s in manifest}
     if len(wanted) != len(manifest):
         seen, dup = set(), []
@@ -64,7 +68,7 @@ def check_manifest(manifest: Sequence[TensorSpec], found: Dict[str, Tuple[int, .
             seen.add(s.name)
         raise WeightsError("model lists a tensor twice: " + ", ".join(sorted(set(dup))))
     missing = [n for n, s in wanted.items() if n not in found and not s.optional]
-    unexpected = [n for n in found if n not in wanted]
+    unexpected = [n for n in found if n not in wanted and not any(fnmatchcase(n, p) for p in ignorable)]
     wrong = [(n, found[n], wanted[n].shape) for n in wanted
              if n in found and tuple(found[n]) != tuple(wanted[n].shape)]
     if not (missing or unexpected or wrong):
@@ -81,11 +85,11 @@ def check_manifest(manifest: Sequence[TensorSpec], found: Dict[str, Tuple[int, .
 
 
 def load_tensors(model_dir: str, manifest: Sequence[TensorSpec], float_dtype: torch.dtype,
-                 device: torch.device | str = "cpu") -> Dict[str, torch.Tensor]:
+                 device: torch.device | str = "cpu", ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """Reads every tensor of ``manifest`` from the folder's safetensors."""
     store = TensorStore(model_dir)
     try:
-        check_manifest(manifest, {n: store.shape(n) for n in store.names()})
+        check_manifest(manifest, {n: store.shape(n) for n in store.names()}, ignorable)
         out: Dict[str, torch.Tensor] = {}
         for spec in manifest:
             if spec.name not in store.where:

@@ -41,7 +41,7 @@ def read_config(model_dir: str) -> dict:
     depth = j.get("scale_depth")
     c["rho"] = 1.0 if depth is None else depth / math.sqrt(c["layers"])
     c["divisor"] = c["hidden"] / (j.get("dim_model_base") or c["hidden"])
-    c["tied"] = bool(j.get("tie_word_embeddings", False))
+    c["tied"] = j.get("tie_word_embeddings")        # None: tied iff the checkpoint has no lm_head.weight
     window = j.get("sliding_window")
     types = j.get("layer_types")
     c["windows"] = [0 if window is None or (types is not None and types[i] != "sliding_attention") else window
@@ -139,7 +139,8 @@ def forward(w: Dict[str, torch.Tensor], c: dict, ids: List[int]) -> torch.Tensor
     for i in range(c["layers"]):
         h = layer(h, w, i, c)
     h = rms_norm(h, w["model.norm.weight"], c["eps"]) / c["divisor"]
-    head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
+    tied = c["tied"] if c["tied"] is not None else "lm_head.weight" not in w
+    head = w["model.embed_tokens.weight"] if tied else w["lm_head.weight"]
     return linear(h, head)
 
 

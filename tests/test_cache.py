@@ -150,3 +150,25 @@ def test_random_traffic_keeps_the_books():
         c.close(s)
     c.check()
     assert all(g.pool.n_held == 0 for g in c.groups) and c.slots.n_free == c.slots.n_slots
+
+
+def test_a_reader_cannot_look_further_back_than_the_cache_it_reads_keeps():
+    own = (KVRequest(2, 16, 32), None, None)
+    SequenceCache([own, (KVRequest(2, 16, 32), None, 0)], 640, allocate=False)       # the same window: fine
+    SequenceCache([own, (KVRequest(2, 16, 8), None, 0)], 640, allocate=False)        # a narrower one: fine
+    SequenceCache([(KVRequest(2, 16, 0), None, None), (KVRequest(2, 16, 8), None, 0)], 640, allocate=False)
+    with pytest.raises(CacheError, match="keeps only a window of 32"):
+        SequenceCache([own, (KVRequest(2, 16, 0), None, 0)], 640, allocate=False)    # every key wanted
+    with pytest.raises(CacheError, match="keeps only a window of 32"):
+        SequenceCache([own, (KVRequest(2, 16, 64), None, 0)], 640, allocate=False)   # a wider window
+
+
+def test_pages_leave_a_window_as_soon_as_no_query_can_see_them():
+    c = SequenceCache([(KVRequest(2, 16, 100), None, None)], 64 * 8, allocate=False)
+    # page 0 (keys 0..63) is last needed by the query at position 162, which sees keys 63..162; a sequence of
+    # 163 tokens has its next query at position 163
+    assert not c.gives_back_at(162)
+    assert c.gives_back_at(163) and not c.gives_back_at(164)
+    assert c.gives_back_at(227) and not c.gives_back_at(226)
+    full = SequenceCache([(KVRequest(2, 16, 0), None, None)], 64 * 8, allocate=False)
+    assert not any(full.gives_back_at(n) for n in range(1, 400))

@@ -18,7 +18,7 @@ def test_defaults_follow_the_reference():
     assert c.head_dim == 16                      # hidden / heads
     assert c.rms_norm_eps == 1e-6 and c.rope_theta == 10000.0
     assert c.scale_emb == 1.0 and c.residual_scale == 1.0 and c.logit_divisor == 1.0
-    assert c.tie_word_embeddings is False and c.eos_token_id == [] and c.bos_token_id is None
+    assert c.tie_word_embeddings is None and c.eos_token_id == [] and c.bos_token_id is None
 
 
 @pytest.mark.parametrize("key", list(REQUIRED))
@@ -50,7 +50,8 @@ def test_eos_as_integer_or_list():
     ({"hidden_act": "gelu"}, "hidden_act"),
     ({"num_key_value_heads": 3}, "num_key_value_heads"),
     ({"hidden_size": 66, "head_dim": 0}, "divisible"),
-    ({"head_dim": 15}, "head_dim"),
+    ({"head_dim": 15}, "'head_dim' must be a multiple of 16"),
+    ({"head_dim": 24}, "'head_dim' must be a multiple of 16"),
     ({"rms_norm_eps": 0}, "rms_norm_eps"),
     ({"vocab_size": "many"}, "vocab_size"),
     ({"num_hidden_layers": 0}, "num_hidden_layers"),

@@ -142,4 +142,81 @@ def test_seeded_temperature_is_reproducible():
     a = generate(eng, [[1], [1]], opt)
     b = generate(eng, [[1], [1]], opt)
     assert [r.tokens for r in a] == [r.tokens for r in b]
-    assert a[0].tokens != a[1].tokens or True          # streams differ per request index
+    assert a[0].tokens != a[1].tokens                  # each request has a stream of its own (seed + index)
+
+
+def test_plan_batches_refuses_more_positions_than_the_model_has():
+    assert plan_batches([10, 20], 100, 8, 4096, max_positions=120) == [[0, 1]]
+    with pytest.raises(ValueError, match="exceed max_position_embeddings 119"):
+        plan_batches([10, 20], 100, 8, 4096, max_positions=119)
+
+
+class AheadEngine(ScriptedEngine):
+    """The scripted engine with a session that can run one step ahead of the host, as the real one does:
+    ``step(None)`` feeds what the last step chose, ``fetch_ids`` hands those tokens out later, ``park`` turns
+    rows into padding."""
+
+    max_positions = 0
+
+    def decode_session(self, slots, max_new=0):
+        eng = self
+
+        class Fetched:
+            def __init__(self, ids):
+                self.ids = ids
+
+            def get(self):
+                return list(self.ids)
+
+        class Session:
+            def __init__(self):
+                self.rows = list(slots)
+                self.chosen = None
+                self.parked = []
+
+            def step(self, tokens):
+                live = [s for s in self.rows if s is not None]
+                eng.calls.append(("decode", live))
+                feed = tokens if tokens is not None else self.chosen
+                for r, s in enumerate(self.rows):
+                    if s is not None:
+                        eng.live[s].append(feed[r])
+                self.chosen = [(eng.live[s][-1] + 1) % V if s is not None else 0 for s in self.rows]
+                return None
+
+            def fetch_ids(self, ids=None):
+                return Fetched(self.chosen)
+
+            def park(self, rows):
+                for r in rows:
+                    assert self.rows[r] is not None, "row parked twice"
+                    self.parked.append(r)
+                    self.rows[r] = None
+
+            def close(self):
+                pass
+
+        self.session = Session()
+        return self.session
+
+
+def test_run_ahead_spends_no_step_after_the_length_limit():
+    eng = AheadEngine(stop=())
+    res = generate(eng, [[1], [5, 6]], GenerateOptions(max_tokens=4))
+    assert [r.tokens for r in res] == [[2, 3, 4, 5], [7, 8, 9, 10]]
+    assert all(r.finish_reason == "length" for r in res)
+    # the prompts' step gives token 1; tokens 2, 3 and 4 take one decode step each and nothing runs after them
+    assert [c[0] for c in eng.calls] == ["step", "decode", "decode", "decode"]
+    assert not eng.live
+
+
+def test_run_ahead_parks_rows_that_stop_and_goes_on_with_the_rest():
+    eng = AheadEngine(stop=(0,))
+    res = generate(eng, [[13], [3]], GenerateOptions(max_tokens=6))
+    assert res[0].tokens == [14, 15, 0] and res[0].finish_reason == "stop"
+    assert res[1].tokens == [4, 5, 6, 7, 8, 9] and res[1].finish_reason == "length"
+    assert eng.session.parked == [0]
+    decodes = [c[1] for c in eng.calls if c[0] == "decode"]
+    # the stop token was seen one step late: the row ran once more into its own pages, then only the other row
+    assert [len(d) for d in decodes] == [2, 2, 2, 1, 1]
+    assert not eng.live and sorted(eng.closed) == sorted(eng.opened)

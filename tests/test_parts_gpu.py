@@ -373,6 +373,49 @@ class HalfSpeedRope:
                         kv.page_size, kv.owns)
 
 
+class TwoTableEmbedding:
+    """An embedding that is not one table gather: a row of the token table plus a row of a small second table
+    chosen by the token id modulo its length."""
+
+    @staticmethod
+    def tensor_specs(spec):
+        from exl3_server_b200.weights import TensorSpec
+        return [TensorSpec(spec.name, (spec.vocab, spec.width)),
+                TensorSpec(spec.params["second"], (spec.params["classes"], spec.width))]
+
+    def __init__(self, spec, tensors, ctx):
+        self.table = tensors[spec.name].to(ctx.dtype)
+        self.second = tensors[spec.params["second"]].to(ctx.dtype)
+        self.scale = spec.scale
+
+    def forward(self, token_ids):
+        from exl3_server_b200.parts import ResidualStream
+        ids = token_ids.long()
+        return ResidualStream((self.table[ids].float() + self.second[ids % self.second.shape[0]].float()) * self.scale)
+
+
+class SoftcapHead:
+    """A head of its own kind: logits squashed to (-cap, cap) by ``cap * tanh(x / cap)``."""
+
+    @staticmethod
+    def tensor_specs(spec):
+        from exl3_server_b200.weights import TensorSpec
+        return [TensorSpec(spec.name, (spec.vocab, spec.width))]
+
+    def __init__(self, spec, tensors, embedding, ctx):
+        from exl3_server_b200.parts.linear import Linear
+        self.linear = Linear(tensors[spec.name], None, ctx.dtype)
+        self.cap = float(spec.params["cap"])
+        self.divisor = spec.input_divisor
+
+    def forward(self, stream, final_norm, rows):
+        r = final_norm.add_norm(stream, rows=rows, out_scale=1.0 / self.divisor)
+        return self.cap * torch.tanh(self.linear(r, out_dtype=torch.float32) / self.cap)
+
+    def read_bytes(self):
+        return self.linear.weight_bytes()
+
+
 @dataclass
 class Toy2Config:
     width: int
@@ -399,15 +442,18 @@ def toy2_plan(cfg):
             FeedForwardSpec("test_routed" if i == 1 else "swiglu", cfg.width, 40),
             NormSpec("rms", cfg.width, 1e-5), NormSpec("rms", cfg.width, 1e-5), 1.0,
             names={"mixer": p + "a.", "feed_forward": p + "f.", "mixer_norm": p + "n1.", "feed_forward_norm": p + "n2."}))
-    return ModelPlan("ToyRoutedLM", EmbeddingSpec(cfg.vocab, cfg.width, 1.0, "t.emb"), layers,
-                     [ScheduleEntry(0), ScheduleEntry(1)], NormSpec("rms", cfg.width, 1e-5), "t.norm.",
-                     HeadSpec(cfg.vocab, cfg.width, 1.0, False, "t.head"), max_positions=0)
+    return ModelPlan("ToyRoutedLM",
+                     EmbeddingSpec(cfg.vocab, cfg.width, 1.0, "t.emb", kind="test_two_tables",
+                                   params={"second": "t.emb2", "classes": 7}),
+                     layers, [ScheduleEntry(0), ScheduleEntry(1)], NormSpec("rms", cfg.width, 1e-5), "t.norm.",
+                     HeadSpec(cfg.vocab, cfg.width, 1.0, False, "t.head", kind="test_softcap", params={"cap": 2.0}),
+                     max_positions=0)
 
 
 def toy2_plain_logits(w, cfg, ids):
     w = {k: v.double() for k, v in w.items()}
     L = len(ids)
-    h = w["t.emb"][torch.tensor(ids)]
+    h = w["t.emb"][torch.tensor(ids)] + w["t.emb2"][torch.tensor(ids) % 7]
     for i in range(2):
         p = f"t.{i}."
         r = P.rms_norm(h, w[p + "n1.weight"], 1e-5)
@@ -430,22 +476,25 @@ def toy2_plain_logits(w, cfg, ids):
                                            w[p + f"f.experts.{e}.up_proj.weight"],
                                            w[p + f"f.experts.{e}.down_proj.weight"])[0]
         h = h + y
-    return P.linear(P.rms_norm(h, w["t.norm.weight"], 1e-5), w["t.head"])
+    return 2.0 * torch.tanh(P.linear(P.rms_norm(h, w["t.norm.weight"], 1e-5), w["t.head"]) / 2.0)
 
 
 def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
-    """A feed-forward with routing and a position encoding of its own, both
+    """A feed-forward with routing, a position encoding, an embedding and a head of their own kinds, all
     defined here, registered and run through the engine in float32 (where a
     routing decision cannot flip by rounding of the activations)."""
     from exl3_server_b200 import Engine
     from exl3_server_b200.config import register_architecture, unregister_architecture
     from exl3_server_b200.engine.model import plan_manifest
-    from exl3_server_b200.parts import register_feed_forward, register_position, unregister
+    from exl3_server_b200.parts import (register_embedding, register_feed_forward, register_head, register_position,
+                                        unregister)
     from exl3_server_b200.weights import write_safetensors
     from exl3_server_b200.weights.random_init import random_tensors
     cfg = Toy2Config(width=32, vocab=40)
     register_feed_forward("test_routed", RoutedFeedForward)
     register_position("test_half_speed_rope", HalfSpeedRope)
+    register_embedding("test_two_tables", TwoTableEmbedding)
+    register_head("test_softcap", SoftcapHead)
     register_architecture(["ToyRoutedLM"], Toy2Config, toy2_plan)
     try:
         folder = str(tmp_path)
@@ -470,3 +519,5 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
         unregister_architecture(["ToyRoutedLM"])
         unregister("feed_forward", "test_routed")
         unregister("position", "test_half_speed_rope")
+        unregister("embedding", "test_two_tables")
+        unregister("head", "test_softcap")

@@ -1,11 +1,10 @@
 """The engine against the plain implementation at layer sizes of real models (two layers of each, random
-weights): the benchmark's MiniCPM-2B sizes (36 heads of 64, width 2304, vocabulary 122753, tied head) and
+weights): the benchmark's MiniCPM-2B sizes (36 heads of 64, width 2304, vocabulary 122753, tied head),
 Llama-3-8B-like sizes (32 query heads on 8 key/value heads of 128, width 4096, feed-forward 14336, vocabulary
-128256).  The tiny configurations of the other tests reach every option; these reach the shapes the kernels are
-tuned for: whole prompt, then the last 40 tokens one by one."""
-import os
-import sys
-
+128256) and the MiniCPM4-8B sizes (32 query heads on 2 key/value heads of 128: 16 query heads share a key/value
+head; feed-forward 16384).  The tiny configurations of the other tests reach every option; these reach the shapes
+the kernels are tuned for: whole prompt, then the last 40 tokens one by one, then a batch of 24 decoding
+together (more than the 16 rows the weight-streaming projection takes)."""
 import numpy as np
 import pytest
 import torch
@@ -15,33 +14,37 @@ from plain_llama import PlainModel
 
 pytestmark = pytest.mark.gpu
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-
-def _configs():
-    import bench
-    from exl3_server_b200 import LlamaConfig
-    return {
-        "minicpm-2b": LlamaConfig(**{**bench.BENCH_MODEL, "num_hidden_layers": 2}),
-        "llama-8b-like": LlamaConfig(**{**bench.OTHER_SIZES["llama-8b-like"][0], "num_hidden_layers": 2}),
-    }
-
-
-@pytest.mark.parametrize("name", ["minicpm-2b", "llama-8b-like"])
+@pytest.mark.parametrize("name", ["minicpm-2b", "llama-8b-like", "minicpm4-8b"])
 def test_two_layers_of_real_sizes(tmp_path, name):
-    from exl3_server_b200 import Engine, write_random_model
-    cfg = _configs()[name]
+    from exl3_server_b200 import Engine, LlamaConfig, write_random_model
+    from exl3_server_b200.config.presets import sizes
+    cfg = LlamaConfig(**sizes(name, num_hidden_layers=2))
     folder = str(tmp_path / name)
     write_random_model(cfg, folder, seed=3, std=0.02)
     g = torch.Generator().manual_seed(2)
     toks = torch.randint(0, cfg.vocab_size, (200,), generator=g).tolist()
     want = PlainModel(folder).logits(toks).numpy()
     for dtype in ("float32", "bfloat16"):
-        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=8192)
         for what, trace in (("whole", whole_trace({"r0": toks})), ("last 40 one by one", tail_trace({"r0": toks}, tail=40))):
             got = run_trace(eng, trace)["r0"]
             per_pos = np.max(np.abs(got - want), axis=1) / np.max(np.abs(want))
             bad = np.nonzero(per_pos > TOL[dtype])[0]
             assert bad.size == 0, f"{name} {dtype} {what}: first wrong position {bad[0]}, error {per_pos[bad[0]]:.3e}"
+        if dtype == "bfloat16":
+            # 24 copies of the request's first 160 tokens, then 40 steps of all 24 rows: every row must follow
+            # the plain implementation's logits for the request
+            from exl3_server_b200 import StepEntry
+            slots = [eng.open() for _ in range(24)]
+            eng.step([StepEntry(s, toks[:160], None) for s in slots])
+            session = eng.decode_session(slots, max_new=64)
+            for p in range(160, 200):
+                got = session.step([toks[p]] * 24).float().cpu().numpy()
+                err = np.max(np.abs(got - want[p][None]), axis=1).max() / np.max(np.abs(want[p]))
+                assert err <= TOL[dtype], f"{name}: 24 rows at position {p}: error {err:.3e}"
+            session.close()
+            for s in slots:
+                eng.close(s)
         del eng
         torch.cuda.empty_cache()

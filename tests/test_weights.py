@@ -109,6 +109,41 @@ def test_tied_head_needs_no_lm_head_and_refuses_a_stray_one(tmp_path):
         load_tensors(untied, plan_manifest(build_plan(tied)), torch.bfloat16)
 
 
+def test_an_absent_tie_key_follows_the_checkpoint(tmp_path):
+    """config.json without ``tie_word_embeddings``: the head is the embedding table exactly when the checkpoint
+    has no ``lm_head.weight``."""
+    d = CFG.to_dict()
+    del d["tie_word_embeddings"]
+    free = LlamaConfig.from_dict(d)
+    assert free.tie_word_embeddings is None and "tie_word_embeddings" not in free.to_dict()
+    plan = build_plan(free)
+    without = write_random_model(free, str(tmp_path / "w"), seed=1)          # optional tensors are not written
+    assert "lm_head.weight" not in TensorStore(without).names()
+    assert "lm_head.weight" not in load_tensors(without, plan_manifest(plan), torch.bfloat16)
+    with_head = write_random_model(CFG, str(tmp_path / "h"), seed=1)
+    assert "lm_head.weight" in load_tensors(with_head, plan_manifest(plan), torch.bfloat16)
+    from exl3_server_b200.engine.engine import load_model
+    assert load_model(without, "float32", "cpu").head.tied and not load_model(with_head, "float32", "cpu").head.tied
+
+
+def test_tensors_the_architecture_declares_ignorable_may_be_there(tmp_path):
+    folder = write_random_model(CFG, str(tmp_path / "m"), seed=1)
+    plan = build_plan(CFG)
+    store = TensorStore(folder)
+    tensors = {n: store.tensor(n).clone() for n in store.names()}
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+    got = load_tensors(folder, plan_manifest(plan), torch.bfloat16, ignorable=plan.ignorable)
+    assert not any("inv_freq" in n for n in got)
+    with pytest.raises(WeightsError, match=r"unexpected tensors \(2\)"):
+        load_tensors(folder, plan_manifest(plan), torch.bfloat16)            # without the plan's patterns
+    tensors["model.layers.0.self_attn.extra.weight"] = torch.zeros(2)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+    with pytest.raises(WeightsError, match=r"unexpected tensors \(1\): model.layers.0.self_attn.extra.weight"):
+        load_tensors(folder, plan_manifest(plan), torch.bfloat16, ignorable=plan.ignorable)
+
+
 def test_optional_biases():
     manifest = [TensorSpec("w", (2, 2)), TensorSpec("b", (2,), optional=True)]
     check_manifest(manifest, {"w": (2, 2)})
