@@ -75,6 +75,19 @@ int exl3_gemv_bf16_normed(const void* x, const void* w, const void* bias, void* 
                           float rho, const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out,
                           cudaStream_t stream);
 
+// The same projection and epilogues for up to 128 rows on tcgen05 tensor cores: the weights are the 128-row operand
+// and stream once by TMA, K is cut over the blocks of a cluster and summed through distributed shared memory (no
+// scratch, no atomics).  ss_in / ss_out are [rows >= M, blocks].  split: cuts of K, 0 = chosen from N and K; tiles:
+// 128-row tiles of w per block (1 or 2), 0 = chosen.
+// exl3_gemm_skinny_status() returns and clears the code a kernel left when one of its bounded waits ran out.
+int exl3_gemm_skinny(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M, int N, int K,
+                     int epilogue, const float* ss_in, int ss_blocks, float eps, float width, float* h, float rho,
+                     const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out, int split, int tiles,
+                     cudaStream_t stream);
+int exl3_gemm_skinny_status();
+int exl3_gemm_skinny_max_rows();
+int exl3_gemm_skinny_split(int N, int K);
+
 // Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64 or 128, pages of 64, up
 // to 8 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing

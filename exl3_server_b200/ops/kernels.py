@@ -251,6 +251,71 @@ def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
+SKINNY_MAX_ROWS = 128
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                gated: bool = False, scale=None, resid=None, split: int = 0, out: Optional[torch.Tensor] = None,
+                tiles: int = 0):
+    """``x @ w.T (+ bias)`` for up to 128 rows of x on the tcgen05 tensor cores with the weights read once (the
+    weights are the 128-row operand, the batch the narrow one; see gemm_skinny.cu).  ``gated``, ``scale`` and
+    ``resid`` as in ``gemv_bf16_normed``; the sums of squares are ``[rows, blocks]`` with any number of rows from
+    M up.  ``split``: blocks that share one tile's K range, 0 for the kernel's own choice from N and K;
+    ``tiles``: 128-row tiles of w per block (1 or 2; changes no result), 0 for the kernel's choice."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemm_skinny: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemm_skinny: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
+    if scale is not None:
+        ss_in, eps, width = scale
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] < M:
+            raise KernelLibraryError("gemm_skinny: ss must be float32 [rows >= M, blocks]")
+        _contig(ss_in, "ss")
+        ss_blocks = ss_in.shape[1]
+    lib = library()
+    if resid is not None:
+        if gated:
+            raise KernelLibraryError("gemm_skinny: the gated epilogue does not write into the residual")
+        h, rho, norm_w = resid
+        if h.dtype != torch.float32 or tuple(h.shape) != (M, N) or tuple(norm_w.shape) != (N,):
+            raise KernelLibraryError(f"gemm_skinny: h {tuple(h.shape)} / norm weight {tuple(norm_w.shape)} "
+                                     f"do not fit an output of {(M, N)}")
+        _contig(h, "h")
+        _contig(norm_w, "norm_w")
+        x_raw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ss_out = torch.empty((M, (N + 15) // 16), dtype=torch.float32, device=x.device)
+        _check(lib.exl3_gemm_skinny(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(None), _c_int(DT_BF16), _c_int(M), _c_int(N), _c_int(K), _c_int(2),
+            _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(h), _c_float(rho), _ptr(norm_w),
+            _c_int(dtype_code(norm_w.dtype)), _ptr(x_raw), _ptr(ss_out), _c_int(split), _c_int(tiles), _stream()), "gemm_skinny")
+        return x_raw, ss_out
+    if out is None:
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    elif tuple(out.shape) != (M, N // 2 if gated else N) or not out.is_contiguous():
+        raise KernelLibraryError(f"gemm_skinny: out must be contiguous {(M, N // 2 if gated else N)}")
+    _check(lib.exl3_gemm_skinny(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(M), _c_int(N), _c_int(K),
+        _c_int(1 if gated else 0), _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(None),
+        _c_float(0.0), _ptr(None), _c_int(DT_BF16), _ptr(None), _ptr(None), _c_int(split), _c_int(tiles), _stream()),
+        "gemm_skinny")
+    return out
+
+
+def gemm_skinny_status() -> int:
+    """0, or the code a skinny GEMM left when a bounded wait ran out (cleared by this call)."""
+    return int(library().exl3_gemm_skinny_status())
+
+
+def gemm_skinny_split(N: int, K: int) -> int:
+    """The number of K cuts ``gemm_skinny`` chooses for a weight matrix ``[N, K]``."""
+    return int(library().exl3_gemm_skinny_split(_c_int(N), _c_int(K)))
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
             gated: bool = False) -> torch.Tensor:
     """``x @ w.T (+ bias)`` in bfloat16 on the tcgen05 tensor cores; with ``gated``
@@ -386,10 +451,11 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
 
 
 def check_status() -> None:
-    """Raises if a kernel with bounded waits (the tcgen05 GEMM and attention, the TMA decode attention) gave up
-    on one since the last call: its results are then not to be trusted.  Reads three flags from the device, so
+    """Raises if a kernel with bounded waits (the tcgen05 GEMMs and attention, the TMA decode attention) gave up
+    on one since the last call: its results are then not to be trusted.  Reads four flags from the device, so
     it waits for the work launched so far; call it where the host waits anyway."""
-    gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("attn_prefill_tc", attn_prefill_tc_status),
+    gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("gemm_skinny", gemm_skinny_status),
+                                     ("attn_prefill_tc", attn_prefill_tc_status),
                                      ("attn_decode", attn_decode_status)) if fn()]
     if gave_up:
         raise KernelLibraryError("a bounded wait ran out in " + ", ".join(gave_up) +

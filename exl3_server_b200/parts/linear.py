@@ -4,11 +4,16 @@ src/model.cpp:214-228; the kernels here read rows of W, so no transpose).
 
 Which kernel runs depends only on the element type and the row count:
 float32 goes through the CUDA-core kernel with a fixed order of summation
-(the true 32-bit path); bfloat16 with at most 16 rows streams the weights once
-through the tensor-core GEMV; larger plain bfloat16 products are the library's
+(the true 32-bit path).  bfloat16 with at most 16 rows streams the weights once
+through the tensor-core GEMV (``mma.sync``, weights as the 16-row operand); with
+17 to ``SKINNY_ROWS`` rows through the skinny tcgen05 GEMM (weights as the
+128-row operand, streamed once by TMA).  Both take a norm's output in two pieces
+and can fold their output into the residual (see ``RawNormed``, ``NormAfter``), so
+a decode step of up to ``SKINNY_ROWS`` sequences has no kernel between its
+projections.  Larger plain bfloat16 products (prompts) are the library's
 (cuBLAS through ``torch``), as the reference's are MLX's (src/model.cpp:549).
-The gated feed-forward projection, whose epilogue is fused, runs on this
-library's own tcgen05 GEMM (``gated``).
+The gated feed-forward projection, whose epilogue is fused, never goes to the
+library: above ``SKINNY_ROWS`` rows it runs on this library's own tcgen05 GEMM.
 """
 from __future__ import annotations
 
@@ -20,8 +25,8 @@ from ..ops import kernels as K
 from .base import RawNormed
 
 
-# Rows up to which the gated projection goes through the library GEMM and a separate silu*mul kernel.
-GATED_LIBRARY_ROWS = 64
+# Rows up to which bfloat16 projections go through the skinny tcgen05 GEMM (17 rows and more; the GEMV below).
+SKINNY_ROWS = 64
 
 
 class Linear:
@@ -33,51 +38,62 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
         self.dtype = dtype
 
+    def _streaming_kernel(self, rows: int):
+        """The kernel that reads the weights once for ``rows`` rows and takes the norm's pieces: the GEMV, the
+        skinny GEMM, or None (float32, sizes they refuse, too many rows)."""
+        if self.dtype != torch.bfloat16 or self.in_features % 8 != 0:
+            return None
+        if rows <= K.GEMV_MAX_ROWS:
+            return K.gemv_bf16_normed
+        if rows <= SKINNY_ROWS:
+            return K.gemm_skinny
+        return None
+
     def __call__(self, x, out_dtype: Optional[torch.dtype] = None, then=None) -> Optional[torch.Tensor]:
-        """``x``: a tensor, or a ``RawNormed`` (a norm's output in two pieces: the weight-streaming GEMV applies
-        the missing factor per row to its results; other paths materialise it first).
-        ``then``: a ``NormAfter`` offer; taken when the weight-streaming GEMV runs (at most 16 rows, bfloat16)
-        and the output is as wide as the residual: its blocks add the output to the residual and leave the
-        pieces of the next norm's output.  Returns None then."""
+        """``x``: a tensor, or a ``RawNormed`` (a norm's output in two pieces: the weight-streaming kernels apply
+        the missing factor per row to their results; other paths materialise it first).
+        ``then``: a ``NormAfter`` offer; taken when a weight-streaming kernel runs (bfloat16, at most
+        ``SKINNY_ROWS`` rows) and the output is as wide as the residual: its blocks add the output to the residual
+        and leave the pieces of the next norm's output.  Returns None then."""
         out_dtype = out_dtype or self.dtype
         M = x.shape[0]
         fast = self.in_features % 8 == 0
-        streams = self.dtype == torch.bfloat16 and fast and M <= K.GEMV_MAX_ROWS
+        kernel = self._streaming_kernel(M)
         scale = None
         if isinstance(x, RawNormed):
-            if streams:
+            if kernel is not None:
                 scale, x = (x.ss, x.eps, float(x.width)), x.x_raw
             else:
                 x = x.materialize()
         if self.dtype == torch.float32:
             return K.gemm_simt(x, self.weight, self.bias, torch.float32)
-        if streams:
+        if kernel is not None:
             if (then is not None and out_dtype == torch.bfloat16 and hasattr(then.norm, "fuse_args")
                     and then.stream.pending is None and tuple(then.stream.h.shape) == (M, self.out_features)):
                 norm_w, eps, width = then.norm.fuse_args()
-                x_raw, ss = K.gemv_bf16_normed(x, self.weight, self.bias, torch.bfloat16, scale=scale,
-                                               resid=(then.stream.h, then.scale, norm_w))
+                x_raw, ss = kernel(x, self.weight, self.bias, torch.bfloat16, scale=scale,
+                                   resid=(then.stream.h, then.scale, norm_w))
                 then.stream.normed = (then.norm, RawNormed(x_raw, ss, eps, width))
                 then.done = True
                 return None
-            if scale is not None:
-                return K.gemv_bf16_normed(x, self.weight, self.bias, out_dtype, scale=scale)
-            return K.gemv_bf16(x, self.weight, self.bias, out_dtype)
+            if scale is None and kernel is K.gemv_bf16_normed:
+                return K.gemv_bf16(x, self.weight, self.bias, out_dtype)
+            return kernel(x, self.weight, self.bias, out_dtype, scale=scale)
         if out_dtype == torch.bfloat16 and fast:
             return torch.nn.functional.linear(x, self.weight, self.bias)
         if fast:
-            # float32 results for many rows (logits at many positions): the
-            # GEMV in groups of 16 rows keeps float32 accumulators end to end
+            # float32 results for many rows (logits at many positions): the skinny GEMM in groups of 128 rows
+            # keeps float32 accumulators end to end
             out = torch.empty((M, self.out_features), dtype=out_dtype, device=x.device)
-            for m0 in range(0, M, K.GEMV_MAX_ROWS):
-                m1 = min(M, m0 + K.GEMV_MAX_ROWS)
-                K.gemv_bf16(x[m0:m1], self.weight, self.bias, out_dtype, out=out[m0:m1])
+            for m0 in range(0, M, K.SKINNY_MAX_ROWS):
+                m1 = min(M, m0 + K.SKINNY_MAX_ROWS)
+                K.gemm_skinny(x[m0:m1], self.weight, self.bias, out_dtype, out=out[m0:m1])
             return out
         return K.gemm_simt(x, self.weight, self.bias, out_dtype)
 
     def streams_weights(self, rows: int) -> bool:
-        """Whether ``rows`` rows of input go through the weight-streaming GEMV."""
-        return self.dtype == torch.bfloat16 and self.in_features % 8 == 0 and rows <= K.GEMV_MAX_ROWS
+        """Whether ``rows`` rows of input go through a kernel that reads the weights once."""
+        return self._streaming_kernel(rows) is not None
 
     def fuses_gate(self) -> bool:
         """Whether ``gated`` can run: bfloat16 with sizes the fused kernels take."""
@@ -87,19 +103,18 @@ class Linear:
         """For a weight whose rows are eight gate rows, then the eight up rows
         of the same features, and so on: ``silu(gate) * up`` in the projection's
         own epilogue, so the gate/up product never goes to memory.  Up to 16 rows:
-        the weight-streaming GEMV; more than 64: the tcgen05 tensor-core GEMM; between, the library's
-        GEMM and a silu*mul kernel."""
+        the weight-streaming GEMV; up to ``SKINNY_ROWS``: the skinny tcgen05 GEMM; more: the tcgen05 GEMM for
+        prompts."""
+        kernel = self._streaming_kernel(x.shape[0])
         if isinstance(x, RawNormed):
-            if x.shape[0] <= K.GEMV_MAX_ROWS:
-                return K.gemv_bf16_normed(x.x_raw, self.weight, self.bias, self.dtype, gated=True,
-                                          scale=(x.ss, x.eps, float(x.width)))
+            if kernel is not None:
+                return kernel(x.x_raw, self.weight, self.bias, self.dtype, gated=True,
+                              scale=(x.ss, x.eps, float(x.width)))
             x = x.materialize()
-        if x.shape[0] <= K.GEMV_MAX_ROWS:
+        if kernel is K.gemv_bf16_normed:
             return K.gemv_bf16(x, self.weight, self.bias, self.dtype, gated=True)
-        if x.shape[0] <= GATED_LIBRARY_ROWS:
-            # 17 to 64 rows: one 128-row tile of the tcgen05 kernel would be mostly empty and its 256-column
-            # tiles too few for the GPU (19 us against 12 + 3 us measured for this path at 2304 x 11520)
-            return K.silu_mul(torch.nn.functional.linear(x, self.weight, self.bias), interleave=8)
+        if kernel is not None:
+            return kernel(x, self.weight, self.bias, self.dtype, gated=True)
         return K.gemm_tc(x, self.weight, self.bias, gated=True)
 
     def weight_bytes(self) -> int:

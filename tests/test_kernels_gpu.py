@@ -216,6 +216,113 @@ def test_gemv_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_dtype
             close(got, torch.nn.functional.silu(gate) * up, 1.5e-2, "gated second projection")
 
 
+@pytest.mark.parametrize("M", [1, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,Kd", [(2304, 2304), (6912, 2304), (263, 96), (50, 40), (1000, 5768), (16, 8), (136, 208)])
+def test_gemm_skinny(M, N, Kd):
+    """The weights as the 128-row tensor-core operand, K cut over the blocks of a cluster: every number of cuts,
+    sizes that are no multiple of a tile, and a row's result independent of its batch."""
+    torch.manual_seed(12)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    want = x.double() @ w.double().T
+    # float32 out of bfloat16 operands: tcgen05.mma adds an instruction's products with fewer guard bits than a
+    # chain of float32 FMAs keeps (3e-6 of the largest value measured at K = 2304, against 7e-7 for mma.sync),
+    # far below the 4e-3 that rounding the operands to bfloat16 costs
+    F32 = 1e-5
+    auto = K().gemm_skinny(x, w, None, torch.float32)
+    close(auto, want, F32, "skinny f32 out")
+    close(K().gemm_skinny(x, w, b, torch.bfloat16), want + b.double(), TOL[torch.bfloat16], "skinny bf16 out + bias")
+    ksteps = (Kd + 63) // 64
+    chosen = K().gemm_skinny_split(N, Kd)
+    assert 1 <= chosen <= min(8, ksteps)
+    for split in range(1, min(8, ksteps) + 1):
+        got = K().gemm_skinny(x, w, None, torch.float32, split=split, tiles=1)
+        close(got, want, F32, f"skinny with {split} cuts")
+        # two tiles of w per block read x once for both: the same numbers bit for bit
+        assert torch.equal(K().gemm_skinny(x, w, None, torch.float32, split=split, tiles=2), got)
+        if split == chosen:
+            assert torch.equal(got, auto)
+    # a row's result does not depend on the other rows, nor on how many there are
+    one = K().gemm_skinny(x[M - 1:].contiguous(), w, None, torch.float32)
+    assert torch.equal(one[0], auto[M - 1])
+    torch.cuda.synchronize()
+    assert K().gemm_skinny_status() == 0
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("I,Kd", [(176, 64), (5760, 2304), (200, 96)])
+def test_gemm_skinny_gated(M, I, Kd):
+    torch.manual_seed(13)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    wg = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    wu = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    bg, bu = torch.randn(I, device=DEV).bfloat16(), torch.randn(I, device=DEV).bfloat16()
+    n = I // 8
+    w = torch.stack([wg.view(n, 8, Kd), wu.view(n, 8, Kd)], dim=1).reshape(2 * I, Kd).contiguous()
+    b = torch.stack([bg.view(n, 8), bu.view(n, 8)], dim=1).reshape(-1).contiguous()
+    g = x.double() @ wg.double().T + bg.double()
+    u = x.double() @ wu.double().T + bu.double()
+    want = g * torch.sigmoid(g) * u
+    close(K().gemm_skinny(x, w, b, torch.bfloat16, gated=True), want, TOL[torch.bfloat16], "gated skinny")
+    close(K().gemm_skinny(x, w, b, torch.float32, gated=True), want, 1e-5, "gated skinny f32 out")
+    assert torch.equal(K().gemm_skinny(x, w, b, torch.bfloat16, gated=True, tiles=2),
+                       K().gemm_skinny(x, w, b, torch.bfloat16, gated=True, tiles=1))
+    torch.cuda.synchronize()
+    assert K().gemm_skinny_status() == 0
+
+
+@pytest.mark.parametrize("M", [17, 33, 64])
+@pytest.mark.parametrize("N,Kd", [(2304, 2304), (2304, 5760), (263, 96), (50, 40), (136, 208)])
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_dtype):
+    """Both sides of a norm that is no kernel of its own, for more rows than the GEMV takes."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    nw = (1.0 + 0.2 * torch.randn(N, generator=g)).to(norm_dtype).to(DEV)
+    h0 = torch.randn(M, N, generator=g).to(DEV)
+    rho, eps = 0.37, 1e-5
+    for bias in (None, b):
+        h = h0.clone()
+        x_raw, ss = K().gemm_skinny(x, w, bias, torch.bfloat16, resid=(h, rho, nw))
+        y = K().gemm_skinny(x, w, bias, torch.bfloat16)      # what the plain epilogue stores
+        want_h = h0.double() + y.double() * rho
+        close(h, want_h, 2e-6, "residual")
+        close(x_raw, want_h * nw.double(), 6e-3, "residual times the norm weight")
+        assert ss.shape == (M, (N + 15) // 16)
+        close(ss.sum(1), (want_h * want_h).sum(1), 1e-5, "sums of squares")
+        N2 = 176
+        w2 = (torch.randn(N2, N, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        b2 = torch.randn(N2, generator=g).to(torch.bfloat16).to(DEV)
+        if N % 8 == 0:
+            h2 = h0.clone()
+            r = K().add_rmsnorm(h2, y, rho, nw, eps, torch.bfloat16)
+            for bias2 in (None, b2):
+                want = r.double() @ w2.double().T + (0 if bias2 is None else bias2.double())
+                got = K().gemm_skinny(x_raw, w2, bias2, torch.float32, scale=(ss, eps, float(N)))
+                close(got, want, 1e-2, "second projection")
+            wg = torch.stack([w2[:N2 // 2].view(-1, 8, N), w2[N2 // 2:].view(-1, 8, N)], dim=1).reshape(N2, N).contiguous()
+            got = K().gemm_skinny(x_raw, wg, None, torch.bfloat16, gated=True, scale=(ss, eps, float(N)))
+            gate, up = r.double() @ w2[:N2 // 2].double().T, r.double() @ w2[N2 // 2:].double().T
+            close(got, torch.nn.functional.silu(gate) * up, 1.5e-2, "gated second projection")
+    torch.cuda.synchronize()
+    assert K().gemm_skinny_status() == 0
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    x = torch.zeros(129, 64, device=DEV).bfloat16()
+    w = torch.zeros(8, 64, device=DEV).bfloat16()
+    with pytest.raises(KernelLibraryError, match="M <= 128"):
+        K().gemm_skinny(x, w, None, torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="multiple of 8"):
+        K().gemm_skinny(x[:20, :60].contiguous(), w[:, :60].contiguous(), None, torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="multiple of 16 when gated"):
+        K().gemm_skinny(x[:20].contiguous(), w, None, torch.bfloat16, gated=True)
+
+
 def test_gemv_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(17, 64, device=DEV).bfloat16()
