@@ -89,7 +89,7 @@ int exl3_gemm_skinny_max_rows();
 int exl3_gemm_skinny_split(int N, int K);
 
 // Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64 or 128, pages of 64, up
-// to 8 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
+// to 16 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing
 // them to the cache itself.  See attention_decode.cu.
 int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys, int max_splits);

@@ -13,7 +13,8 @@
 // multiply-adds per element: the kernel is bound by memory, and on the CUDA
 // cores by the instructions that unpack and multiply the elements.  Here a
 // page of keys is the 16-row operand of the matrix instruction (keys x
-// features), the queries of the kv head's group are the 8 columns, and the
+// features), the queries of the kv head's group are the 8 columns (two
+// instructions side by side for groups of 9 to 16 query heads), and the
 // scores come out transposed: S^T = K Q^T, then O^T = V^T P^T with V read
 // through ldmatrix.trans and P^T made from the score registers by movmatrix.
 // One page costs a warp 32 matrix instructions instead of some 600 scalar ones.
@@ -61,7 +62,7 @@ namespace exl3 {
 
 constexpr int AD_WARPS = 4;
 constexpr int AD_PAGE = 64;
-constexpr int AD_MAX_GROUP = 8;                            // query heads per kv head: the columns of one instruction
+constexpr int AD_MAX_GROUP = 16;                           // query heads per kv head: one or two blocks of 8 instruction columns
 // A stage holds the keys, then the values, of one page of one kv head (heads of 64) or of half a page (heads of
 // 128): 8 KB each either way.
 constexpr int AD_TILE_BYTES = 8192;
@@ -138,7 +139,9 @@ __device__ inline uint32_t ad_pack(float lo, float hi) {
 // are copied to shared memory at the start; page numbers are asked for 32 pages at a time, one
 // batch ahead; queries are asked for one (token, kv head) ahead; records are stored and left
 // behind, and one fence at the end of the warp's work covers them all before it draws tickets.
-template <int HD>
+// NC: blocks of 8 query heads of a kv head's group (the columns of an instruction): 1 for groups of up to 8, 2 for
+// up to 16.  Both blocks use the same key and value fragments, so a page is read from shared memory once.
+template <int HD, int NC>
 __global__ void __launch_bounds__(AD_WARPS * 32, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
@@ -316,15 +319,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 #pragma unroll 1
   for (int s = 0; s < AD_STAGES; ++s) produce();
 
-  // Q^T as the right operand: column gl is query head gl of the group, zero beyond the group
-  auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[NJ][2]) {
-    const unsigned* qrow = reinterpret_cast<const unsigned*>(q + (int64_t)t * q_row_stride +
-                                                             (int64_t)(g * G + gl) * HD);
-    const bool live = some && gl < G;
+  // Q^T as the right operand: column gl of block c is query head 8 c + gl of the group, zero beyond the group
+  auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[NC][NJ][2]) {
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      qq[j][0] = live ? __ldcg(qrow + 8 * j + tl) : 0u;
-      qq[j][1] = live ? __ldcg(qrow + 8 * j + tl + 4) : 0u;
+    for (int c = 0; c < NC; ++c) {
+      const unsigned* qrow = reinterpret_cast<const unsigned*>(q + (int64_t)t * q_row_stride +
+                                                               (int64_t)(g * G + 8 * c + gl) * HD);
+      const bool live = some && 8 * c + gl < G;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        qq[c][j][0] = live ? __ldcg(qrow + 8 * j + tl) : 0u;
+        qq[c][j][1] = live ? __ldcg(qrow + 8 * j + tl + 4) : 0u;
+      }
     }
   };
   // the (token, kv head) after (t, g), if this warp holds chunks of it
@@ -449,7 +455,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   auto merge = [&](int mt, int mg) {
     const int n_rec = chunks_of(mt);
     int hg = 1;                                          // as many heads at once as the weights' table takes
-    while (hg < G && 2 * hg * n_rec <= AD_MAX_SPLITS) hg *= 2;
+    while (hg < G && hg < 8 && 2 * hg * n_rec <= AD_MAX_SPLITS) hg *= 2;
     for (int n0 = 0; n0 < G; n0 += hg) {
       switch (hg) {
         case 1: merge_heads(std::integral_constant<int, 1>{}, mt, mg, n0); break;
@@ -465,7 +471,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   uint32_t cn = 0;                                       // pages used
   bool ok = true;
   int t = t0, g = g0, sp = sp0;
-  uint32_t qb[NJ][2], qn[NJ][2];
+  uint32_t qb[NC][NJ][2], qn[NC][NJ][2];
   int nt = 0, ng = 0;
   bool nsome = false;
   if (rotate && i0 < i1) angles_of(t0);                  // positions are the step's inputs
@@ -474,7 +480,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     load_q(t, g, true, qb);
     nsome = next_run(t, g, nt, ng);
     load_q(nt, ng, nsome, qn);                           // used when this warp gets to (nt, ng)
-    if (rotate) rotate_at(t, qb);
+    if (rotate) {
+#pragma unroll
+      for (int c = 0; c < NC; ++c) rotate_at(t, qb[c]);
+    }
   }
 #pragma unroll 1
   for (int i = i0; i < i1 && ok; ++i) {
@@ -501,35 +510,49 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       }
       new_page = __ldcg(block_table + (int64_t)s_seq[t] * bt_stride + s_pos[t] / AD_PAGE);
     }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[NJ][4];
+    float m[NC][2], l[NC][2];
+    float o[NC][NJ][4];
 #pragma unroll
-    for (int a = 0; a < NJ; ++a) {
+    for (int c = 0; c < NC; ++c) {
+      m[c][0] = m[c][1] = -INFINITY;
+      l[c][0] = l[c][1] = 0.0f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[a][e] = 0.0f;
+      for (int a = 0; a < NJ; ++a) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[c][a][e] = 0.0f;
+      }
     }
 #pragma unroll 1
     for (int pi = first_sub; pi <= last_sub; ++pi) {
       const uint32_t st = cn % AD_STAGES;
       if (!ad_mbar_wait(bars + st, (cn / AD_STAGES) & 1)) { ok = false; break; }
       const uint32_t kb = ring + st * AD_STAGE_BYTES;
-      // S^T = K Q^T: s[a] holds keys 16 a + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
-      float s[MT][4];
+      // S^T = K Q^T: s[c][a] holds keys 16 a + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1 of block c
+      float s[NC][MT][4];
 #pragma unroll
       for (int a = 0; a < MT; ++a) {
+        float s_hi[NC][4];                                 // features 64 .. of a head of 128: a chain of its own
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[a][e] = 0.0f;
-        float s_hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};         // features 64 .. of a head of 128: a chain of its own
+        for (int c = 0; c < NC; ++c) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { s[c][a][e] = 0.0f; s_hi[c][e] = 0.0f; }
+        }
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {                     // features 16 j ..: box j / 4, its piece j % 4
           uint32_t f[4];
           ad_ldsm(f, kb + (j >> 2) * BOX_BYTES + a * 2048 + k_row + k_col[j & 3]);
-          if (j < 4) ad_mma(s[a], f, qb[j][0], qb[j][1]);
-          else ad_mma(s_hi, f, qb[j][0], qb[j][1]);
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            if (j < 4) ad_mma(s[c][a], f, qb[c][j][0], qb[c][j][1]);
+            else ad_mma(s_hi[c], f, qb[c][j][0], qb[c][j][1]);
+          }
         }
         if (NJ > 4) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[a][e] += s_hi[e];
+          for (int c = 0; c < NC; ++c) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[c][a][e] += s_hi[c][e];
+          }
         }
       }
       const int key0 = pi * KS;
@@ -538,57 +561,60 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         for (int a = 0; a < MT; ++a) {
           const int ka = key0 + 16 * a + gl, kb2 = ka + 8;
           const bool da = (ka < c_lo) | (ka >= c_hi), db = (kb2 < c_lo) | (kb2 >= c_hi);
-          s[a][0] = da ? -INFINITY : s[a][0];
-          s[a][1] = da ? -INFINITY : s[a][1];
-          s[a][2] = db ? -INFINITY : s[a][2];
-          s[a][3] = db ? -INFINITY : s[a][3];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            s[c][a][0] = da ? -INFINITY : s[c][a][0];
+            s[c][a][1] = da ? -INFINITY : s[c][a][1];
+            s[c][a][2] = db ? -INFINITY : s[c][a][2];
+            s[c][a][3] = db ? -INFINITY : s[c][a][3];
+          }
         }
       }
-      float mx[2];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        mx[c] = fmaxf(s[0][c], s[0][c + 2]);
-#pragma unroll
-        for (int a = 1; a < MT; ++a) mx[c] = fmaxf(mx[c], fmaxf(s[a][c], s[a][c + 2]));
-        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
-        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
-        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
-      }
-      float corr[2];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float mn = fmaxf(m[c], mx[c] * scale_log2);   // a page in the chunk has a live key: finite
-        corr[c] = ad_exp2(m[c] - mn);                        // 0 on the first page
-        m[c] = mn;
-      }
       // P^T as the right operand of the second product, by transposing 8x8 pieces across the warp
-      uint32_t pb[MT][2];
+      uint32_t pb[NC][MT][2];
 #pragma unroll
-      for (int a = 0; a < MT; ++a) {
-        const float p0 = ad_exp2(fmaf(s[a][0], scale_log2, -m[0]));
-        const float p1 = ad_exp2(fmaf(s[a][1], scale_log2, -m[1]));
-        const float p2 = ad_exp2(fmaf(s[a][2], scale_log2, -m[0]));
-        const float p3 = ad_exp2(fmaf(s[a][3], scale_log2, -m[1]));
-        l[0] = l[0] * (a == 0 ? corr[0] : 1.0f) + (p0 + p2);
-        l[1] = l[1] * (a == 0 ? corr[1] : 1.0f) + (p1 + p3);
-        pb[a][0] = ad_transpose(ad_pack(p0, p1));
-        pb[a][1] = ad_transpose(ad_pack(p2, p3));
-      }
+      for (int c = 0; c < NC; ++c) {
+        float mx[2], corr[2];
 #pragma unroll
-      for (int d = 0; d < NJ; ++d) {
-        o[d][0] *= corr[0];
-        o[d][1] *= corr[1];
-        o[d][2] *= corr[0];
-        o[d][3] *= corr[1];
+        for (int h = 0; h < 2; ++h) {
+          mx[h] = fmaxf(s[c][0][h], s[c][0][h + 2]);
+#pragma unroll
+          for (int a = 1; a < MT; ++a) mx[h] = fmaxf(mx[h], fmaxf(s[c][a][h], s[c][a][h + 2]));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+          const float mn = fmaxf(m[c][h], mx[h] * scale_log2);   // a page in the chunk has a live key: finite
+          corr[h] = ad_exp2(m[c][h] - mn);                        // 0 on the first page
+          m[c][h] = mn;
+        }
+#pragma unroll
+        for (int a = 0; a < MT; ++a) {
+          const float p0 = ad_exp2(fmaf(s[c][a][0], scale_log2, -m[c][0]));
+          const float p1 = ad_exp2(fmaf(s[c][a][1], scale_log2, -m[c][1]));
+          const float p2 = ad_exp2(fmaf(s[c][a][2], scale_log2, -m[c][0]));
+          const float p3 = ad_exp2(fmaf(s[c][a][3], scale_log2, -m[c][1]));
+          l[c][0] = l[c][0] * (a == 0 ? corr[0] : 1.0f) + (p0 + p2);
+          l[c][1] = l[c][1] * (a == 0 ? corr[1] : 1.0f) + (p1 + p3);
+          pb[c][a][0] = ad_transpose(ad_pack(p0, p1));
+          pb[c][a][1] = ad_transpose(ad_pack(p2, p3));
+        }
+#pragma unroll
+        for (int d = 0; d < NJ; ++d) {
+          o[c][d][0] *= corr[0];
+          o[c][d][1] *= corr[1];
+          o[c][d][2] *= corr[0];
+          o[c][d][3] *= corr[1];
+        }
       }
-      // O^T += V^T P^T: o[d] holds features 16 d + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
+      // O^T += V^T P^T: o[c][d] holds features 16 d + gl (elements 0, 1) and + 8 (2, 3) for queries 2 tl, 2 tl + 1
 #pragma unroll
       for (int a = 0; a < MT; ++a) {
 #pragma unroll
         for (int d = 0; d < NJ; ++d) {
           uint32_t f[4];
           ad_ldsm_t(f, kb + (d >> 2) * BOX_BYTES + a * 2048 + v_row + v_col[d & 3]);
-          ad_mma(o[d], f, pb[a][0], pb[a][1]);
+#pragma unroll
+          for (int c = 0; c < NC; ++c) ad_mma(o[c][d], f, pb[c][a][0], pb[c][a][1]);
         }
       }
       __syncwarp();                                      // every lane has read the stage
@@ -614,63 +640,73 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           reinterpret_cast<uint4*>(v_pool + at)[lane] = __ldcg(vsrc + lane);
         }
       }
-      // its score against this lane group's query (column gl), then to the lanes that hold that column's state
-      float dot = 0.0f;
+      // its score against this lane group's queries (column gl of each block), then to the lanes that hold those
+      // columns' state
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
+      for (int c = 0; c < NC; ++c) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            dot = fmaf(__uint_as_float(qb[c][j][h] << 16), __uint_as_float(kf[j][h] << 16), dot);
+            dot = fmaf(__uint_as_float(qb[c][j][h] & 0xffff0000u), __uint_as_float(kf[j][h] & 0xffff0000u), dot);
+          }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          dot = fmaf(__uint_as_float(qb[j][h] << 16), __uint_as_float(kf[j][h] << 16), dot);
-          dot = fmaf(__uint_as_float(qb[j][h] & 0xffff0000u), __uint_as_float(kf[j][h] & 0xffff0000u), dot);
-        }
-      }
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+          const float sc = __shfl_sync(0xffffffffu, dot, (2 * tl + h) * 4) * scale_log2;
+          const float mn = fmaxf(m[c][h], sc);
+          const float corr = ad_exp2(m[c][h] - mn);              // 0 when the cache held no key of this chunk
+          const uint32_t pp = ad_pack(ad_exp2(sc - mn), 0.0f);   // rounded as the other probabilities are
+          const float pr = __uint_as_float(pp << 16);
+          m[c][h] = mn;
+          l[c][h] = l[c][h] * corr + (gl == 0 ? pr : 0.0f);      // the sum over lane groups below counts it once
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float sc = __shfl_sync(0xffffffffu, dot, (2 * tl + c) * 4) * scale_log2;
-        const float mn = fmaxf(m[c], sc);
-        const float corr = ad_exp2(m[c] - mn);               // 0 when the cache held no key of this chunk
-        const uint32_t pp = ad_pack(ad_exp2(sc - mn), 0.0f);  // rounded as the other probabilities are
-        const float pr = __uint_as_float(pp << 16);
-        m[c] = mn;
-        l[c] = l[c] * corr + (gl == 0 ? pr : 0.0f);          // the sum over lane groups below counts it once
-#pragma unroll
-        for (int d = 0; d < NJ; ++d) {
-          o[d][c] = o[d][c] * corr + pr * __uint_as_float((uint32_t)vf[2 * d] << 16);
-          o[d][c + 2] = o[d][c + 2] * corr + pr * __uint_as_float((uint32_t)vf[2 * d + 1] << 16);
+          for (int d = 0; d < NJ; ++d) {
+            o[c][d][h] = o[c][d][h] * corr + pr * __uint_as_float((uint32_t)vf[2 * d] << 16);
+            o[c][d][h + 2] = o[c][d][h + 2] * corr + pr * __uint_as_float((uint32_t)vf[2 * d + 1] << 16);
+          }
         }
       }
     }
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
-      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 8);
-      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 16);
+    for (int c = 0; c < NC; ++c) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        l[c][h] += __shfl_xor_sync(0xffffffffu, l[c][h], 4);
+        l[c][h] += __shfl_xor_sync(0xffffffffu, l[c][h], 8);
+        l[c][h] += __shfl_xor_sync(0xffffffffu, l[c][h], 16);
+      }
     }
     // ---- the chunk's result ------------------------------------------------------------------
     const int n_rec = chunks_of(t);
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int n = 2 * tl + c;
-      if (n >= G) continue;
-      const int head = g * G + n;
-      if (n_rec == 1) {
-        __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * HD;
-        const float inv = 1.0f / l[c];
+    for (int c = 0; c < NC; ++c) {
 #pragma unroll
-        for (int d = 0; d < NJ; ++d) {
-          dst[16 * d + gl] = __float2bfloat16(o[d][c] * inv);
-          dst[16 * d + gl + 8] = __float2bfloat16(o[d][c + 2] * inv);
-        }
-      } else {
-        float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
+      for (int h = 0; h < 2; ++h) {
+        const int n = 8 * c + 2 * tl + h;
+        if (n >= G) continue;
+        const int head = g * G + n;
+        if (n_rec == 1) {
+          __nv_bfloat16* dst = out + ((int64_t)t * nh + head) * HD;
+          const float inv = 1.0f / l[c][h];
 #pragma unroll
-        for (int d = 0; d < NJ; ++d) {
-          sc[16 * d + gl] = o[d][c];
-          sc[16 * d + gl + 8] = o[d][c + 2];
+          for (int d = 0; d < NJ; ++d) {
+            dst[16 * d + gl] = __float2bfloat16(o[c][d][h] * inv);
+            dst[16 * d + gl + 8] = __float2bfloat16(o[c][d][h + 2] * inv);
+          }
+        } else {
+          float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
+#pragma unroll
+          for (int d = 0; d < NJ; ++d) {
+            sc[16 * d + gl] = o[c][d][h];
+            sc[16 * d + gl + 8] = o[c][d][h + 2];
+          }
+          if (gl == 0) { sc[HD] = m[c][h]; sc[HD + 1] = l[c][h]; }
         }
-        if (gl == 0) { sc[HD] = m[c]; sc[HD + 1] = l[c]; }
       }
     }
     // on to the next chunk; a new (token, kv head) brings its queries, asked for a run ago
@@ -679,8 +715,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       t = nt;
       g = ng;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) { qb[j][0] = qn[j][0]; qb[j][1] = qn[j][1]; }
-      if (rotate && i + 1 < i1) rotate_at(t, qb);
+      for (int c = 0; c < NC; ++c) {
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) { qb[c][j][0] = qn[c][j][0]; qb[c][j][1] = qn[c][j][1]; }
+        if (rotate && i + 1 < i1) rotate_at(t, qb[c]);
+      }
       if (nsome) {
         nsome = next_run(t, g, nt, ng);
         load_q(nt, ng, nsome, qn);
@@ -805,9 +844,13 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   }
   static int sms = 0;
   if (!sms) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+      e = cudaFuncSetAttribute(attn_decode_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e != cudaSuccess) { set_error("attn_decode: cannot get %u bytes of shared memory: %s", AD_SMEM, cudaGetErrorString(e)); return (int)e; }
     int dev = 0;
     cudaGetDevice(&dev);
@@ -826,13 +869,15 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * nkv * max_splits);
   int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
-#define EXL3_AD_LAUNCH(HD_)                                                                                       \
-  launch_pdl(attn_decode_kernel<HD_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
+#define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
+  launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,           \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
              static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool))
-  if (hd == 64) EXL3_AD_LAUNCH(64); else EXL3_AD_LAUNCH(128);
+  const bool wide = nh / nkv > 8;                          // more than one block of 8 query heads per kv head
+  if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2); else EXL3_AD_LAUNCH(64, 1); }
+  else { if (wide) EXL3_AD_LAUNCH(128, 2); else EXL3_AD_LAUNCH(128, 1); }
 #undef EXL3_AD_LAUNCH
   return launch_status("attn_decode");
 }

@@ -451,7 +451,9 @@ def test_attn_tokens_finds_one_far_key_among_many():
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (4, 2, 64), (8, 1, 64), (16, 2, 64), (5, 5, 64), (6, 2, 64),
-                                       (5, 1, 64), (3, 3, 128), (8, 1, 128), (8, 2, 128), (6, 1, 128), (9, 3, 128)])
+                                       (5, 1, 64), (3, 3, 128), (8, 1, 128), (8, 2, 128), (6, 1, 128), (9, 3, 128),
+                                       # 9 to 16 query heads per kv head: two blocks of instruction columns
+                                       (16, 1, 64), (9, 1, 64), (26, 2, 64), (32, 2, 128), (12, 1, 128), (30, 3, 128)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("split", [64, 256])
 def test_attn_decode(nh, nkv, hd, window, split):
@@ -502,7 +504,7 @@ def test_attn_decode_many_items_per_warp(hd):
     assert K().attn_decode_status() == 0
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(8, 1, 64), (14, 2, 128), (4, 1, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 1, 64), (14, 2, 128), (4, 1, 128), (16, 1, 128), (22, 2, 64)])
 def test_attn_decode_merges_many_chunks_of_grouped_heads(nh, nkv, hd):
     # so many chunks for each token that the heads of a group are merged in several passes
     lens = [2100, 1, 2049, 640]
@@ -545,7 +547,8 @@ def test_attn_decode_finds_one_far_key_among_many():
     assert float((out.cpu().float() - case.v[0][far].reshape(1, -1).float()).abs().max()) > 0.1
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (8, 1, 64), (16, 2, 64), (4, 2, 128), (8, 1, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(3, 3, 64), (8, 1, 64), (16, 2, 64), (4, 2, 128), (8, 1, 128), (16, 1, 64),
+                                       (32, 2, 128), (10, 1, 128)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("rotary", [True, False])
 @pytest.mark.parametrize("split", [64, 256, 2048])
@@ -604,7 +607,9 @@ def test_attn_decode_is_refused_for_other_shapes():
     assert not K().attn_decode_supported(torch.float32, 8, 4, 4, 64, 64, 256, 16)
     assert K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 128, 64, 256, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 96, 64, 256, 16)
-    assert not K().attn_decode_supported(torch.bfloat16, 8, 16, 1, 64, 64, 256, 16)
+    assert K().attn_decode_supported(torch.bfloat16, 8, 16, 1, 64, 64, 256, 16)          # 16 query heads per kv head
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 17, 1, 64, 64, 256, 16)
+    assert not K().attn_decode_supported(torch.bfloat16, 8, 40, 2, 128, 64, 256, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 100, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 5000, 4, 4, 64, 64, 256, 16)
     assert not K().attn_decode_supported(torch.bfloat16, 8, 4, 4, 64, 64, 256, 1000)
