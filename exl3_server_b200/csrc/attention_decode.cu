@@ -150,7 +150,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
                    const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, float pos_scale,
                    int rotate, int write_new,
-                   __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool) {
+                   __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int kv_rep) {
+  // nkv counts groups of query heads that are worked on together.  With kv_rep = 2 the query heads of a kv head
+  // are two such groups (g and g + 1 read kv head g / 2): twice the work items and two merges of half the size,
+  // for steps with few tokens, where a single warp's merge of a wide group is what takes the time.
   constexpr int KS = HD == 64 ? 64 : 32;                 // keys of a stage
   constexpr int SPP = AD_PAGE / KS;                      // stages of a page
   constexpr int MT = KS / 16;                            // 16-key tiles of a stage
@@ -305,7 +308,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (lane == 0) {
       const uint32_t s = pn % AD_STAGES;
       const uint32_t dst = ring + s * AD_STAGE_BYTES;
-      const int row = (pg * nkv + cur_b.g) * AD_PAGE + (p_pi % SPP) * KS;
+      const int row = (pg * (nkv / kv_rep) + cur_b.g / kv_rep) * AD_PAGE + (p_pi % SPP) * KS;
       ad_mbar_expect_tx(bars + s, AD_STAGE_BYTES);
 #pragma unroll
       for (int b = 0; b < NBOX; ++b) {
@@ -499,8 +502,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     int new_page = 0;
     if (has_new) {
       const __nv_bfloat16* row = q + (int64_t)t * q_row_stride;
-      const unsigned* krow = reinterpret_cast<const unsigned*>(row + (int64_t)(nh + g) * HD);
-      const unsigned short* vrow = reinterpret_cast<const unsigned short*>(row + (int64_t)(nh + nkv + g) * HD);
+      const unsigned* krow = reinterpret_cast<const unsigned*>(row + (int64_t)(nh + g / kv_rep) * HD);
+      const unsigned short* vrow = reinterpret_cast<const unsigned short*>(row + (int64_t)(nh + nkv / kv_rep + g / kv_rep) * HD);
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
         kf[j][0] = __ldcg(krow + 8 * j + tl);
@@ -625,7 +628,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (has_new) {
       if (rotate) rotate_at(t, kf);
       // to the cache, for the steps to come: the key from the lanes of query column 0, the value as it is
-      const int64_t at = (((int64_t)new_page * nkv + g) * AD_PAGE + (s_pos[t] % AD_PAGE)) * HD;
+      // (with kv_rep = 2 both groups of a kv head write the same key and value to the same place)
+      const int64_t at = (((int64_t)new_page * (nkv / kv_rep) + g / kv_rep) * AD_PAGE + (s_pos[t] % AD_PAGE)) * HD;
       if (new_page >= 0) {
         if (gl == 0) {
           unsigned* kdst = reinterpret_cast<unsigned*>(k_pool + at);
@@ -636,7 +640,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           }
         }
         if (lane < HD / 8) {
-          const uint4* vsrc = reinterpret_cast<const uint4*>(q + (int64_t)t * q_row_stride + (int64_t)(nh + nkv + g) * HD);
+          const uint4* vsrc = reinterpret_cast<const uint4*>(q + (int64_t)t * q_row_stride +
+                                                             (int64_t)(nh + nkv / kv_rep + g / kv_rep) * HD);
           reinterpret_cast<uint4*>(v_pool + at)[lane] = __ldcg(vsrc + lane);
         }
       }
@@ -819,8 +824,12 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
                                 const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
                                 float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
-                                int write_new, cudaStream_t stream) {
+                                int write_new, int head_split, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (head_split != 1 && (head_split != 2 || (nkv > 0 && (nh / nkv) % 2 != 0))) {
+    set_error("attn_decode: head_split is 1, or 2 for an even number of query heads per kv head; got %d", head_split);
+    return ERR_BAD_ARGUMENT;
+  }
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
       !exl3_attn_decode_supported(DT_BF16, T, nh, nkv, hd, page, split_keys, max_splits)) {
     set_error("attn_decode: needs bfloat16, head_dim 64 or 128, pages of 64, at most %d tokens, %d query heads per kv "
@@ -866,16 +875,21 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   if (rc) return rc;
   // one block per SM as soon as there is a chunk for each: the warps' equal shares then spread few chunks over all
   // SMs (and their memory pipes) instead of filling the warps of half of them
-  const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * nkv * max_splits);
+  const int groups = nkv * head_split;                     // groups of query heads worked on together
+  if (max_splits > 1 && (int64_t)T * groups > AD_COUNTER_SLOTS) {
+    set_error("attn_decode: %d tokens x %d groups of heads exceed the %d merge counters", T, groups, AD_COUNTER_SLOTS);
+    return ERR_UNSUPPORTED;
+  }
+  const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
   int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
 #define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
   launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
-             bt_stride, tok_pos, tok_seq, T, nh, nkv, window, scale * 1.4426950408889634f, split_keys,           \
+             bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
-             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool))
-  const bool wide = nh / nkv > 8;                          // more than one block of 8 query heads per kv head
+             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split)
+  const bool wide = nh / groups > 8;                       // more than one block of 8 query heads per group
   if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2); else EXL3_AD_LAUNCH(64, 1); }
   else { if (wide) EXL3_AD_LAUNCH(128, 2); else EXL3_AD_LAUNCH(128, 1); }
 #undef EXL3_AD_LAUNCH

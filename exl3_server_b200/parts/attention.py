@@ -107,17 +107,22 @@ class Attention:
             return False
         inv_freq, rot, pos_scale = rotation
         T = qkv.shape[0]
-        split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
-        n = self._chunks(batch.max_kv_len, split)
-        if not K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
+        if not self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             return False
+        split, head_split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+        n = self._chunks(batch.max_kv_len, split)
         scratch = None
         if n > 1:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
         K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
-                      inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns)
+                      inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns, head_split=head_split)
         return True
+
+    def _decode_kernel_takes(self, dtype: torch.dtype, T: int, page: int) -> bool:
+        """Whether the tensor-core decode kernel takes this mixer's shapes at all (any chunking)."""
+        s = self.spec
+        return K.attn_decode_supported(dtype, T, s.heads, s.kv_heads, s.head_dim, page, page, 1)
 
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> None:
         s = self.spec
@@ -130,15 +135,16 @@ class Attention:
                               tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
                               self.scale)
             return
-        split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device) if qkv.dtype == torch.bfloat16 else 0
-        n = self._chunks(batch.max_kv_len, split) if split else 0
-        if split and K.attn_decode_supported(qkv.dtype, T, s.heads, s.kv_heads, s.head_dim, kv.page_size, split, n):
+        if self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             # decoded tokens, heads of 64 or 128: pages by TMA, both products on the tensor cores, a warp per chunk
+            split, head_split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+            n = self._chunks(batch.max_kv_len, split)
             scratch = None
             if n > 1:
                 scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
             K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
-                          s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+                          s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
+                          head_split=head_split)
             return
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
@@ -156,21 +162,45 @@ class Attention:
         K.attn_tokens(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
 
-    def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device) -> int:
-        """Keys per chunk for the tensor-core decode kernel: about two chunks per SM, in whole pages, 1 to 64 of
-        them.  Every chunk costs its warp a record and a ticket, so few long chunks beat many
-        short ones once every warp has work (measured at batch 1 to 64).  The choice depends on the step's
-        size, not on a token's position: results differ between batch sizes by rounding."""
-        keys = min(max_kv_len, self.spec.window) if self.spec.window > 0 else max_kv_len
-        pages = T * self.spec.kv_heads * ((keys + page - 1) // page)
-        # counted in 16 KB of keys and values (a page of a head of 64), which cost a warp about the same time
-        # whatever the head's size; at most 64 pages (at batch 8 and 4,096 tokens one chunk per token and head,
-        # so no merge at all: 52.4 us against 54.4 with two)
-        wide = max(1, self.spec.head_dim // 64)
-        per = max(1.0, pages * wide / (2.0 * K.sm_count(device)))
-        per = min(64 * wide, 1 << int(round(math.log2(per))))
-        per = max(1, per // wide)
-        return page * per
+    def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
+        """``(keys per chunk, head_split)`` for the tensor-core decode kernel: chunks of whole pages (a power of two
+        of them, at most 64 of 16 KB), and whether the query heads of a kv head are worked on as one group or as two
+        (``head_split`` 2: twice the work items, each merge half the size).  By a small model of the kernel's time:
+        a warp walks its chunk at about 0.6 us per 16 KB of keys and values when it is alone (1.0 us with more than
+        8 query heads in its group); all warps together cannot read faster than the memory does; and the chunks of
+        a (token, group of heads), when there is more than one, are merged by a single warp, which costs about 3 us
+        for the records' trip through memory and the ticket, plus 1.5 us for every 8 KB of records (the group's
+        heads x the head's size x the chunks, in float32).  So few long chunks win for wide groups (16 query heads
+        of 128 on a kv head at 2,048 tokens: 32 chunks cost 59 us, 4 cost 20), one chunk wins for short contexts
+        (no merge at all), and many short chunks only where they are needed to give every SM work.  The choice
+        depends on the step's size, not on a token's position: results differ between batch sizes by rounding."""
+        s = self.spec
+        keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
+        pages_seq = max(1, (keys + page - 1) // page)
+        wide = max(1, s.head_dim // 64)                     # 16 KB stages in a page
+        group = s.heads // s.kv_heads
+        warps = 4 * K.sm_count(device)
+        best = None
+        for head_split in ((1, 2) if group >= 8 and group % 2 == 0 else (1,)):
+            g = group // head_split
+            if g > 16:
+                continue
+            stage_us = 1.0 if g > 8 else 0.6
+            stream_us = T * s.kv_heads * head_split * pages_seq * wide * 16384 / 6.0e6     # all pages at 6 TB/s
+            per = 1
+            while True:
+                n = (pages_seq + per - 1) // per
+                if n + (1 if s.window > 0 else 0) <= K.ATTN_DECODE_MAX_CHUNKS:     # a window may straddle one chunk more
+                    rounds = (T * s.kv_heads * head_split * n + warps - 1) // warps
+                    cost = max(rounds * per * wide * stage_us, stream_us)
+                    if n > 1:
+                        cost += 3.0 + 1.5 * n * g * s.head_dim / 2048.0
+                    if best is None or cost < best[0] - 1e-9:
+                        best = (cost, per, head_split)
+                if per >= pages_seq or per * wide >= 64:
+                    break
+                per *= 2
+        return page * best[1], best[2]
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
         """The most chunks of ``split`` keys that a token's keys can touch."""

@@ -475,6 +475,12 @@ def test_attn_decode(nh, nkv, hd, window, split):
         K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
                         nh, nkv, hd, 64, window, scale, split, n, scratch)
         close(out, case.reference(window, scale), 1e-2, "attn_decode")
+    if (nh // nkv) % 2 == 0:
+        # the query heads of a kv head as two groups of work: the same numbers
+        halves = torch.full_like(out, 7.0)
+        K().attn_decode(q, q.stride(0), halves, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, window, scale, split, n, scratch, head_split=2)
+        assert torch.equal(halves, out)
     assert K().attn_decode_status() == 0
 
 
@@ -584,6 +590,7 @@ def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, hd, window, rotar
         case.v_pool[pg, :, pos % 64] = -100.0
     qkv = torch.cat([q_raw.reshape(B, -1), k_raw.reshape(B, -1), v_raw.reshape(B, -1)], dim=1).to(DEV).contiguous()
     out = torch.empty((B, nh * hd), dtype=torch.bfloat16, device=DEV)
+    head_split = 2 if (nh // nkv) % 2 == 0 and split == 256 else 1     # two groups of work per kv head in some cases
     scale = 0.7 / math.sqrt(hd)
     n = (max(lens) + split - 1) // split
     if window > 0:
@@ -592,7 +599,7 @@ def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, hd, window, rotar
     K().attn_decode(qkv, qkv.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, B,
                     nh, nkv, hd, 64, window, scale, split, n, scratch,
                     inv_freq=(K().rotary_table(inv_freq) if split == 256 else inv_freq).to(DEV), rot=rot,
-                    pos_scale=pos_scale, write_new=True)
+                    pos_scale=pos_scale, write_new=True, head_split=head_split)
     close(out, case.reference(window, scale), 1e-2, "attn_decode, own key and value")
     for b in range(B):
         pos = lens[b] - 1
