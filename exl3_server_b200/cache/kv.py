@@ -2,7 +2,7 @@
 fixed-size per-sequence state.
 
 A *slot* is one live sequence.  Keys and values live in *groups*: layers whose
-mixers ask for the same thing (kv heads, head size, window) share one pool of
+mixers ask for the same thing (kv heads, key and value size, window) share one pool of
 pages ``[layer, page, kv_head, position_in_page, head_dim]`` with a page list
 per slot; groups with other needs have a pool of their own.  A group with a
 window gives back the pages that no later query can see.  Pages and slots
@@ -34,7 +34,7 @@ PAGE_SIZE = 64
 class KVLayerView:
     """What a mixer sees of the cache during one step."""
     k: torch.Tensor               # [pages, kv_heads, page_size, head_dim] of this layer
-    v: torch.Tensor
+    v: torch.Tensor               # [pages, kv_heads, page_size, value_dim or head_dim]
     block_table: torch.Tensor     # int32 [batch rows, pages per row] for this step; -1: no page
     page_size: int
     owns: bool                    # False: the layer reads another layer's keys and values
@@ -49,17 +49,44 @@ class KVGroup:
         self.pages: Dict[int, List[int]] = {}          # slot -> physical page per logical page (-1: given back)
         self.k: Optional[torch.Tensor] = None
         self.v: Optional[torch.Tensor] = None
+        self._k_store: Optional[torch.Tensor] = None
+        self._v_store: Optional[torch.Tensor] = None
 
     def allocate(self, dtype: torch.dtype, device) -> None:
         r = self.request
         # one page more than the pool hands out: rows that only pad a batch write there
-        shape = (len(self.owners), self.pool.n_pages + 1, r.kv_heads, self.page_size, r.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (len(self.owners), self.pool.n_pages + 1, r.kv_heads, self.page_size)
+        self.k, self._k_store = self._guarded(shape + (r.head_dim,), dtype, device)
+        self.v, self._v_store = self._guarded(shape + (r.value_dim or r.head_dim,), dtype, device)
+
+    GUARD = 512                    # elements of a known pattern before and after each pool
+    PATTERN = 1.5
+
+    @classmethod
+    def _guarded(cls, shape, dtype, device):
+        """A zeroed tensor of ``shape`` inside a larger allocation whose first and last ``GUARD`` elements hold a
+        pattern: a kernel that writes before or beyond the pool (a page number out of range) changes them, and
+        ``guards_intact`` says so."""
+        n = 1
+        for d in shape:
+            n *= d
+        store = torch.zeros(n + 2 * cls.GUARD, dtype=dtype, device=device)
+        store[:cls.GUARD] = cls.PATTERN
+        store[-cls.GUARD:] = cls.PATTERN
+        return store[cls.GUARD:cls.GUARD + n].view(shape), store
+
+    def guards_intact(self) -> bool:
+        for store in (self._k_store, self._v_store):
+            if store is None:
+                continue
+            edge = torch.cat([store[:self.GUARD], store[-self.GUARD:]])
+            if not bool((edge == self.PATTERN).all()):
+                return False
+        return True
 
     def bytes_per_token(self, itemsize: int) -> int:
         r = self.request
-        return 2 * len(self.owners) * r.kv_heads * r.head_dim * itemsize
+        return len(self.owners) * r.kv_heads * (r.head_dim + (r.value_dim or r.head_dim)) * itemsize
 
     def first_needed_page(self, length: int) -> int:
         """Logical pages below this hold no key that a query at position
@@ -99,7 +126,8 @@ class SequenceCache:
                     raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which owns none")
                 if kv is not None:
                     src_req = self.groups[self.entry_group[src][0]].request
-                    if (kv.kv_heads, kv.head_dim) != (src_req.kv_heads, src_req.head_dim):
+                    if (kv.kv_heads, kv.head_dim, kv.value_dim or kv.head_dim) != (
+                            src_req.kv_heads, src_req.head_dim, src_req.value_dim or src_req.head_dim):
                         raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: head shapes differ")
                     # the owner gives back the pages its own window no longer reaches: a reader that looks
                     # further back would find them gone (the kernels skip pages that are not there)
@@ -248,6 +276,13 @@ class SequenceCache:
     def tokens_held(self) -> int:
         """Tokens held by live sequences, each rounded up to whole pages."""
         return sum((n + self.page_size - 1) // self.page_size * self.page_size for n in self.lengths.values())
+
+    def check_guards(self) -> None:
+        """Raises if anything was written before or beyond a pool of keys or values (reads the guard words from
+        the device: it waits for the work launched so far)."""
+        for i, g in enumerate(self.groups):
+            if not g.guards_intact():
+                raise CacheError(f"the guard words around the key/value pool of cache group {i} were overwritten")
 
     def check(self) -> None:
         self.slots.check()

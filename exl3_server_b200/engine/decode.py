@@ -318,6 +318,9 @@ class DecodeSession:
         if shrunk:
             self.runner.push_tables(shrunk)
         self.engine.steps_run += 1
+        live = [n - 1 for n, s in zip(self.lens, self.slots) if s is not None]
+        if live:
+            self.engine.count_step(live, [1] * len(live), len(live))
         return logits[:len(self.slots)]
 
     @property

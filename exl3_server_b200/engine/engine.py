@@ -33,6 +33,32 @@ class StepError(ValueError):
 
 
 @dataclass
+class Stats:
+    """What the engine's steps have had to do since it was made (or since ``reset``): the counts from which a
+    caller makes rates and roofline fractions.  ``weight_bytes`` counts every weight a step uses once per step,
+    ``cache_bytes`` the keys and values of the contexts that the step's tokens attend over (each sequence's
+    context once per step), ``flops`` two per weight and token (the head only for the wanted rows) plus four per
+    query head, head feature and visible key.  The reference reports seconds and token counts per request only
+    (src/engine.h:58-75)."""
+    steps: int = 0
+    prompt_steps: int = 0
+    decode_steps: int = 0
+    tokens: int = 0
+    weight_bytes: int = 0
+    cache_bytes: int = 0
+    flops: float = 0.0
+
+    def reset(self) -> None:
+        self.__init__()
+
+    def minus(self, earlier: "Stats") -> "Stats":
+        return Stats(**{k: getattr(self, k) - getattr(earlier, k) for k in self.__dataclass_fields__})
+
+    def copy(self) -> "Stats":
+        return Stats(**{k: getattr(self, k) for k in self.__dataclass_fields__})
+
+
+@dataclass
 class StepEntry:
     slot: int
     tokens: Sequence[int]
@@ -79,6 +105,30 @@ class Engine:
         self.workspace = Workspace(self.device)
         self.decode_runners = {}
         self.steps_run = 0
+        self.stats = Stats()
+        self.last_generate_stats: Optional[Stats] = None
+        itemsize = 4 if model.dtype == torch.float32 else 2
+        self._body_params = (model.weight_bytes() - model.head.read_bytes()) // itemsize
+        self._head_params = model.head.read_bytes() // itemsize
+        self._cache_bytes_per_token = sum(g.bytes_per_token(itemsize) for g in self.cache.groups)
+        self._score_flops_per_key = sum(4.0 * m.spec.heads * m.spec.head_dim
+                                        for m in (model.blocks[e.layer].mixer for e in model.plan.schedule)
+                                        if getattr(getattr(m, "spec", None), "heads", 0))
+
+    def count_step(self, starts: Sequence[int], counts: Sequence[int], wanted: int) -> None:
+        """Adds one step to ``stats``: rows that were ``starts`` long bring ``counts`` tokens each."""
+        st = self.stats
+        tokens = int(sum(counts))
+        st.steps += 1
+        if max(counts) > 1:
+            st.prompt_steps += 1
+        else:
+            st.decode_steps += 1
+        st.tokens += tokens
+        st.weight_bytes += self.model.weight_bytes()
+        st.cache_bytes += self._cache_bytes_per_token * int(sum(s + n for s, n in zip(starts, counts)))
+        keys = sum(n * s + n * (n + 1) // 2 for s, n in zip(starts, counts))      # visible keys over the new tokens
+        st.flops += 2.0 * self._body_params * tokens + 2.0 * self._head_params * wanted + self._score_flops_per_key * keys
 
     @classmethod
     def from_folder(cls, model_dir: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
@@ -94,14 +144,23 @@ class Engine:
         return self.cache.max_tokens
 
     @property
+    def page_size(self) -> int:
+        """Tokens per page of the cache: a sequence holds its length rounded up to whole pages."""
+        return self.cache.page_size
+
+    @property
     def max_positions(self) -> int:
         """The most positions a sequence may have (0: no limit given by the configuration)."""
         return int(self.model.plan.max_positions or 0)
 
     def generate(self, prompts, options=None, cancelled=None, on_token=None):
-        """See ``engine.generate.generate``."""
+        """See ``engine.generate.generate``.  ``last_generate_stats`` holds the call's share of ``stats``."""
         from .generate import generate
-        return generate(self, prompts, options, cancelled, on_token)
+        before = self.stats.copy()
+        try:
+            return generate(self, prompts, options, cancelled, on_token)
+        finally:
+            self.last_generate_stats = self.stats.minus(before)
 
     def decode_session(self, slots, max_new: int = 0):
         """Sequences that go on one token per step from a CUDA graph; see
@@ -136,6 +195,7 @@ class Engine:
         for s, st in zip(slots, starts):
             self.cache.commit(s, st + 1)
         self.steps_run += 1
+        self.count_step(starts, [1] * len(slots), sum(len(w) for w in wants))
         rows = [i for i, w in enumerate(wants) for _ in w]
         if not rows:
             return None
@@ -146,8 +206,10 @@ class Engine:
     # -- the step ------------------------------------------------------------
     def check_kernels(self) -> None:
         """Raises if a kernel with bounded waits gave up on one since the last call (see
-        ``ops.kernels.check_status``).  Waits for the work launched so far."""
+        ``ops.kernels.check_status``), or if the guard words around the cache's pools were overwritten.  Waits
+        for the work launched so far."""
         K.check_status()
+        self.cache.check_guards()
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the given tokens, as one batch, from the cache.  Returns the
@@ -204,4 +266,5 @@ class Engine:
         for s, st, t in zip(slots, starts, toks):
             self.cache.commit(s, st + len(t))
         self.steps_run += 1
+        self.count_step(starts, [len(t) for t in toks], sum(len(w) for w in wants))
         return logits

@@ -23,9 +23,8 @@ from typing import Callable, List, Optional, Sequence
 
 from ..sampling.options import SampleOptions
 from ..sampling.sampler import RowSampler, launch_on_device, on_device, record, sample_rows
+from ..cache.kv import PAGE_SIZE
 from .engine import StepEntry
-
-PAGE = 64
 
 
 @dataclass
@@ -49,14 +48,14 @@ class GenerateResult:
 
 
 def plan_batches(prompt_lens: Sequence[int], max_tokens: int, max_batch: int, cache_tokens: int,
-                 max_positions: int = 0) -> List[List[int]]:
+                 max_positions: int = 0, page: int = PAGE_SIZE) -> List[List[int]]:
     """Splits request indices, in order, into batches that fit the cache: a
     request may grow to its prompt plus ``max_tokens`` tokens, counted in whole
     pages.  With ``max_positions`` a request that could grow beyond the model's positions is refused here,
     before anything runs, as the step function would refuse it later."""
     def need(n: int) -> int:
         # one token more than asked for: greedy decoding runs one step ahead of the host
-        return (n + max_tokens + 1 + PAGE - 1) // PAGE * PAGE
+        return (n + max_tokens + 1 + page - 1) // page * page
 
     batches: List[List[int]] = []
     cur: List[int] = []
@@ -95,7 +94,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
             results[i].finish_reason = "stop" if len(p) == 0 else "length"   # src/engine.cpp:227-230
     todo = [len(p) if opt.max_tokens > 0 else 0 for p in prompts]
     for batch in plan_batches(todo, opt.max_tokens, opt.max_batch, engine.cache_tokens,
-                              getattr(engine, "max_positions", 0)):
+                              getattr(engine, "max_positions", 0), getattr(engine, "page_size", PAGE_SIZE)):
         _run_batch(engine, prompts, batch, results, opt, stops, cancelled, on_token)
         check = getattr(engine, "check_kernels", None)
         if check is not None:

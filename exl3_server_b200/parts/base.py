@@ -38,10 +38,13 @@ class BuildContext:
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values for every position (window 0) or the last ``window``."""
+    """Keys and values for every position (window 0) or the last ``window``.  ``value_dim`` is the width of a
+    value per head when it differs from the key's (0: the same), as in mixers that keep narrow keys or a
+    compressed value."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)

@@ -172,3 +172,27 @@ def test_pages_leave_a_window_as_soon_as_no_query_can_see_them():
     assert c.gives_back_at(227) and not c.gives_back_at(226)
     full = SequenceCache([(KVRequest(2, 16, 0), None, None)], 64 * 8, allocate=False)
     assert not any(full.gives_back_at(n) for n in range(1, 400))
+
+
+def test_keys_and_values_of_different_widths_make_a_group_of_their_own():
+    import torch
+    reqs = [(KVRequest(2, 16), None, None), (KVRequest(2, 16, 0, value_dim=32), None, None),
+            (KVRequest(2, 16, 0, value_dim=32), None, None)]
+    c = SequenceCache(reqs, 640, dtype=torch.float32, device="cpu")
+    assert len(c.groups) == 2 and [len(g.owners) for g in c.groups] == [1, 2]
+    assert c.groups[0].k.shape[-1] == 16 and c.groups[0].v.shape[-1] == 16
+    assert c.groups[1].k.shape[-1] == 16 and c.groups[1].v.shape[-1] == 32
+    assert c.groups[0].bytes_per_token(4) == 2 * (16 + 16) * 4 and c.groups[1].bytes_per_token(4) == 2 * 2 * (16 + 32) * 4
+    with pytest.raises(CacheError, match="head shapes differ"):
+        SequenceCache([reqs[1], (KVRequest(2, 16), None, 0)], 640, allocate=False)
+
+
+def test_guard_words_around_the_pools_show_a_stray_write():
+    import torch
+    c = SequenceCache([(KVRequest(2, 16), None, None)], 640, dtype=torch.float32, device="cpu")
+    g = c.groups[0]
+    c.check_guards()
+    assert float(g.k.abs().sum()) == 0.0 and g.k.is_contiguous() and g.k.data_ptr() % 16 == 0
+    g._v_store[-3] = 0.0                                   # what a write one page beyond the pool would do
+    with pytest.raises(CacheError, match="guard words"):
+        c.check_guards()

@@ -326,3 +326,33 @@ def test_kernels_report_no_bounded_wait_that_ran_out(model_folders):
     res = eng.generate(list(toks.values()), GenerateOptions(max_tokens=8, ignore_eos=True))
     assert all(r.completion_tokens == 8 for r in res)
     eng.check_kernels()
+
+
+def test_stats_count_what_the_steps_had_to_do(model_folders):
+    """Tokens, steps, bytes and flops of a prompt step, three one-token steps and a generation call, against the
+    sizes of configuration B worked out by hand."""
+    from exl3_server_b200 import Engine, GenerateOptions, StepEntry
+    cfg = TINY["B"]["cfg"]
+    eng = Engine.from_folder(model_folders["B"], dtype="bfloat16", max_tokens=1024)
+    H, I, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    layer = (q + 2 * kv) * H + H * q + 3 * I * H                       # matrix weights of a layer
+    norms = (2 * L + 1) * H
+    assert eng.model.weight_bytes() == 2 * (L * layer + norms + V * H)   # the untied head's matrix; the embedding is not read
+    s = eng.open()
+    eng.step([StepEntry(s, list(range(1, 41)), "last")])
+    for t in (5, 6, 7):
+        eng.step([StepEntry(s, [t], "last")])
+    st = eng.stats
+    assert (st.steps, st.prompt_steps, st.decode_steps, st.tokens) == (4, 1, 3, 43)
+    assert st.weight_bytes == 4 * eng.model.weight_bytes()
+    per_token = 2 * L * 2 * kv                                          # bfloat16 keys and values of every layer
+    assert st.cache_bytes == per_token * (40 + 41 + 42 + 43)
+    keys = 40 * 41 // 2 + 41 + 42 + 43
+    want = 2.0 * (L * layer + norms) * 43 + 2.0 * V * H * 4 + 4.0 * L * q * keys
+    assert abs(st.flops - want) <= 1e-9 * want
+    eng.close(s)
+    eng.generate([[1, 2, 3], [4, 5]], GenerateOptions(max_tokens=5, ignore_eos=True))
+    g = eng.last_generate_stats
+    assert g.prompt_steps == 1 and g.decode_steps == 4 and g.tokens == 5 + 2 * 4
+    eng.check_kernels()                                                 # the cache's guard words among other things

@@ -521,3 +521,133 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
         unregister("position", "test_half_speed_rope")
         unregister("embedding", "test_two_tables")
         unregister("head", "test_softcap")
+
+
+# -- a mixer whose keys and values differ in width (its cache group has pools of two shapes) ----
+
+class WideValueMixer:
+    """Causal attention with narrow keys (16 per head) and wide values (32 per head), no position encoding,
+    written with tensor operations only, so that the same code runs inside the recorded decode step."""
+
+    HEADS, DK, DV = 2, 16, 32
+
+    @classmethod
+    def tensor_specs(cls, spec, prefix):
+        from exl3_server_b200.weights import TensorSpec
+        h = cls.HEADS
+        return [TensorSpec(prefix + "wq", (h * cls.DK, spec.width)), TensorSpec(prefix + "wk", (h * cls.DK, spec.width)),
+                TensorSpec(prefix + "wv", (h * cls.DV, spec.width)), TensorSpec(prefix + "wo", (spec.width, h * cls.DV))]
+
+    def __init__(self, spec, tensors, prefix, ctx):
+        self.w = {n: tensors[prefix + n].float() for n in ("wq", "wk", "wv", "wo")}
+
+    def cache_request(self):
+        from exl3_server_b200.parts import KVRequest
+        return KVRequest(self.HEADS, self.DK, 0, value_dim=self.DV)
+
+    def state_request(self):
+        return None
+
+    def forward(self, x, batch, kv, state):
+        T, H, P = x.shape[0], self.HEADS, kv.page_size
+        xf = x.float()
+        q = (xf @ self.w["wq"].T).view(T, H, self.DK)
+        k = (xf @ self.w["wk"].T).view(T, H, self.DK)
+        v = (xf @ self.w["wv"].T).view(T, H, self.DV)
+        rows, pos = batch.tok_seq.long(), batch.tok_pos.long()
+        table = kv.block_table.long()
+        page = table[rows, pos // P]
+        kv.k[page, :, pos % P] = k.to(kv.k.dtype)
+        kv.v[page, :, pos % P] = v.to(kv.v.dtype)
+        mine = table[rows]                                           # [T, pages]; -1 beyond a row's pages
+        keys = kv.k[mine].permute(0, 2, 1, 3, 4).reshape(T, H, -1, self.DK).float()
+        vals = kv.v[mine].permute(0, 2, 1, 3, 4).reshape(T, H, -1, self.DV).float()
+        s = torch.einsum("thd,thkd->thk", q, keys) / math.sqrt(self.DK)
+        later = torch.arange(keys.shape[2], device=x.device)[None, :] > pos[:, None]
+        s = s.masked_fill(later[:, None, :], float("-inf"))
+        o = torch.einsum("thk,thkd->thd", torch.softmax(s, dim=-1), vals)
+        return (o.reshape(T, -1) @ self.w["wo"].T).to(x.dtype)
+
+
+@dataclass
+class Toy3Config:
+    width: int
+    vocab: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["width"], d["vocab"])
+
+    def to_dict(self):
+        return {"architectures": ["ToyWideValueLM"], "width": self.width, "vocab": self.vocab}
+
+
+def toy3_plan(cfg):
+    from exl3_server_b200.parts import (EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerSpec, MixerSpec, ModelPlan,
+                                        NormSpec, ScheduleEntry)
+    layers = [LayerSpec("prenorm", MixerSpec("test_wide_value", width=cfg.width),
+                        FeedForwardSpec("swiglu", cfg.width, 48), NormSpec("rms", cfg.width, 1e-5),
+                        NormSpec("rms", cfg.width, 1e-5), 1.0,
+                        names={"mixer": f"w.{i}.m.", "feed_forward": f"w.{i}.f.", "mixer_norm": f"w.{i}.n1.",
+                               "feed_forward_norm": f"w.{i}.n2."}) for i in range(2)]
+    return ModelPlan("ToyWideValueLM", EmbeddingSpec(cfg.vocab, cfg.width, 1.0, "w.emb"), layers,
+                     [ScheduleEntry(0), ScheduleEntry(1)], NormSpec("rms", cfg.width, 1e-5), "w.norm.",
+                     HeadSpec(cfg.vocab, cfg.width, 1.0, None, "w.head"), max_positions=0)
+
+
+def toy3_plain_logits(w, cfg, ids):
+    w = {k: v.double() for k, v in w.items()}
+    L, H, DK, DV = len(ids), WideValueMixer.HEADS, WideValueMixer.DK, WideValueMixer.DV
+    h = w["w.emb"][torch.tensor(ids)]
+    for i in range(2):
+        p = f"w.{i}."
+        r = P.rms_norm(h, w[p + "n1.weight"], 1e-5)
+        q = P.linear(r, w[p + "m.wq"]).view(L, H, DK).transpose(0, 1)
+        k = P.linear(r, w[p + "m.wk"]).view(L, H, DK).transpose(0, 1)
+        v = P.linear(r, w[p + "m.wv"]).view(L, H, DV).transpose(0, 1)
+        s = (q @ k.transpose(1, 2)) / math.sqrt(DK)
+        s = s.masked_fill(torch.arange(L)[None, :] > torch.arange(L)[:, None], float("-inf"))
+        o = (torch.softmax(s, dim=-1) @ v).transpose(0, 1).reshape(L, -1)
+        h = h + P.linear(o, w[p + "m.wo"])
+        r = P.rms_norm(h, w[p + "n2.weight"], 1e-5)
+        h = h + P.swiglu(r, w[p + "f.gate_proj.weight"], w[p + "f.up_proj.weight"], w[p + "f.down_proj.weight"])
+    return P.linear(P.rms_norm(h, w["w.norm.weight"], 1e-5), w["w.emb"])     # no head tensor: tied
+
+
+def test_toy_mixer_with_keys_and_values_of_different_widths(tmp_path):
+    """A mixer from outside whose cache holds 16 numbers per key and 32 per value: the cache makes a group with two
+    pool shapes for it, and the step function, the decode graphs and slot reuse work unchanged.  The head's tie is
+    left to the checkpoint (no head tensor: tied)."""
+    from exl3_server_b200 import Engine
+    from exl3_server_b200.config import register_architecture, unregister_architecture
+    from exl3_server_b200.engine.model import plan_manifest
+    from exl3_server_b200.parts import register_mixer, unregister
+    from exl3_server_b200.weights import write_safetensors
+    from exl3_server_b200.weights.random_init import random_tensors
+    cfg = Toy3Config(width=32, vocab=40)
+    register_mixer("test_wide_value", WideValueMixer)
+    register_architecture(["ToyWideValueLM"], Toy3Config, toy3_plan)
+    try:
+        folder = str(tmp_path)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg.to_dict(), f)
+        tensors = dict(random_tensors(plan_manifest(toy3_plan(cfg)), seed=8, std=0.2, norm_std=0.1))
+        assert "w.head" not in tensors                                  # optional and not written: the head is tied
+        write_safetensors(os.path.join(folder, "model.safetensors"), tensors.items())
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=1024)
+        group = eng.cache.groups[0]
+        assert group.k.shape[-1] == 16 and group.v.shape[-1] == 32 and eng.model.head.tied
+        rng = np.random.default_rng(2)
+        reqs = {f"r{i}": rng.integers(0, cfg.vocab, n).tolist() for i, n in enumerate([70, 5, 130, 1])}
+        want = {rid: toy3_plain_logits(tensors, cfg, t).numpy() for rid, t in reqs.items()}
+        ids = list(reqs)
+        for trace in (whole_trace(reqs), tail_trace(reqs, 32),
+                      batched_trace(reqs, [[ids[0], ids[1], ids[3]], [ids[2], ids[1]]],
+                                    {ids[0]: 60, ids[1]: 2, ids[2]: 100, ids[3]: 1})):
+            got = run_trace(eng, trace)
+            for rid in got:
+                assert rel_err(got[rid], want[rid]) <= 2e-5, rid
+        assert eng.cache.tokens_held() == 0
+    finally:
+        unregister_architecture(["ToyWideValueLM"])
+        unregister("mixer", "test_wide_value")
