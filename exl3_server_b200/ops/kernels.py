@@ -223,8 +223,8 @@ def gemv_bf16_normed(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
     if scale is not None:
         ss_in, eps, width = scale
-        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] != 16:
-            raise KernelLibraryError("gemv_bf16_normed: ss must be float32 [16, blocks]")
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] < M:
+            raise KernelLibraryError("gemv_bf16_normed: ss must be float32 [rows >= M, blocks]")
         _contig(ss_in, "ss")
         ss_blocks = ss_in.shape[1]
     if resid is not None:

@@ -25,8 +25,17 @@ from ..ops import kernels as K
 from .base import RawNormed
 
 
+import os
+
 # Rows up to which bfloat16 projections go through the skinny tcgen05 GEMM (17 rows and more; the GEMV below).
 SKINNY_ROWS = 64
+# Bytes of weights from which the skinny GEMM also takes 1 to 16 rows: its TMA stream is faster than the GEMV's
+# per-thread copies once a matrix is large (in chains of one kernel: 53 MB 11.1 against 14.0 us, 134 MB 24.0
+# against 27.7 us, 32 MB 8.1 against 7.7 us).  Inside a step the 53 MB matrix gains only from 8 rows on (batch 8
+# at the 2B sizes 3.40 -> 3.32 ms, batch 1 1.51 -> 1.53 ms), the larger ones always (8B sizes, batch 1: 3.38 ->
+# 3.31 ms).
+SKINNY_MIN_BYTES = int(os.environ.get("EXL3_SKINNY_MIN_BYTES", 48 << 20))
+SKINNY_MIN_BYTES_FEW_ROWS = int(os.environ.get("EXL3_SKINNY_MIN_BYTES_FEW", 100 << 20))     # fewer than 8 rows
 
 
 class Linear:
@@ -43,7 +52,8 @@ class Linear:
         skinny GEMM, or None (float32, sizes they refuse, too many rows)."""
         if self.dtype != torch.bfloat16 or self.in_features % 8 != 0:
             return None
-        if rows <= K.GEMV_MAX_ROWS:
+        if rows <= K.GEMV_MAX_ROWS and self.weight.numel() * 2 < (SKINNY_MIN_BYTES if rows >= 8
+                                                                    else SKINNY_MIN_BYTES_FEW_ROWS):
             return K.gemv_bf16_normed
         if rows <= SKINNY_ROWS:
             return K.gemm_skinny
