@@ -165,15 +165,18 @@ class Attention:
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
         """``(keys per chunk, head_split)`` for the tensor-core decode kernel: chunks of whole pages (a power of two
         of them, at most 64 of 16 KB), and whether the query heads of a kv head are worked on as one group or as two
-        (``head_split`` 2: twice the work items, each merge half the size).  By a small model of the kernel's time:
-        a warp walks its chunk at about 0.6 us per 16 KB of keys and values when it is alone (1.0 us with more than
-        8 query heads in its group); all warps together cannot read faster than the memory does; and the chunks of
-        a (token, group of heads), when there is more than one, are merged by a single warp, which costs about 3 us
-        for the records' trip through memory and the ticket, plus 1.5 us for every 8 KB of records (the group's
-        heads x the head's size x the chunks, in float32).  So few long chunks win for wide groups (16 query heads
-        of 128 on a kv head at 2,048 tokens: 32 chunks cost 59 us, 4 cost 20), one chunk wins for short contexts
-        (no merge at all), and many short chunks only where they are needed to give every SM work.  The choice
-        depends on the step's size, not on a token's position: results differ between batch sizes by rounding."""
+        (``head_split`` 2: twice the work items, each merge half the size).  By a small model of the kernel's time,
+        its constants fitted to sweeps at four head layouts (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128) and
+        batches of 1 to 64: a warp walks its chunk at about 0.9 us per 16 KB of keys and values (1.4 us with more
+        than 8 query heads in its group); when there are more chunks than warps a warp takes several in turn; all
+        warps together cannot read faster than the memory does; and the chunks of a (token, group of heads), when
+        there is more than one, are merged by a single warp: about 4 us for the records' trip through memory and
+        the ticket, plus 0.5 us per chunk, plus 0.01 us per chunk for every group that merges at the same time,
+        twice that for groups of more than 8 heads (two passes).  So few long chunks win for wide groups (16 query
+        heads of 128 on a kv head at 2,048 tokens: 32 chunks cost 59 us, 4 cost 20), one chunk wins for short
+        contexts and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks
+        only where they are needed to give every SM work.  The choice depends on the step's size, not on a token's
+        position: results differ between batch sizes by rounding."""
         s = self.spec
         keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
         pages_seq = max(1, (keys + page - 1) // page)
@@ -185,16 +188,17 @@ class Attention:
             g = group // head_split
             if g > 16:
                 continue
-            stage_us = 1.0 if g > 8 else 0.6
-            stream_us = T * s.kv_heads * head_split * pages_seq * wide * 16384 / 6.0e6     # all pages at 6 TB/s
+            stage_us = 1.4 if g > 8 else 0.9
+            groups = T * s.kv_heads * head_split
+            stream_us = groups * pages_seq * wide * 16384 / 6.0e6     # all pages at 6 TB/s
             per = 1
             while True:
                 n = (pages_seq + per - 1) // per
                 if n + (1 if s.window > 0 else 0) <= K.ATTN_DECODE_MAX_CHUNKS:     # a window may straddle one chunk more
-                    rounds = (T * s.kv_heads * head_split * n + warps - 1) // warps
+                    rounds = (groups * n + warps - 1) // warps
                     cost = max(rounds * per * wide * stage_us, stream_us)
                     if n > 1:
-                        cost += 3.0 + 1.5 * n * g * s.head_dim / 2048.0
+                        cost += 4.0 + n * (0.5 + 0.01 * groups) * (2.0 if g > 8 else 1.0)
                     if best is None or cost < best[0] - 1e-9:
                         best = (cost, per, head_split)
                 if per >= pages_seq or per * wide >= 64:
