@@ -57,13 +57,14 @@ size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
 
 size_t exl3_argmax_scratch_bytes(int R, int V);
 // Whole prompts on tcgen05 tensor cores with TMA loads from the paged cache (bfloat16, heads of 64 or 128, pages
-// of 64, tiles of 128 queries); see attention_prefill_tc.cu.
+// of 64, tiles of 128 queries); variant 0: chosen by the number of blocks, 1: two blocks an SM, 2: four (heads of 64);
+// see attention_prefill_tc.cu.
 int exl3_attn_prefill_tc_supported(int dtype, int hd, int page);
 int exl3_attn_prefill_tc_status();
 int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
                          const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
                          const int* row_start, const int* row_pos0, const int* tile_seq, const int* tile_q0,
-                         int n_tiles, int nh, int nkv, int hd, int page, int window, float scale,
+                         int n_tiles, int nh, int nkv, int hd, int page, int window, float scale, int variant,
                          cudaStream_t stream);
 
 // exl3_gemv_bf16 as the two sides of a norm that is no kernel of its own.  With ss_in the input is the x_raw of a

@@ -410,6 +410,233 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FA_TMEM_COLS) : "memory");
 }
 
+
+// ---- heads of 64: four blocks per SM ---------------------------------------------------------------
+// What bounds the kernel above is the chain of fixed latencies inside one page of a row's softmax, with two warps
+// per scheduler to hide it.  This variant trades the overlap inside a block (one S buffer instead of two, P written
+// over S, a ring of two pages) for blocks: 128 columns of tensor memory, 49 KB of shared memory and at most 102
+// registers a thread let four blocks share an SM, sixteen softmax warps instead of eight.  A block alone is
+// slower (1.64 against 1.53 us a page), so the variant is used when the blocks do not all fit the GPU at once
+// (more than four per SM): 452 against 530 us at 8,192 tokens with 36 heads, 84 against 96 us at 3,072, 117 against
+// 142 us for 24 prompts of 16 to 2,048 tokens with 16 heads; at 2,048 tokens, where one wave of blocks runs and the
+// heaviest tile's 32 pages are the kernel's length, the kernel above stays (48.7 against 52.6 us).  Same
+// arithmetic in the same order per row: the two give the same numbers bit for bit.
+constexpr int F4_STAGES = 2;
+constexpr uint32_t F4_SMEM = fa_q_bytes(64) + 2 * F4_STAGES * fa_kv_bytes(64) + 1024 + 128;
+
+__global__ void __launch_bounds__(FA_THREADS, 4)
+attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
+                        const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
+                        const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
+  extern __shared__ unsigned char fa_smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr uint32_t QB = fa_q_bytes(64), KVB = fa_kv_bytes(64);
+  unsigned char* sQ = base;
+  unsigned char* sK = sQ + QB;
+  unsigned char* sV = sK + F4_STAGES * KVB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + F4_STAGES * KVB);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                   // [2]
+  uint64_t* kv_free = kv_full + F4_STAGES;        // [2]
+  uint64_t* s_full = kv_free + F4_STAGES;         // S written by the tensor core
+  uint64_t* p_full = s_full + 1;                  // P written over S by all 128 softmax threads
+  uint64_t* pv_done = p_full + 1;                 // O += P V finished: the S columns are free again
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x, tile = blockIdx.y;
+  const int b = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = row_start[b + 1] - row_start[b];
+  const int pos0 = row_pos0[b];
+  const int g = head / (nh / nkv);
+  const int rows = min(FA_BQ, n_new - q0);
+  const int p_first = pos0 + q0, p_last = pos0 + q0 + rows - 1;
+  const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int page_lo = k_lo / FA_BK, page_hi = p_last / FA_BK;
+  const int n_blocks = page_hi - page_lo + 1;
+  const int* bt = block_table + (int64_t)b * bt_stride;
+
+  if (threadIdx.x == 0) {
+    fa_mbar_init(q_full, 1);
+    for (int i = 0; i < F4_STAGES; ++i) { fa_mbar_init(kv_full + i, 1); fa_mbar_init(kv_free + i, 1); }
+    fa_mbar_init(s_full, 1);
+    fa_mbar_init(p_full, 128);
+    fa_mbar_init(pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(fa_smem_u32(tmem_slot)), "r"(128) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fa_fence_before();
+  __syncthreads();
+  fa_fence_after();
+  const uint32_t tmem_base = *tmem_slot;                    // columns: S 0..63 (P over 0..31), O 64..127
+  const uint32_t tmem_o = tmem_base + 64;
+  bool ok = true;
+
+  if (warp == 4) {
+    // ---- issuer: TMA and MMA -----------------------------------------------------------
+    if (lane == 0) {
+      fa_mbar_expect_tx(q_full, QB);
+      fa_tma_2d(sQ, &map_q, q_full, head * 64, row_start[b] + q0);
+    }
+    auto load_kv = [&](int j) {
+      const int st = j % F4_STAGES;
+      const int pg = bt[page_lo + j];
+      if (lane == 0) {
+        fa_mbar_expect_tx(kv_full + st, 2 * KVB);
+        fa_tma_2d(sK + st * KVB, &map_k, kv_full + st, 0, (pg * nkv + g) * FA_BK);
+        fa_tma_2d(sV + st * KVB, &map_v, kv_full + st, 0, (pg * nkv + g) * FA_BK);
+      }
+    };
+    for (int j = 0; j < F4_STAGES && j < n_blocks; ++j) load_kv(j);
+    ok = fa_mbar_wait(q_full, 0);
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int st = j % F4_STAGES;
+      if (!fa_mbar_wait(kv_full + st, (j / F4_STAGES) & 1)) { ok = false; break; }
+      // S_j goes where P of page j - 1 still is until that page's product is done
+      if (j > 0 && !fa_mbar_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+      fa_fence_after();
+      if (lane == 0) {
+        const uint64_t da = fa_desc(fa_smem_u32(sQ));
+        const uint64_t db = fa_desc(fa_smem_u32(sK + st * KVB));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) fa_umma(tmem_base, da + 2 * k, db + 2 * k, FA_IDESC_S, k > 0);
+        fa_commit(s_full);
+      }
+      __syncwarp();
+      // the stage of page j - 1 is free (its product is done): the page after next goes there
+      if (j >= 1 && j + 1 < n_blocks) load_kv(j + 1);
+      if (!fa_mbar_wait(p_full, j & 1)) { ok = false; break; }
+      fa_fence_after();
+      if (lane == 0) {
+        const uint64_t db = fa_desc(fa_smem_u32(sV + st * KVB));
+#pragma unroll
+        for (int k = 0; k < FA_BK / 16; ++k)
+          fa_umma_ts(tmem_o, tmem_base + 8 * k, db + 128 * k, FA_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        fa_commit(pv_done);
+      }
+      __syncwarp();
+    }
+    if (!ok) {
+      for (int j = max(0, n_blocks - F4_STAGES); j < n_blocks; ++j) fa_mbar_wait(kv_full + j % F4_STAGES, (j / F4_STAGES) & 1);
+      if (lane == 0) atomicExch(&g_fa_error, 1);
+    }
+  } else {
+    // ---- softmax and epilogue: thread r = query row r = TMEM lane r ---------------------
+    const int r = threadIdx.x;
+    const int p = p_first + r;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_used = -INFINITY, l_run = 0.0f;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      if (!fa_mbar_wait(s_full, j & 1)) { ok = false; break; }
+      fa_fence_after();
+      uint32_t sr[2][32];
+      fa_ld32(tmem_base + lane_addr, sr[0]);
+      fa_ld32(tmem_base + lane_addr + 32, sr[1]);
+      fa_wait_ld();
+      const int key0 = (page_lo + j) * FA_BK;
+      const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
+      if (need_mask) {
+        const int lo_key = (window > 0) ? p - window : -1;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int key = key0 + h * 32 + c;
+            const bool dead = (key > p) | (key <= lo_key);
+            sr[h][c] = dead ? 0xff800000u : sr[h][c];
+          }
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      mx *= scale_log2;
+      const bool grow = mx > m_used + FA_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : m_used;
+        const float corr = (m_used == -INFINITY) ? 0.0f : fa_exp2(m_used - m_new);
+        if (j > 0) {
+          // the product of page j - 1 is in O: S_j was issued after it was done.  16 columns at a time: the
+          // row of scores stays in its registers meanwhile
+#pragma unroll 1
+          for (int c0 = 0; c0 < 64; c0 += 16) {
+            uint32_t o[16];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                         : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7]),
+                           "=r"(o[8]), "=r"(o[9]), "=r"(o[10]), "=r"(o[11]), "=r"(o[12]), "=r"(o[13]), "=r"(o[14]), "=r"(o[15])
+                         : "r"(tmem_o + lane_addr + c0));
+            fa_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                         ::"r"(tmem_o + lane_addr + c0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+                           "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+          }
+          fa_wait_st();
+        }
+        l_run *= corr;
+        m_used = m_new;
+      }
+      const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {                         // two keys per column, written over the scores' registers
+        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), scale_log2, -mref));
+        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), scale_log2, -mref));
+        sum4[c & 3] += e0 + e1;
+        sr[0][c] = fa_pack(e0, e1);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      fa_st32(tmem_base + lane_addr, sr[0]);
+      fa_wait_st();
+      fa_fence_before();
+      fa_mbar_arrive(p_full);
+    }
+    if (ok) {
+      const int jl = n_blocks - 1;
+      ok = fa_mbar_wait(pv_done, jl & 1);
+      if (ok) {
+        fa_fence_after();
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * 64;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t o[32];
+          fa_ld32(tmem_o + lane_addr + c0, o);
+          fa_wait_ld();
+          if (r < rows) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint4 w;
+              const int c = ch * 8;
+              w.x = fa_pack(__uint_as_float(o[c + 0]) * inv, __uint_as_float(o[c + 1]) * inv);
+              w.y = fa_pack(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+              w.z = fa_pack(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+              w.w = fa_pack(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+            }
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(&g_fa_error, 2);
+  }
+
+  fa_fence_before();
+  __syncthreads();
+  fa_fence_after();
+  if (warp == 4)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128) : "memory");
+}
+
 // ---- host side --------------------------------------------------------------------------
 
 typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -461,11 +688,15 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
                                     const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
                                     const int* row_start, const int* row_pos0, const int* tile_seq,
                                     const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
-                                    float scale, cudaStream_t stream) {
+                                    float scale, int variant, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   if (!exl3_attn_prefill_tc_supported(DT_BF16, hd, page)) {
     set_error("attn_prefill_tc: needs bfloat16, head_dim 64 or 128 and pages of 64, got head_dim %d page %d", hd, page);
     return ERR_UNSUPPORTED;
+  }
+  if (variant < 0 || variant > 2 || (variant == 2 && hd != 64)) {
+    set_error("attn_prefill_tc: variant is 0 (chosen), 1 (two blocks an SM) or 2 (four blocks an SM, heads of 64), got %d", variant);
+    return ERR_BAD_ARGUMENT;
   }
   if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || q_row_stride % 8 != 0) {
     set_error("attn_prefill_tc: bad sizes tiles=%d T=%d heads=%d kv_heads=%d window=%d", n_tiles, T, nh, nkv, window);
@@ -476,8 +707,15 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
     return ERR_ALIGNMENT;
   }
   static bool configured = false;
+  static int sms = 148;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem(64));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms < 1) sms = 148;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F4_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem(64));
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem(128));
     if (e != cudaSuccess) { set_error("attn_prefill_tc: cannot get %u bytes of shared memory: %s", fa_smem(128), cudaGetErrorString(e)); return (int)e; }
@@ -491,7 +729,13 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   rc = fa_make_map(&map_v, v_pool, n_pool_rows, hd, hd, FA_BK);
   if (rc) return rc;
   dim3 grid(nh, n_tiles);
-  if (hd == 64)
+  // four blocks an SM when there are more blocks than that holds at once
+  const bool four = hd == 64 && (variant == 2 || (variant == 0 && (int64_t)n_tiles * nh > 4 * (int64_t)sms));
+  if (four)
+    attn_prefill_tc4_kernel<<<grid, FA_THREADS, F4_SMEM, stream>>>(
+        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
+        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+  else if (hd == 64)
     attn_prefill_tc_kernel<64><<<grid, FA_THREADS, fa_smem(64), stream>>>(
         map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
         tile_q0, nh, nkv, window, scale * 1.4426950408889634f);

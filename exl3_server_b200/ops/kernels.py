@@ -379,9 +379,11 @@ def attn_prefill_tc_status() -> int:
 def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     block_table: torch.Tensor, row_start: torch.Tensor, row_pos0: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, heads: int, kv_heads: int,
-                    head_dim: int, page: int, window: int, scale: float) -> torch.Tensor:
+                    head_dim: int, page: int, window: int, scale: float, variant: int = 0) -> torch.Tensor:
     """Causal attention of whole prompts on tcgen05 tensor cores (tiles of 128 queries; see
-    attention_prefill_tc.cu).  ``k_pool`` / ``v_pool``: one layer's ``[pages, kv_heads, 64, head_dim]``."""
+    attention_prefill_tc.cu).  ``k_pool`` / ``v_pool``: one layer's ``[pages, kv_heads, 64, head_dim]``.
+    ``variant``: 0 lets the kernel choose between two and four blocks per SM (heads of 64) by the number of
+    blocks; 1 and 2 force the one or the other (the same numbers either way)."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_prefill_tc: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
@@ -391,7 +393,7 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
         _ptr(q), _c_int64(q_row_stride), _c_int(q.shape[0]), _ptr(out), _ptr(k_pool), _ptr(v_pool),
         _c_int64(pool_rows), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start), _ptr(row_pos0),
         _ptr(tile_seq), _ptr(tile_q0), _c_int(n_tiles), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-        _c_int(page), _c_int(window), _c_float(scale), _stream()), "attn_prefill_tc")
+        _c_int(page), _c_int(window), _c_float(scale), _c_int(variant), _stream()), "attn_prefill_tc")
     return out
 
 
