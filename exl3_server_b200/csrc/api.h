@@ -89,6 +89,16 @@ int exl3_gemm_skinny_status();
 int exl3_gemm_skinny_max_rows();
 int exl3_gemm_skinny_split(int N, int K);
 
+// Projections of many rows with two blocks of a cluster as one tensor core (tcgen05.mma.cta_group::2, tiles of
+// 256 x 256): input and epilogues as exl3_gemm_skinny's (0 plain, 1 gated, 2 residual and the next norm's pieces),
+// y bfloat16; ss_out is [M, exl3_gemm_pair_ss_blocks(N)].  exl3_gemm_pair_status() returns and clears the code a
+// kernel left when one of its bounded waits ran out.
+int exl3_gemm_pair(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int epilogue,
+                   const float* ss_in, int ss_blocks, float eps, float width, float* h, float rho,
+                   const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out, cudaStream_t stream);
+int exl3_gemm_pair_status();
+int exl3_gemm_pair_ss_blocks(int N);
+
 // Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64 or 128, pages of 64, up
 // to 16 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing

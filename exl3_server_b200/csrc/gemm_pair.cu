@@ -1,0 +1,516 @@
+// Projections of many rows (prompts) on the 5th-generation tensor cores, two blocks of a cluster as one tensor core:
+//   y[M,N] = x[M,K] . w[N,K]^T (+ bias), bfloat16 operands, float32 accumulation in tensor memory
+// In the reference these are library matmuls with separate element-wise ops around them (src/model.cpp:549,
+// 583-586, 600-611).
+//
+// A pair of blocks (a cluster of two, on two neighbouring SMs) works on one tile of 256 x 256 outputs with
+// tcgen05.mma.cta_group::2 (M 256, N 256, K 16): each block copies its 128 rows of x and its 128 rows of w into its
+// own shared memory (16 KB + 16 KB per 64 of K, a ring of five or six stages), the pair's even block issues the
+// instructions, which read both blocks' shared memory, and each block finds its 128 rows of the accumulator in its
+// own tensor memory.  Per flop a block copies and reads two thirds of what a block that works alone on 128 x 256
+// does; that is what lets the tensor pipe run without waiting for shared memory.
+//
+//   warp 0    TMA producer (both blocks): cp.async.bulk.tensor tiles, their bytes counted on the even block's
+//             mbarrier; no multicast, every block copies what it needs itself
+//   warp 1    even block: one thread issues the MMAs; tcgen05.commit frees ring stages in both blocks and hands
+//             accumulators to both blocks' epilogues.  Both blocks: allocates and frees the tensor memory
+//   warps 2-5 epilogue (both blocks): thread = row; 64 accumulator columns at a time from tensor memory, results
+//             into 128B-swizzled staging tiles of 32 rows x 128 bytes, which TMA stores write out (clipped at the
+//             matrix's edges), so that no thread stores a row-strided sliver itself
+// Two accumulators (2 x 256 of the 512 columns) let the epilogue of one tile overlap the products of the next.
+// Pairs are persistent; tiles go round-robin over them, M fastest, so that pairs that run together share w in L2.
+//
+// Input: x, or a norm's output in two pieces (x_raw = h * w_norm and per-row pieces of sum(h^2)): the accumulator is
+// multiplied by k = rsqrt(sum / width + eps) per row.
+// Epilogues: 0 y bfloat16; 1 silu(gate) * up for a weight whose rows are 8 gate rows, the 8 up rows of the same
+// features, and so on (y is N/2 wide); 2 the output times rho is added to the float32 residual h in place, and the
+// next norm's pieces are left: x_raw = h * w_norm and, per row and tile of 256 columns, sum(h^2).  For 2 the residual
+// does not wait for the epilogue: while the tensor core is busy with earlier tiles, the epilogue warps bring the
+// tile of h into the accumulator itself (TMA to shared memory, divided by rho * k, tcgen05.st), the products are
+// added on top of it, and the epilogue only multiplies by rho * k, adds rho * bias and writes.  (The product is
+// therefore not rounded to bfloat16 before it is added, as it is where the addition is a separate step.)
+//
+// Every wait on an mbarrier is bounded: when one runs out the kernel records a code, leaves its loops, waits
+// (bounded) for the copies it may have in flight, meets its partner at the cluster barrier that every path reaches,
+// frees its tensor memory and returns; exl3_gemm_pair_status() reads the code.
+#include "api.h"
+#include "tcgen05.cuh"
+
+#include <cuda.h>
+
+namespace exl3 {
+
+using namespace tc5;
+
+constexpr int GP_BM = 256, GP_BN = 256, GP_BK = 64;
+constexpr int GP_THREADS = 192;
+constexpr uint32_t GP_STAGE_A = 128 * GP_BK * 2, GP_STAGE_B = 128 * GP_BK * 2;       // per block
+constexpr uint32_t GP_BOX = 32 * 128;                                                  // a staging tile: 32 rows x 128 bytes
+__host__ __device__ constexpr int gp_stages(int epi) { return epi == 2 ? 5 : 6; }
+__host__ __device__ constexpr int gp_boxes(int epi) { return epi == 2 ? 4 : 2; }       // staging tiles per epilogue warp
+__host__ __device__ constexpr uint32_t gp_smem(int epi) {
+  return 1024 /* alignment */ + gp_stages(epi) * (GP_STAGE_A + GP_STAGE_B) + 4 * gp_boxes(epi) * GP_BOX +
+         GP_BN * 4 /* norm weights */ + GP_BN * 2 /* bias */ + 256 /* barriers */;
+}
+constexpr uint32_t GP_IDESC = idesc_bf16(GP_BM, GP_BN);
+
+static __device__ int g_gp_error = 0;
+
+// Barrier 1 over the 128 epilogue threads, returning whether the predicate held for all of them.
+__device__ inline bool gp_epilogue_all(bool pred) {
+  int r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.s32 %0, 1, 0, q;\n\t}"
+               : "=r"(r) : "r"((int)pred) : "memory");
+  return r != 0;
+}
+__device__ inline void gp_tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ inline uint32_t gp_pack(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+// 16 bytes number j (0..7) of row r of a 128B-swizzled staging tile.
+__device__ inline uint4* gp_box_chunk(unsigned char* box, int r, int j) {
+  return reinterpret_cast<uint4*>(box + r * 128 + ((j ^ (r & 7)) << 4));
+}
+
+struct PairArgs {
+  const __nv_bfloat16* bias;
+  int M, N, K;
+  const float* ss_in;        // [rows >= M, ss_blocks] or null
+  int ss_blocks;
+  float eps, width;
+  float rho;
+  const void* norm_w;        // [N], float32 or bfloat16
+  int norm_w_f32;
+  float* ss_out;             // [M, tiles of 256 columns]
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(GP_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_y,      // y (0, 1) or x_raw (2): bfloat16, boxes of 64 columns
+                 const __grid_constant__ CUtensorMap map_h,      // 2: the float32 residual, boxes of 32 columns
+                 const PairArgs a) {
+  constexpr int STAGES = gp_stages(EPI), BOXES = gp_boxes(EPI);
+  extern __shared__ unsigned char gp_smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gp_smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = base;
+  unsigned char* sB = base + STAGES * GP_STAGE_A;
+  unsigned char* boxes = base + STAGES * (GP_STAGE_A + GP_STAGE_B);       // [4 warps][BOXES] staging tiles
+  float* s_normw = reinterpret_cast<float*>(boxes + 4 * BOXES * GP_BOX);
+  __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(s_normw + GP_BN);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + GP_BN);
+  uint64_t* full = bars;                       // [STAGES] even block only: both blocks' copies landed
+  uint64_t* empty = bars + STAGES;             // [STAGES] each block: the MMAs that read the stage are done
+  uint64_t* acc_full = bars + 2 * STAGES;      // [2] each block: accumulator complete
+  uint64_t* acc_empty = acc_full + 2;          // [2] even block only: both blocks' epilogues are done with it
+  uint64_t* hbar = acc_empty + 2;              // [4 warps][4] epilogue 2: a tile of h landed in a staging tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(hbar + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();        // 0: issues the MMAs
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  if (threadIdx.x == 0) {
+    prefetch_map(&map_x);
+    prefetch_map(&map_w);
+    prefetch_map(&map_y);
+    if (EPI == 2) prefetch_map(&map_h);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 8); }
+    for (int i = 0; i < 16; ++i) mbar_init(hbar + i, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc_pair<512>(tmem_slot);
+  fence_before();
+  cluster_sync_all();                          // both blocks' barriers exist before either signals the other's
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_m = (a.M + GP_BM - 1) / GP_BM, n_n = (a.N + GP_BN - 1) / GP_BN;
+  const int n_tiles = n_m * n_n, kblocks = (a.K + GP_BK - 1) / GP_BK;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ---- producer: this block's halves of the pair's tiles ---------------------------------------------
+    uint32_t it = 0;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+      const int m0 = (tile % n_m) * GP_BM + (int)rank * 128, n0 = (tile / n_m) * GP_BN + (int)rank * 128;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t bar = cluster_addr(full + s, 0);
+          if (rank == 0) mbar_expect_tx(full + s, 2 * (GP_STAGE_A + GP_STAGE_B));
+          tma_load_2d_pair(sA + s * GP_STAGE_A, &map_x, bar, kb * GP_BK, m0);
+          tma_load_2d_pair(sB + s * GP_STAGE_B, &map_w, bar, kb * GP_BK, n0);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      if (lane == 0) atomicExch(&g_gp_error, 1);
+      // Copies still in flight must land before either block's shared memory goes away.  Their bytes are counted
+      // on the even block's barriers: it waits for the last stages it armed, and the partner stays until the
+      // cluster barrier at the end, which the even block reaches after these waits.
+      if (rank == 0)
+        for (uint32_t back = 1; back <= (uint32_t)STAGES && back <= it; ++back) {
+          const uint32_t j = it - back;
+          mbar_wait(full + (j % STAGES), (j / STAGES) & 1);
+        }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (even block) ----------------------------------------------------------------------------
+    if (rank == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++tcount) {
+        const uint32_t buf = tcount & 1;
+        // 0, 1: an accumulator is free from the start and after each epilogue; 2: it is ready when the epilogue
+        // warps have put the tile's residual into it
+        if (!mbar_wait(acc_empty + buf, ((tcount >> 1) & 1) ^ (EPI == 2 ? 0u : 1u))) { ok = false; break; }
+        fence_after();
+        const uint32_t d_tmem = tmem_base + buf * GP_BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full + s, (it / STAGES) & 1)) { ok = false; break; }
+          fence_after();
+          if (lane == 0) {
+            const uint64_t da = smem_desc_k128(smem_u32(sA + s * GP_STAGE_A));
+            const uint64_t db = smem_desc_k128(smem_u32(sB + s * GP_STAGE_B));
+#pragma unroll
+            for (int k = 0; k < GP_BK / 16; ++k)
+              mma_ss_pair(d_tmem, da + 2 * k, db + 2 * k, GP_IDESC, (EPI == 2 || kb > 0 || k > 0) ? 1u : 0u);
+            mma_commit_pair(empty + s);
+          }
+          __syncwarp();
+        }
+        if (!ok) break;
+        if (lane == 0) mma_commit_pair(acc_full + buf);
+        __syncwarp();
+      }
+      if (!ok && lane == 0) atomicExch(&g_gp_error, 2);
+    }
+  } else {
+    // ---- epilogue: thread = row of this block's 128 -----------------------------------------------------------
+    const int q = warp & 3;                               // the 32 TMEM lanes this warp may read
+    const int t = q * 32 + lane;
+    unsigned char* my_boxes = boxes + q * BOXES * GP_BOX;
+    uint64_t* my_hbar = hbar + q * 4;
+    const uint32_t acc_empty_addr[2] = {cluster_addr(acc_empty, 0), cluster_addr(acc_empty + 1, 0)};
+    const uint32_t lane_taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint32_t n_store = 0;                                 // 0, 1: staging tiles stored so far (they alternate)
+    uint32_t n_hload = 0;                                 // 2: tiles of h loaded so far (four staging tiles in turn)
+
+    // k of a row: what its accumulator is multiplied by
+    auto row_factor = [&](int row) {
+      float k = 1.0f;
+      if (a.ss_in && row < a.M) {
+        float ss = 0.0f;
+        for (int j = 0; j < a.ss_blocks; ++j) ss += __ldcg(a.ss_in + (int64_t)row * a.ss_blocks + j);
+        k = rsqrtf(ss / a.width + a.eps);
+      }
+      return k;
+    };
+    // 2: this warp's 32 rows of a tile of h, divided by rho * k, into accumulator `buf`; then the accumulator is
+    // handed to the MMA issuer.  False when a wait ran out.
+    auto preload = [&](int tile, uint32_t buf) -> bool {
+      const int row0 = (tile % n_m) * GP_BM + (int)rank * 128 + q * 32, n0 = (tile / n_m) * GP_BN;
+      const float inv = 1.0f / (a.rho * row_factor(row0 + lane));
+      if (lane == 0) tma_store_wait_read<0>();            // the last epilogue's stores have read the staging tiles
+      __syncwarp();
+      if (lane == 0)
+        for (int c = 0; c < 4; ++c) {
+          mbar_expect_tx(my_hbar + c, GP_BOX);
+          tma_load_2d(my_boxes + c * GP_BOX, &map_h, my_hbar + c, n0 + c * 32, row0);
+        }
+      bool good = true;
+      for (int c = 0; c < GP_BN / 32; ++c, ++n_hload) {
+        const int k = n_hload & 3;
+        good = __all_sync(0xffffffffu, mbar_wait(my_hbar + k, (n_hload >> 2) & 1));
+        if (!good) break;
+        uint32_t f[32];
+        unsigned char* box = my_boxes + k * GP_BOX;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 v = *gp_box_chunk(box, lane, j);
+          f[4 * j + 0] = __float_as_uint(__uint_as_float(v.x) * inv);
+          f[4 * j + 1] = __float_as_uint(__uint_as_float(v.y) * inv);
+          f[4 * j + 2] = __float_as_uint(__uint_as_float(v.z) * inv);
+          f[4 * j + 3] = __float_as_uint(__uint_as_float(v.w) * inv);
+        }
+        __syncwarp();                                     // every lane has read the staging tile
+        if (lane == 0 && c + 4 < GP_BN / 32) {
+          mbar_expect_tx(my_hbar + k, GP_BOX);
+          tma_load_2d(box, &map_h, my_hbar + k, n0 + (c + 4) * 32, row0);
+        }
+        gp_tmem_st32(lane_taddr + buf * GP_BN + c * 32, f);
+      }
+      if (!good) {
+        // loads that may still be in flight get the time to land before the block's shared memory goes away
+        for (int i = 0; i < 1000; ++i) __nanosleep(100);
+        return false;
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_addr[buf]);
+      return true;
+    };
+
+    if (EPI == 2) {
+      int tile = pair;
+      for (uint32_t b = 0; b < 2 && tile < n_tiles && ok; ++b, tile += n_pairs) ok = preload(tile, b);
+    }
+    uint32_t tcount = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tcount) {
+      const int row0 = (tile % n_m) * GP_BM + (int)rank * 128 + q * 32, n0 = (tile / n_m) * GP_BN;
+      const uint32_t buf = tcount & 1;
+      const int row = row0 + lane;
+      // the tile's bias and norm weights, once for all rows (the previous tile's readers are past their last read:
+      // they have met at the barrier after it); every thread comes here, whatever its verdict so far
+      if (!gp_epilogue_all(ok)) { ok = false; break; }
+      for (int c = t; c < GP_BN; c += 128) {
+        const int n = n0 + c;
+        s_bias[c] = (a.bias && n < a.N) ? a.bias[n] : __float2bfloat16(0.0f);
+        if (EPI == 2)
+          s_normw[c] = n >= a.N ? 0.0f : a.norm_w_f32 ? __ldg(static_cast<const float*>(a.norm_w) + n)
+                                                     : __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(a.norm_w) + n));
+      }
+      const float k_row = (EPI == 2 ? a.rho : 1.0f) * row_factor(row);
+      const float k_bias = EPI == 2 ? a.rho : 1.0f;
+      // (also the barrier after which the staged bias and norm weights may be read) one verdict for all 128
+      // threads, so that they leave the loop together
+      if (!gp_epilogue_all(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
+      fence_after();
+      const uint32_t taddr = lane_taddr + buf * GP_BN;
+      float sq = 0.0f;
+#pragma unroll 1
+      for (int s = 0; s < GP_BN / 64; ++s) {                // 64 accumulator columns at a time
+        uint32_t r0[32], r1[32];
+        __syncwarp();
+        tmem_ld32_issue(taddr + s * 64, r0);
+        tmem_ld32_issue(taddr + s * 64 + 32, r1);
+        if (EPI == 0 || (EPI == 1 && (s & 1) == 0)) {
+          // the store before the last one used this staging tile
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        tmem_ld_wait(r0);
+        tmem_ld_wait(r1);
+        float v[64];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[j] = fmaf(__uint_as_float(r0[j]), k_row, k_bias * __bfloat162float(s_bias[s * 64 + j]));
+          v[32 + j] = fmaf(__uint_as_float(r1[j]), k_row, k_bias * __bfloat162float(s_bias[s * 64 + 32 + j]));
+        }
+        if (EPI == 0) {
+          unsigned char* box = my_boxes + (n_store & 1) * GP_BOX;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *gp_box_chunk(box, lane, j) = make_uint4(gp_pack(v[8 * j], v[8 * j + 1]), gp_pack(v[8 * j + 2], v[8 * j + 3]),
+                                                     gp_pack(v[8 * j + 4], v[8 * j + 5]), gp_pack(v[8 * j + 6], v[8 * j + 7]));
+          fence_smem_to_tma();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < a.M && n0 + s * 64 < a.N) tma_store_2d(&map_y, box, n0 + s * 64, row0);
+            else tma_store_skip();
+          }
+          ++n_store;
+        } else if (EPI == 1) {
+          // four groups of (8 gate, 8 up) -> 32 outputs: half a staging tile
+          unsigned char* box = my_boxes + (n_store & 1) * GP_BOX;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float gate = v[g * 16 + j], up = v[g * 16 + 8 + j];
+              o[j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+            }
+            *gp_box_chunk(box, lane, (s & 1) * 4 + g) = make_uint4(gp_pack(o[0], o[1]), gp_pack(o[2], o[3]), gp_pack(o[4], o[5]), gp_pack(o[6], o[7]));
+          }
+          if (s & 1) {
+            fence_smem_to_tma();
+            __syncwarp();
+            if (lane == 0) {
+              if (row0 < a.M && n0 + (s >> 1) * 128 < a.N) tma_store_2d(&map_y, box, (n0 >> 1) + (s >> 1) * 64, row0);
+              else tma_store_skip();
+            }
+            ++n_store;
+          }
+        } else {
+          // v is the new h (columns beyond N: zero in h, in the products and in the staged bias).  Per step two
+          // float32 tiles of it and one bfloat16 tile of x_raw go out, in this order; a staging tile is written
+          // again a step later (x_raw's: two steps), when all but the two newest stores have read theirs.
+          unsigned char* xbox = my_boxes + (2 + (s & 1)) * GP_BOX;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) sq = fmaf(v[j], v[j], sq);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            unsigned char* hbox = my_boxes + half * GP_BOX;
+            if (lane == 0) tma_store_wait_read<2>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float* f = v + 32 * half + 4 * j;
+              *gp_box_chunk(hbox, lane, j) = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float* f = v + 32 * half + 8 * j;
+              const float* wn = s_normw + s * 64 + 32 * half + 8 * j;
+              *gp_box_chunk(xbox, lane, 4 * half + j) = make_uint4(gp_pack(f[0] * wn[0], f[1] * wn[1]), gp_pack(f[2] * wn[2], f[3] * wn[3]),
+                                                                   gp_pack(f[4] * wn[4], f[5] * wn[5]), gp_pack(f[6] * wn[6], f[7] * wn[7]));
+            }
+            fence_smem_to_tma();
+            __syncwarp();
+            if (lane == 0 && row0 < a.M) {
+              if (n0 + s * 64 + 32 * half < a.N) tma_store_2d(&map_h, hbox, n0 + s * 64 + 32 * half, row0);
+              else tma_store_skip();
+              if (half == 1) {
+                if (n0 + s * 64 < a.N) tma_store_2d(&map_y, xbox, n0 + s * 64, row0);
+                else tma_store_skip();
+              }
+            }
+          }
+        }
+      }
+      if (EPI == 2) {
+        if (row < a.M) a.ss_out[(int64_t)row * n_n + tile / n_m] = sq;
+        // the accumulator is free: the tile after next of this pair goes into it (or nobody waits for it)
+        const int next = tile + 2 * n_pairs;
+        fence_before();
+        if (next < n_tiles) ok = preload(next, buf);
+      } else {
+        fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_addr[buf]);
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+    if (!ok && lane == 0) atomicExch(&g_gp_error, 3);
+  }
+
+  fence_before();
+  cluster_sync_all();                          // nobody reads the partner's shared or tensor memory after this
+  fence_after();
+  if (warp == 1) tmem_free_pair<512>(tmem_base);
+}
+
+template <int EPI> static const void* gp_kernel() { return reinterpret_cast<const void*>(&gemm_pair_kernel<EPI>); }
+
+static void gp_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int blocks, int epi, cudaStream_t stream) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3(blocks);
+  cfg->blockDim = dim3(GP_THREADS);
+  cfg->dynamicSmemBytes = gp_smem(epi);
+  cfg->stream = stream;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
+// Pairs that the GPU runs at once (a pair needs two SMs of one cluster-capable group).
+static int gp_max_pairs(int epi) {
+  static int pairs[3] = {0, 0, 0};
+  if (pairs[epi]) return pairs[epi];
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int n = sms / 2;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  gp_launch_config(&cfg, attr, sms & ~1, epi, nullptr);
+  int clusters = 0;
+  const void* fn = epi == 0 ? gp_kernel<0>() : epi == 1 ? gp_kernel<1>() : gp_kernel<2>();
+  if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 && clusters < n) n = clusters;
+  cudaGetLastError();
+  pairs[epi] = n > 0 ? n : 1;
+  return pairs[epi];
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+// 0 when no kernel has given up on a wait since the last call; else 1 (producer), 2 (MMA), 3 (epilogue).
+extern "C" int exl3_gemm_pair_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gp_error, sizeof(int));
+  if (v) { int z = 0; cudaMemcpyToSymbol(g_gp_error, &z, sizeof(int)); }
+  return v;
+}
+
+extern "C" int exl3_gemm_pair(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                              int epilogue, const float* ss_in, int ss_blocks, float eps, float width, float* h,
+                              float rho, const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out,
+                              cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < 0 || N < 0 || K < 8 || K % 8 != 0 || N % 8 != 0 || epilogue < 0 || epilogue > 2 || (epilogue == 1 && N % 16 != 0)) {
+    set_error("gemm_pair: needs K and N multiples of 8 (N of 16 with the gated epilogue) and epilogue 0, 1 or 2, got M=%d N=%d K=%d epilogue %d",
+              M, N, K, epilogue);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (!aligned16(x) || !aligned16(w) || (epilogue != 2 && !aligned16(y))) { set_error("gemm_pair: x, w and y must be 16-byte aligned"); return ERR_ALIGNMENT; }
+  if (ss_in && (ss_blocks < 1 || !(width > 0.0f))) { set_error("gemm_pair: the norm's pieces need blocks >= 1 and a width"); return ERR_BAD_ARGUMENT; }
+  if (epilogue == 2) {
+    if (!h || !norm_w || !x_raw || !ss_out || !aligned16(h) || !aligned16(x_raw) ||
+        (norm_w_dtype != DT_F32 && norm_w_dtype != DT_BF16) || !(rho != 0.0f)) {
+      set_error("gemm_pair: the residual epilogue needs h, norm_w (float32 or bfloat16), x_raw and ss_out, 16-byte aligned, and a scale that is not zero");
+      return ERR_BAD_ARGUMENT;
+    }
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(0));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(1));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(2));
+    if (e != cudaSuccess) { set_error("gemm_pair: cannot get %u bytes of shared memory: %s", gp_smem(2), cudaGetErrorString(e)); return (int)e; }
+    configured = true;
+  }
+  CUtensorMap map_x, map_w, map_y, map_h;
+  int rc = make_map_k64(&map_x, x, M, K, 128, "gemm_pair");
+  if (rc) return rc;
+  rc = make_map_k64(&map_w, w, N, K, 128, "gemm_pair");
+  if (rc) return rc;
+  rc = make_map_128b(&map_y, epilogue == 2 ? x_raw : y, M, epilogue == 1 ? N / 2 : N, 2, 32, "gemm_pair");
+  if (rc) return rc;
+  if (epilogue == 2) {
+    rc = make_map_128b(&map_h, h, M, N, 4, 32, "gemm_pair");
+    if (rc) return rc;
+  } else {
+    map_h = map_y;
+  }
+  PairArgs a = {};
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.M = M; a.N = N; a.K = K;
+  a.ss_in = ss_in; a.ss_blocks = ss_blocks; a.eps = eps; a.width = width;
+  a.rho = rho; a.norm_w = norm_w; a.norm_w_f32 = norm_w_dtype == DT_F32 ? 1 : 0;
+  a.ss_out = ss_out;
+  const int tiles = ceil_div(M, GP_BM) * ceil_div(N, GP_BN);
+  const int max_pairs = gp_max_pairs(epilogue);
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  gp_launch_config(&cfg, attr, 2 * pairs, epilogue, stream);
+  cudaError_t e;
+  if (epilogue == 0) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<0>, map_x, map_w, map_y, map_h, a);
+  else if (epilogue == 1) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<1>, map_x, map_w, map_y, map_h, a);
+  else e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<2>, map_x, map_w, map_y, map_h, a);
+  if (e != cudaSuccess) { set_error("gemm_pair: launch failed: %s", cudaGetErrorString(e)); return (int)e; }
+  return launch_status("gemm_pair");
+}
+
+// Tiles of 256 columns per row in ss_out of the residual epilogue.
+extern "C" int exl3_gemm_pair_ss_blocks(int N) { return ceil_div(N, GP_BN); }

@@ -316,6 +316,59 @@ def gemm_skinny_split(N: int, K: int) -> int:
     return int(library().exl3_gemm_skinny_split(_c_int(N), _c_int(K)))
 
 
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], gated: bool = False, scale=None,
+              resid=None, out: Optional[torch.Tensor] = None):
+    """``x @ w.T (+ bias)`` in bfloat16 for many rows of x, two blocks of a cluster as one tensor core
+    (tcgen05.mma.cta_group::2, tiles of 256 x 256; see gemm_pair.cu).  ``gated``, ``scale`` and ``resid`` as in
+    ``gemm_skinny``; with ``resid`` the sums of squares come back as ``[M, tiles of 256 columns]``."""
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelLibraryError(f"gemm_pair: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemm_pair: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
+    if scale is not None:
+        ss_in, eps, width = scale
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] < M:
+            raise KernelLibraryError("gemm_pair: ss must be float32 [rows >= M, blocks]")
+        _contig(ss_in, "ss")
+        ss_blocks = ss_in.shape[1]
+    lib = library()
+    if resid is not None:
+        if gated:
+            raise KernelLibraryError("gemm_pair: the gated epilogue does not write into the residual")
+        h, rho, norm_w = resid
+        if h.dtype != torch.float32 or tuple(h.shape) != (M, N) or tuple(norm_w.shape) != (N,):
+            raise KernelLibraryError(f"gemm_pair: h {tuple(h.shape)} / norm weight {tuple(norm_w.shape)} "
+                                     f"do not fit an output of {(M, N)}")
+        _contig(h, "h")
+        _contig(norm_w, "norm_w")
+        x_raw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        ss_out = torch.empty((M, int(lib.exl3_gemm_pair_ss_blocks(_c_int(N)))), dtype=torch.float32, device=x.device)
+        _check(lib.exl3_gemm_pair(
+            _ptr(x), _ptr(w), _ptr(bias), _ptr(None), _c_int(M), _c_int(N), _c_int(K), _c_int(2), _ptr(ss_in),
+            _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(h), _c_float(rho), _ptr(norm_w),
+            _c_int(dtype_code(norm_w.dtype)), _ptr(x_raw), _ptr(ss_out), _stream()), "gemm_pair")
+        return x_raw, ss_out
+    if out is None:
+        out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=x.device)
+    elif tuple(out.shape) != (M, N // 2 if gated else N) or not out.is_contiguous() or out.dtype != torch.bfloat16:
+        raise KernelLibraryError(f"gemm_pair: out must be contiguous bfloat16 {(M, N // 2 if gated else N)}")
+    _check(lib.exl3_gemm_pair(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(1 if gated else 0),
+        _ptr(ss_in), _c_int(ss_blocks), _c_float(eps), _c_float(width), _ptr(None), _c_float(0.0), _ptr(None),
+        _c_int(DT_BF16), _ptr(None), _ptr(None), _stream()), "gemm_pair")
+    return out
+
+
+def gemm_pair_status() -> int:
+    """0, or the code a paired tensor-core GEMM left when a bounded wait ran out (cleared by this call)."""
+    return int(library().exl3_gemm_pair_status())
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
             gated: bool = False) -> torch.Tensor:
     """``x @ w.T (+ bias)`` in bfloat16 on the tcgen05 tensor cores; with ``gated``
@@ -461,6 +514,7 @@ def check_status() -> None:
     on one since the last call: its results are then not to be trusted.  Reads four flags from the device, so
     it waits for the work launched so far; call it where the host waits anyway."""
     gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("gemm_skinny", gemm_skinny_status),
+                                     ("gemm_pair", gemm_pair_status),
                                      ("attn_prefill_tc", attn_prefill_tc_status),
                                      ("attn_decode", attn_decode_status)) if fn()]
     if gave_up:
