@@ -5,7 +5,7 @@
 //
 // A pair of blocks (a cluster of two, on two neighbouring SMs) works on one tile of 256 x 256 outputs with
 // tcgen05.mma.cta_group::2 (M 256, N 256, K 16): each block copies its 128 rows of x and its 128 rows of w into its
-// own shared memory (16 KB + 16 KB per 64 of K, a ring of five or six stages), the pair's even block issues the
+// own shared memory (16 KB + 16 KB per 64 of K, a ring of five stages), the pair's even block issues the
 // instructions, which read both blocks' shared memory, and each block finds its 128 rows of the accumulator in its
 // own tensor memory.  Per flop a block copies and reads two thirds of what a block that works alone on 128 x 256
 // does; that is what lets the tensor pipe run without waiting for shared memory.
@@ -14,9 +14,10 @@
 //             mbarrier; no multicast, every block copies what it needs itself
 //   warp 1    even block: one thread issues the MMAs; tcgen05.commit frees ring stages in both blocks and hands
 //             accumulators to both blocks' epilogues.  Both blocks: allocates and frees the tensor memory
-//   warps 2-5 epilogue (both blocks): thread = row; 64 accumulator columns at a time from tensor memory, results
-//             into 128B-swizzled staging tiles of 32 rows x 128 bytes, which TMA stores write out (clipped at the
-//             matrix's edges), so that no thread stores a row-strided sliver itself
+//   warps 2-  epilogue (both blocks; eight warps, four with the residual epilogue): thread = row; 64 accumulator
+//             columns at a time from tensor memory, results into 128B-swizzled staging tiles of 32 rows x 128
+//             bytes, which TMA stores write out (clipped at the matrix's edges), so that no thread stores a
+//             row-strided sliver itself
 // Two accumulators (2 x 256 of the 512 columns) let the epilogue of one tile overlap the products of the next.
 // Pairs are persistent; tiles go round-robin over them, M fastest, so that pairs that run together share w in L2.
 //
@@ -43,24 +44,26 @@ namespace exl3 {
 using namespace tc5;
 
 constexpr int GP_BM = 256, GP_BN = 256, GP_BK = 64;
-constexpr int GP_THREADS = 192;
+// Epilogue warps: four (one per 32 lanes of tensor memory), or eight, two per 32 lanes with half of the columns each.
+__host__ __device__ constexpr int gp_epi_warps(int epi) { return epi == 2 ? 4 : 8; }
+__host__ __device__ constexpr int gp_threads(int epi) { return 64 + 32 * gp_epi_warps(epi); }
 constexpr uint32_t GP_STAGE_A = 128 * GP_BK * 2, GP_STAGE_B = 128 * GP_BK * 2;       // per block
 constexpr uint32_t GP_BOX = 32 * 128;                                                  // a staging tile: 32 rows x 128 bytes
-__host__ __device__ constexpr int gp_stages(int epi) { return epi == 2 ? 5 : 6; }
+__host__ __device__ constexpr int gp_stages(int) { return 5; }
 __host__ __device__ constexpr int gp_boxes(int epi) { return epi == 2 ? 4 : 2; }       // staging tiles per epilogue warp
 __host__ __device__ constexpr uint32_t gp_smem(int epi) {
-  return 1024 /* alignment */ + gp_stages(epi) * (GP_STAGE_A + GP_STAGE_B) + 4 * gp_boxes(epi) * GP_BOX +
+  return 1024 /* alignment */ + gp_stages(epi) * (GP_STAGE_A + GP_STAGE_B) + gp_epi_warps(epi) * gp_boxes(epi) * GP_BOX +
          GP_BN * 4 /* norm weights */ + GP_BN * 2 /* bias */ + 256 /* barriers */;
 }
 constexpr uint32_t GP_IDESC = idesc_bf16(GP_BM, GP_BN);
 
 static __device__ int g_gp_error = 0;
 
-// Barrier 1 over the 128 epilogue threads, returning whether the predicate held for all of them.
-__device__ inline bool gp_epilogue_all(bool pred) {
+// Barrier 1 over the THREADS epilogue threads, returning whether the predicate held for all of them.
+template <int THREADS> __device__ inline bool gp_epilogue_all(bool pred) {
   int r;
-  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.s32 %0, 1, 0, q;\n\t}"
-               : "=r"(r) : "r"((int)pred) : "memory");
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %1, 0;\n\tbar.red.and.pred q, 1, %2, p;\n\tselp.s32 %0, 1, 0, q;\n\t}"
+               : "=r"(r) : "r"((int)pred), "n"(THREADS) : "memory");
   return r != 0;
 }
 __device__ inline void gp_tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -95,18 +98,18 @@ struct PairArgs {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(GP_THREADS, 1)
+__global__ void __launch_bounds__(gp_threads(EPI), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y,      // y (0, 1) or x_raw (2): bfloat16, boxes of 64 columns
                  const __grid_constant__ CUtensorMap map_h,      // 2: the float32 residual, boxes of 32 columns
                  const PairArgs a) {
-  constexpr int STAGES = gp_stages(EPI), BOXES = gp_boxes(EPI);
+  constexpr int STAGES = gp_stages(EPI), BOXES = gp_boxes(EPI), EPI_WARPS = gp_epi_warps(EPI), EPI_THREADS = 32 * EPI_WARPS;
   extern __shared__ unsigned char gp_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gp_smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = base;
   unsigned char* sB = base + STAGES * GP_STAGE_A;
-  unsigned char* boxes = base + STAGES * (GP_STAGE_A + GP_STAGE_B);       // [4 warps][BOXES] staging tiles
-  float* s_normw = reinterpret_cast<float*>(boxes + 4 * BOXES * GP_BOX);
+  unsigned char* boxes = base + STAGES * (GP_STAGE_A + GP_STAGE_B);       // [EPI_WARPS][BOXES] staging tiles
+  float* s_normw = reinterpret_cast<float*>(boxes + EPI_WARPS * BOXES * GP_BOX);
   __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(s_normw + GP_BN);
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_bias + GP_BN);
   uint64_t* full = bars;                       // [STAGES] even block only: both blocks' copies landed
@@ -125,7 +128,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     prefetch_map(&map_y);
     if (EPI == 2) prefetch_map(&map_h);
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 8); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 2 * EPI_WARPS); }
     for (int i = 0; i < 16; ++i) mbar_init(hbar + i, 1);
     mbar_init_fence();
   }
@@ -134,6 +137,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   cluster_sync_all();                          // both blocks' barriers exist before either signals the other's
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything so far touched nothing that another kernel writes; from here on x, h and the norm's pieces are read
+  // and results written.  The next kernel in the stream may be set up meanwhile.
+  pdl_trigger();
+  pdl_wait();
 
   const int n_m = (a.M + GP_BM - 1) / GP_BM, n_n = (a.N + GP_BN - 1) / GP_BN;
   const int n_tiles = n_m * n_n, kblocks = (a.K + GP_BK - 1) / GP_BK;
@@ -201,8 +208,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   } else {
     // ---- epilogue: thread = row of this block's 128 -----------------------------------------------------------
     const int q = warp & 3;                               // the 32 TMEM lanes this warp may read
-    const int t = q * 32 + lane;
-    unsigned char* my_boxes = boxes + q * BOXES * GP_BOX;
+    const int t = (warp - 2) * 32 + lane;
+    // with eight warps, warps 2-5 take the tile's columns 0-127 and warps 6-9 the columns 128-255
+    const int s_lo = EPI_WARPS == 8 ? ((warp - 2) >> 2) * 2 : 0, s_hi = s_lo + (EPI_WARPS == 8 ? 2 : 4);
+    unsigned char* my_boxes = boxes + (warp - 2) * BOXES * GP_BOX;
     uint64_t* my_hbar = hbar + q * 4;
     const uint32_t acc_empty_addr[2] = {cluster_addr(acc_empty, 0), cluster_addr(acc_empty + 1, 0)};
     const uint32_t lane_taddr = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -276,8 +285,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int row = row0 + lane;
       // the tile's bias and norm weights, once for all rows (the previous tile's readers are past their last read:
       // they have met at the barrier after it); every thread comes here, whatever its verdict so far
-      if (!gp_epilogue_all(ok)) { ok = false; break; }
-      for (int c = t; c < GP_BN; c += 128) {
+      if (!gp_epilogue_all<EPI_THREADS>(ok)) { ok = false; break; }
+      for (int c = t; c < GP_BN; c += EPI_THREADS) {
         const int n = n0 + c;
         s_bias[c] = (a.bias && n < a.N) ? a.bias[n] : __float2bfloat16(0.0f);
         if (EPI == 2)
@@ -286,14 +295,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       const float k_row = (EPI == 2 ? a.rho : 1.0f) * row_factor(row);
       const float k_bias = EPI == 2 ? a.rho : 1.0f;
-      // (also the barrier after which the staged bias and norm weights may be read) one verdict for all 128
+      // (also the barrier after which the staged bias and norm weights may be read) one verdict for all epilogue
       // threads, so that they leave the loop together
-      if (!gp_epilogue_all(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
+      if (!gp_epilogue_all<EPI_THREADS>(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
       fence_after();
       const uint32_t taddr = lane_taddr + buf * GP_BN;
       float sq = 0.0f;
 #pragma unroll 1
-      for (int s = 0; s < GP_BN / 64; ++s) {                // 64 accumulator columns at a time
+      for (int s = s_lo; s < s_hi; ++s) {                   // 64 accumulator columns at a time
         uint32_t r0[32], r1[32];
         __syncwarp();
         tmem_ld32_issue(taddr + s * 64, r0);
@@ -395,7 +404,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (lane == 0) mbar_arrive_cluster(acc_empty_addr[buf]);
       }
     }
-    if (lane == 0) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_read<0>();               // the staging tiles have been read; the kernel's end covers the rest
     if (!ok && lane == 0) atomicExch(&g_gp_error, 3);
   }
 
@@ -407,18 +416,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
 template <int EPI> static const void* gp_kernel() { return reinterpret_cast<const void*>(&gemm_pair_kernel<EPI>); }
 
+// attr: room for two attributes.
 static void gp_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int blocks, int epi, cudaStream_t stream) {
   *cfg = cudaLaunchConfig_t{};
   cfg->gridDim = dim3(blocks);
-  cfg->blockDim = dim3(GP_THREADS);
+  cfg->blockDim = dim3(gp_threads(epi));
   cfg->dynamicSmemBytes = gp_smem(epi);
   cfg->stream = stream;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg->attrs = attr;
-  cfg->numAttrs = 1;
+  cfg->numAttrs = pdl_enabled() ? 2 : 1;
 }
 
 // Pairs that the GPU runs at once (a pair needs two SMs of one cluster-capable group).
@@ -430,8 +442,9 @@ static int gp_max_pairs(int epi) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int n = sms / 2;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   gp_launch_config(&cfg, attr, sms & ~1, epi, nullptr);
+  cfg.numAttrs = 1;
   int clusters = 0;
   const void* fn = epi == 0 ? gp_kernel<0>() : epi == 1 ? gp_kernel<1>() : gp_kernel<2>();
   if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 && clusters < n) n = clusters;
@@ -502,7 +515,7 @@ extern "C" int exl3_gemm_pair(const void* x, const void* w, const void* bias, vo
   const int max_pairs = gp_max_pairs(epilogue);
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   gp_launch_config(&cfg, attr, 2 * pairs, epilogue, stream);
   cudaError_t e;
   if (epilogue == 0) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<0>, map_x, map_w, map_y, map_h, a);

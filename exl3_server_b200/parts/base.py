@@ -99,10 +99,14 @@ class RawNormed:
     def shape(self):
         return self.x_raw.shape
 
-    def materialize(self, out_scale: float = 1.0) -> torch.Tensor:
-        rows = self.x_raw.shape[0]
-        inv = torch.rsqrt(self.ss[:rows].sum(dim=1) / float(self.width) + self.eps)
-        return (self.x_raw.float() * (inv * out_scale)[:, None]).to(self.x_raw.dtype)
+    def materialize(self, out_scale: float = 1.0, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The norm's output, of all rows or of the rows listed (a prompt's last position, say)."""
+        n = self.x_raw.shape[0]
+        x_raw, ss = self.x_raw, self.ss[:n]
+        if rows is not None:
+            x_raw, ss = x_raw.index_select(0, rows.long()), ss.index_select(0, rows.long())
+        inv = torch.rsqrt(ss.sum(dim=1) / float(self.width) + self.eps)
+        return (x_raw.float() * (inv * out_scale)[:, None]).to(x_raw.dtype)
 
 
 class NormAfter:

@@ -2,18 +2,20 @@
 ``(out, in)`` order (the reference transposes to ``(in, out)`` at load,
 src/model.cpp:214-228; the kernels here read rows of W, so no transpose).
 
-Which kernel runs depends only on the element type and the row count:
+Which kernel runs depends only on the element type and the sizes:
 float32 goes through the CUDA-core kernel with a fixed order of summation
 (the true 32-bit path).  bfloat16 with at most 16 rows streams the weights once
 through the tensor-core GEMV (``mma.sync``, weights as the 16-row operand); with
 17 to ``SKINNY_ROWS`` rows through the skinny tcgen05 GEMM (weights as the
-128-row operand, streamed once by TMA).  Both take a norm's output in two pieces
-and can fold their output into the residual (see ``RawNormed``, ``NormAfter``), so
-a decode step of up to ``SKINNY_ROWS`` sequences has no kernel between its
-projections.  Larger plain bfloat16 products (prompts) are the library's
-(cuBLAS through ``torch``), as the reference's are MLX's (src/model.cpp:549).
-The gated feed-forward projection, whose epilogue is fused, never goes to the
-library: above ``SKINNY_ROWS`` rows it runs on this library's own tcgen05 GEMM.
+128-row operand, streamed once by TMA); with more rows (prompts) through the
+paired tcgen05 GEMM (two blocks of a cluster on tiles of 256 x 256), when its
+tiles fill the GPU (``PAIR_MIN_EFFICIENCY``).  All three take a norm's output in
+two pieces and can fold their output into the residual (see ``RawNormed``,
+``NormAfter``), so a step has no kernel between its projections but attention and
+position encoding.  Products in between (some hundred rows, or a narrow output)
+are the library's (cuBLAS through ``torch``), as the reference's are MLX's
+(src/model.cpp:549); the gated feed-forward projection, whose epilogue is fused,
+never goes to the library.
 """
 from __future__ import annotations
 
@@ -36,6 +38,9 @@ SKINNY_ROWS = 64
 # 3.31 ms).
 SKINNY_MIN_BYTES = int(os.environ.get("EXL3_SKINNY_MIN_BYTES", 48 << 20))
 SKINNY_MIN_BYTES_FEW_ROWS = int(os.environ.get("EXL3_SKINNY_MIN_BYTES_FEW", 100 << 20))     # fewer than 8 rows
+# Above SKINNY_ROWS rows: the least share of the GPU's pairs of SMs that the paired GEMM's tiles must keep busy for
+# it to run instead of the library's product (one prompt of 2,048 tokens at the 2B sizes: 0.97 for every projection).
+PAIR_MIN_EFFICIENCY = float(os.environ.get("EXL3_PAIR_MIN_EFFICIENCY", 0.7))
 
 
 class Linear:
@@ -48,8 +53,8 @@ class Linear:
         self.dtype = dtype
 
     def _streaming_kernel(self, rows: int):
-        """The kernel that reads the weights once for ``rows`` rows and takes the norm's pieces: the GEMV, the
-        skinny GEMM, or None (float32, sizes they refuse, too many rows)."""
+        """The kernel of this library that takes ``rows`` rows and the norm's pieces: the GEMV, the skinny GEMM, the
+        paired GEMM, or None (float32, sizes they refuse, or too few tiles for the paired one)."""
         if self.dtype != torch.bfloat16 or self.in_features % 8 != 0:
             return None
         if rows <= K.GEMV_MAX_ROWS and self.weight.numel() * 2 < (SKINNY_MIN_BYTES if rows >= 8
@@ -57,18 +62,23 @@ class Linear:
             return K.gemv_bf16_normed
         if rows <= SKINNY_ROWS:
             return K.gemm_skinny
+        if self.out_features % 8 == 0 and \
+                K.gemm_pair_efficiency(rows, self.out_features, self.weight.device) >= PAIR_MIN_EFFICIENCY:
+            return K.gemm_pair
         return None
 
     def __call__(self, x, out_dtype: Optional[torch.dtype] = None, then=None) -> Optional[torch.Tensor]:
         """``x``: a tensor, or a ``RawNormed`` (a norm's output in two pieces: the weight-streaming kernels apply
         the missing factor per row to their results; other paths materialise it first).
-        ``then``: a ``NormAfter`` offer; taken when a weight-streaming kernel runs (bfloat16, at most
-        ``SKINNY_ROWS`` rows) and the output is as wide as the residual: its blocks add the output to the residual
-        and leave the pieces of the next norm's output.  Returns None then."""
+        ``then``: a ``NormAfter`` offer; taken when one of this library's bfloat16 kernels runs and the output is
+        as wide as the residual: its blocks add the output to the residual and leave the pieces of the next norm's
+        output.  Returns None then."""
         out_dtype = out_dtype or self.dtype
         M = x.shape[0]
         fast = self.in_features % 8 == 0
         kernel = self._streaming_kernel(M)
+        if kernel is K.gemm_pair and out_dtype != torch.bfloat16:
+            kernel = None                       # float32 results for many rows: below
         scale = None
         if isinstance(x, RawNormed):
             if kernel is not None:
@@ -113,8 +123,8 @@ class Linear:
         """For a weight whose rows are eight gate rows, then the eight up rows
         of the same features, and so on: ``silu(gate) * up`` in the projection's
         own epilogue, so the gate/up product never goes to memory.  Up to 16 rows:
-        the weight-streaming GEMV; up to ``SKINNY_ROWS``: the skinny tcgen05 GEMM; more: the tcgen05 GEMM for
-        prompts."""
+        the weight-streaming GEMV; up to ``SKINNY_ROWS``: the skinny tcgen05 GEMM; more: the paired tcgen05 GEMM,
+        or the one-block tcgen05 GEMM when the paired one's tiles would leave the GPU half empty."""
         kernel = self._streaming_kernel(x.shape[0])
         if isinstance(x, RawNormed):
             if kernel is not None:

@@ -40,8 +40,7 @@ class RMSNorm:
         if left is not None:
             if rows is None and raw_ok and out_scale == 1.0:
                 return left
-            r = left.materialize(out_scale)
-            return r if rows is None else r.index_select(0, rows.long())
+            return left.materialize(out_scale, rows)
         y, s = stream.take()
         return K.add_rmsnorm(stream.h, y, s, self.weight, self.spec.eps, self.out_dtype,
                              out_scale=out_scale, rows=rows)

@@ -311,6 +311,111 @@ def test_gemm_skinny_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, nor
     assert K().gemm_skinny_status() == 0
 
 
+# Sizes for the paired GEMM: one tile; ragged in M, N and K; one row more than a pair's even block holds; fewer
+# columns than a staging tile; more tiles than the GPU has pairs (several per pair, both accumulators in turn).
+PAIR_SIZES = [(256, 256, 64), (300, 520, 264), (129, 16, 8), (65, 4608, 128), (1000, 1000, 1000), (2048, 2304, 2304),
+              (5000, 2304, 72)]
+
+
+@pytest.mark.parametrize("M,N,Kd", PAIR_SIZES)
+def test_gemm_pair(M, N, Kd):
+    """Two blocks of a cluster as one tensor core (tcgen05.mma.cta_group::2): plain, with a bias, with a norm's row
+    factors, and a row's result independent of the other rows."""
+    torch.manual_seed(14)
+    x = (torch.randn(M, Kd, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    want = x.double() @ w.double().T
+    got = K().gemm_pair(x, w, None)
+    close(got, want, TOL[torch.bfloat16], "pair")
+    close(K().gemm_pair(x, w, b), want + b.double(), TOL[torch.bfloat16], "pair + bias")
+    width, eps = 77.0, 1e-5
+    ss = torch.rand(M + 3, 5, device=DEV) * 40 + 1
+    k = torch.rsqrt(ss[:M].sum(1) / width + eps).double()
+    close(K().gemm_pair(x, w, b, scale=(ss, eps, width)), want * k[:, None] + b.double(), TOL[torch.bfloat16],
+          "pair with row factors")
+    # the last rows alone: other tiles, another place in their tile, the same numbers
+    tail = K().gemm_pair(x[M - 40:].contiguous(), w, None)
+    assert torch.equal(tail, got[M - 40:])
+    torch.cuda.synchronize()
+    assert K().gemm_pair_status() == 0
+
+
+@pytest.mark.parametrize("M,I,Kd", [(256, 128, 64), (300, 264, 264), (129, 8, 8), (2048, 5760, 2304), (700, 1000, 520)])
+def test_gemm_pair_gated(M, I, Kd):
+    torch.manual_seed(15)
+    x = (torch.randn(M, Kd, device=DEV) * 0.5).bfloat16()
+    wg = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    wu = (torch.randn(I, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    bg, bu = torch.randn(I, device=DEV).bfloat16(), torch.randn(I, device=DEV).bfloat16()
+    n = I // 8
+    w = torch.stack([wg.view(n, 8, Kd), wu.view(n, 8, Kd)], dim=1).reshape(2 * I, Kd).contiguous()
+    b = torch.stack([bg.view(n, 8), bu.view(n, 8)], dim=1).reshape(-1).contiguous()
+    g = x.double() @ wg.double().T + bg.double()
+    u = x.double() @ wu.double().T + bu.double()
+    close(K().gemm_pair(x, w, b, gated=True), g * torch.sigmoid(g) * u, TOL[torch.bfloat16], "gated pair")
+    # against the one-block kernel with the same epilogue
+    close(K().gemm_pair(x, w, b, gated=True), K().gemm_tc(x, w, b, gated=True).double(), TOL[torch.bfloat16], "pair and one block")
+    torch.cuda.synchronize()
+    assert K().gemm_pair_status() == 0
+
+
+@pytest.mark.parametrize("M,N,Kd", PAIR_SIZES)
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_pair_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_dtype):
+    """The residual goes into the accumulator before the products and comes out with them added: h in place,
+    h times the norm's weight, and the row sums of h squared per tile of 256 columns; then both pieces into the
+    next projection.  With 5,000 rows a pair has several tiles and brings the residual of a later tile in while
+    the tensor core works on an earlier one."""
+    g = torch.Generator().manual_seed(M + N)
+    x = (torch.randn(M, Kd, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    nw = (1.0 + 0.2 * torch.randn(N, generator=g)).to(norm_dtype).to(DEV)
+    h0 = (torch.randn(M, N, generator=g) * 3).to(DEV)
+    rho, eps = 0.37, 1e-5
+    width = 77.0
+    ss_in = (torch.rand(M, 3, generator=g) * 40 + 1).to(DEV)
+    k = torch.rsqrt(ss_in.sum(1) / width + eps).double()
+    for bias, scale in ((None, None), (b, None), (b, (ss_in, eps, width))):
+        h = h0.clone()
+        x_raw, ss = K().gemm_pair(x, w, bias, scale=scale, resid=(h, rho, nw))
+        y = x.double() @ w.double().T * (1.0 if scale is None else k[:, None]) + (0 if bias is None else bias.double())
+        want_h = h0.double() + y * rho
+        # the products are added to h inside the tensor core: 1e-5 of the largest h (fewer guard bits than a chain
+        # of float32 FMAs), against the 2e-3 that rounding the product to bfloat16 first would cost
+        close(h, want_h, 2e-5, "residual")
+        close(x_raw, want_h * nw.double(), 6e-3, "residual times the norm weight")
+        assert ss.shape == (M, (N + 255) // 256)
+        close(ss.sum(1), (want_h * want_h).sum(1), 2e-5, "sums of squares")
+    # the pieces feed the next projection as the norm's output would
+    if N % 8 == 0:
+        N2 = 176
+        w2 = (torch.randn(N2, N, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        r = (h.double() * torch.rsqrt((h.double() ** 2).mean(1, keepdim=True) + eps) * nw.double())
+        got = K().gemm_pair(x_raw, w2, None, scale=(ss, eps, float(N)))
+        close(got, r @ w2.double().T, 1e-2, "second projection")
+    torch.cuda.synchronize()
+    assert K().gemm_pair_status() == 0
+
+
+def test_gemm_pair_refuses_what_it_cannot_do():
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    x = torch.zeros(300, 64, device=DEV).bfloat16()
+    w = torch.zeros(24, 64, device=DEV).bfloat16()
+    with pytest.raises(KernelLibraryError, match="multiples of 8"):
+        K().gemm_pair(x[:, :60].contiguous(), w[:, :60].contiguous(), None)
+    with pytest.raises(KernelLibraryError, match="multiples of 8"):
+        K().gemm_pair(x, w[:20].contiguous(), None)
+    with pytest.raises(KernelLibraryError, match="N of 16 with the gated"):
+        K().gemm_pair(x, w, None, gated=True)
+    with pytest.raises(KernelLibraryError, match="output is bfloat16"):
+        K().gemm_pair(x, w, None, torch.float32)
+    h = torch.zeros(300, 24, device=DEV)
+    with pytest.raises(KernelLibraryError, match="scale that is not zero"):
+        K().gemm_pair(x, w, None, resid=(h, 0.0, torch.ones(24, device=DEV)))
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(129, 64, device=DEV).bfloat16()
