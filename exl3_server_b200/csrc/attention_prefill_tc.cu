@@ -200,6 +200,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   fa_fence_before();
   __syncthreads();
   fa_fence_after();
+  // so far nothing was touched that another kernel writes; the next kernel in the stream may be set up meanwhile
+  pdl_trigger();
+  pdl_wait();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;                  // columns: S0 0..63, S1 64..127, O from 128
   const uint32_t tmem_p = tmem_base + 128 + FA_HD;          // P0, then P1: 32 columns each (two bfloat16 per column)
@@ -474,6 +477,9 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   fa_fence_before();
   __syncthreads();
   fa_fence_after();
+  // so far nothing was touched that another kernel writes; the next kernel in the stream may be set up meanwhile
+  pdl_trigger();
+  pdl_wait();
   const uint32_t tmem_base = *tmem_slot;                    // columns: S 0..63 (P over 0..31), O 64..127
   const uint32_t tmem_o = tmem_base + 64;
   bool ok = true;
@@ -731,17 +737,16 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   dim3 grid(nh, n_tiles);
   // four blocks an SM when there are more blocks than that holds at once
   const bool four = hd == 64 && (variant == 2 || (variant == 0 && (int64_t)n_tiles * nh > 4 * (int64_t)sms));
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  const float scale_log2 = scale * 1.4426950408889634f;
   if (four)
-    attn_prefill_tc4_kernel<<<grid, FA_THREADS, F4_SMEM, stream>>>(
-        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
-        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+    launch_pdl(attn_prefill_tc4_kernel, grid, dim3(FA_THREADS), F4_SMEM, stream, map_q, map_k, map_v, o, block_table,
+               bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
   else if (hd == 64)
-    attn_prefill_tc_kernel<64><<<grid, FA_THREADS, fa_smem(64), stream>>>(
-        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
-        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+    launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(FA_THREADS), fa_smem(64), stream, map_q, map_k, map_v, o,
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
   else
-    attn_prefill_tc_kernel<128><<<grid, FA_THREADS, fa_smem(128), stream>>>(
-        map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), block_table, bt_stride, row_start, row_pos0, tile_seq,
-        tile_q0, nh, nkv, window, scale * 1.4426950408889634f);
+    launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(FA_THREADS), fa_smem(128), stream, map_q, map_k, map_v, o,
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
   return launch_status("attn_prefill_tc");
 }

@@ -144,6 +144,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
   const int n_m = (a.M + GP_BM - 1) / GP_BM, n_n = (a.N + GP_BN - 1) / GP_BN;
   const int n_tiles = n_m * n_n, kblocks = (a.K + GP_BK - 1) / GP_BK;
+  // 2, when no pair has a second tile: the second accumulator is free, so the residual goes there while the products
+  // start from zero in the first at once, and the epilogue adds the two.  (With several tiles per pair both
+  // accumulators are in use in turn, and the residual goes into the accumulator before the tile's products.)
+  const bool beside = EPI == 2 && n_tiles <= n_pairs;
   bool ok = true;
 
   if (warp == 0) {
@@ -182,7 +186,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t buf = tcount & 1;
         // 0, 1: an accumulator is free from the start and after each epilogue; 2: it is ready when the epilogue
         // warps have put the tile's residual into it
-        if (!mbar_wait(acc_empty + buf, ((tcount >> 1) & 1) ^ (EPI == 2 ? 0u : 1u))) { ok = false; break; }
+        if (!beside && !mbar_wait(acc_empty + buf, ((tcount >> 1) & 1) ^ (EPI == 2 ? 0u : 1u))) { ok = false; break; }
         fence_after();
         const uint32_t d_tmem = tmem_base + buf * GP_BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -194,7 +198,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const uint64_t db = smem_desc_k128(smem_u32(sB + s * GP_STAGE_B));
 #pragma unroll
             for (int k = 0; k < GP_BK / 16; ++k)
-              mma_ss_pair(d_tmem, da + 2 * k, db + 2 * k, GP_IDESC, (EPI == 2 || kb > 0 || k > 0) ? 1u : 0u);
+              mma_ss_pair(d_tmem, da + 2 * k, db + 2 * k, GP_IDESC, ((EPI == 2 && !beside) || kb > 0 || k > 0) ? 1u : 0u);
             mma_commit_pair(empty + s);
           }
           __syncwarp();
@@ -228,11 +232,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       return k;
     };
-    // 2: this warp's 32 rows of a tile of h, divided by rho * k, into accumulator `buf`; then the accumulator is
-    // handed to the MMA issuer.  False when a wait ran out.
+    // 2: this warp's 32 rows of a tile of h into accumulator `buf`: divided by rho * k, and the accumulator is then
+    // handed to the MMA issuer; or as they are, beside the products.  False when a wait ran out.
     auto preload = [&](int tile, uint32_t buf) -> bool {
       const int row0 = (tile % n_m) * GP_BM + (int)rank * 128 + q * 32, n0 = (tile / n_m) * GP_BN;
-      const float inv = 1.0f / (a.rho * row_factor(row0 + lane));
+      const float inv = beside ? 1.0f : 1.0f / (a.rho * row_factor(row0 + lane));
       if (lane == 0) tma_store_wait_read<0>();            // the last epilogue's stores have read the staging tiles
       __syncwarp();
       if (lane == 0)
@@ -270,13 +274,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_addr[buf]);
+      if (lane == 0 && !beside) mbar_arrive_cluster(acc_empty_addr[buf]);
       return true;
     };
 
     if (EPI == 2) {
-      int tile = pair;
-      for (uint32_t b = 0; b < 2 && tile < n_tiles && ok; ++b, tile += n_pairs) ok = preload(tile, b);
+      if (beside) {
+        if (pair < n_tiles) ok = preload(pair, 1);
+      } else {
+        int tile = pair;
+        for (uint32_t b = 0; b < 2 && tile < n_tiles && ok; ++b, tile += n_pairs) ok = preload(tile, b);
+      }
     }
     uint32_t tcount = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tcount) {
@@ -295,6 +303,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       const float k_row = (EPI == 2 ? a.rho : 1.0f) * row_factor(row);
       const float k_bias = EPI == 2 ? a.rho : 1.0f;
+      const bool plain = a.bias == nullptr && a.ss_in == nullptr && EPI != 2;      // the accumulator as it is
       // (also the barrier after which the staged bias and norm weights may be read) one verdict for all epilogue
       // threads, so that they leave the loop together
       if (!gp_epilogue_all<EPI_THREADS>(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
@@ -315,10 +324,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tmem_ld_wait(r0);
         tmem_ld_wait(r1);
         float v[64];
+        if (plain) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = fmaf(__uint_as_float(r0[j]), k_row, k_bias * __bfloat162float(s_bias[s * 64 + j]));
-          v[32 + j] = fmaf(__uint_as_float(r1[j]), k_row, k_bias * __bfloat162float(s_bias[s * 64 + 32 + j]));
+          for (int j = 0; j < 32; ++j) { v[j] = __uint_as_float(r0[j]); v[32 + j] = __uint_as_float(r1[j]); }
+        } else if (a.bias == nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { v[j] = __uint_as_float(r0[j]) * k_row; v[32 + j] = __uint_as_float(r1[j]) * k_row; }
+        } else {
+#pragma unroll
+          for (int j8 = 0; j8 < 8; ++j8) {
+            const uint4 b8 = *reinterpret_cast<const uint4*>(s_bias + s * 64 + 8 * j8);      // eight bfloat16
+            const uint32_t bw[4] = {b8.x, b8.y, b8.z, b8.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = __uint_as_float(bw[e] << 16), hi = __uint_as_float(bw[e] & 0xffff0000u);
+              const int j = 8 * j8 + 2 * e;
+              v[j] = fmaf(__uint_as_float(j < 32 ? r0[j] : r1[j - 32]), k_row, k_bias * lo);
+              v[j + 1] = fmaf(__uint_as_float(j < 32 ? r0[j + 1] : r1[j - 31]), k_row, k_bias * hi);
+            }
+          }
+        }
+        if (EPI == 2 && beside) {
+          // the residual from the other accumulator
+          tmem_ld32_issue(lane_taddr + GP_BN + s * 64, r0);
+          tmem_ld32_issue(lane_taddr + GP_BN + s * 64 + 32, r1);
+          tmem_ld_wait(r0);
+          tmem_ld_wait(r1);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { v[j] += __uint_as_float(r0[j]); v[32 + j] += __uint_as_float(r1[j]); }
         }
         if (EPI == 0) {
           unsigned char* box = my_boxes + (n_store & 1) * GP_BOX;
@@ -404,12 +437,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (lane == 0) mbar_arrive_cluster(acc_empty_addr[buf]);
       }
     }
-    if (lane == 0) tma_store_wait_read<0>();               // the staging tiles have been read; the kernel's end covers the rest
     if (!ok && lane == 0) atomicExch(&g_gp_error, 3);
   }
 
   fence_before();
-  cluster_sync_all();                          // nobody reads the partner's shared or tensor memory after this
+  cluster_arrive_all();
+  // (meanwhile) the stores have read their staging tiles; the kernel's end covers the rest of their way
+  if (warp >= 2 && lane == 0) tma_store_wait_read<0>();
+  __syncwarp();
+  cluster_wait_all();                          // nobody reads the partner's shared or tensor memory after this
   fence_after();
   if (warp == 1) tmem_free_pair<512>(tmem_base);
 }
