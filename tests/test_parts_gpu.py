@@ -138,6 +138,50 @@ def test_feed_forward_part(dtype, inner, rows):
     assert rel_err(y.float().cpu().numpy(), want.numpy()) <= TOLS[dtype]
 
 
+@pytest.mark.parametrize("rows", [40, 300])
+def test_feed_forward_between_two_norms_that_are_no_kernels(rows, monkeypatch):
+    """The feed-forward takes the norm before it in two pieces and leaves the norm after it in two pieces, with its
+    output already in the residual: for a decode batch (40 rows: the skinny GEMM) and for a prompt (300 rows: the
+    paired GEMM, which a batch this small gets only because the test lowers its threshold)."""
+    from exl3_server_b200.parts import FeedForwardSpec, NormSpec, ResidualStream, feed_forward_class, norm_class
+    from exl3_server_b200.parts import linear as LIN
+    from exl3_server_b200.parts.base import NormAfter, RawNormed
+    monkeypatch.setattr(LIN, "PAIR_MIN_EFFICIENCY", 0.0)
+    torch.manual_seed(5)
+    dtype, H, inner, eps, rho = torch.bfloat16, 264, 176, 2e-6, 0.4
+    t = {"f.gate_proj.weight": (torch.randn(inner, H) / 16).to(dtype).to(DEV),
+         "f.up_proj.weight": (torch.randn(inner, H) / 16).to(dtype).to(DEV),
+         "f.down_proj.weight": (torch.randn(H, inner) / 13).to(dtype).to(DEV)}
+    part = feed_forward_class("swiglu")(FeedForwardSpec("swiglu", H, inner), t, "f.", ctx(dtype))
+    w1 = (1 + 0.2 * torch.randn(H)).to(dtype)
+    w2 = (1 + 0.2 * torch.randn(H)).to(dtype)
+    after = norm_class("rms")(NormSpec("rms", H, eps), {"n.weight": w2.to(DEV)}, "n.", ctx(dtype))
+    h0 = torch.randn(rows, H) * 2
+    # the norm before, as a projection would have left it: h times the weight, and sums of squares in three pieces
+    x_raw = (h0 * w1.float()).to(dtype).to(DEV)
+    sq = (h0.double() ** 2)
+    ss = torch.stack([sq[:, :100].sum(1), sq[:, 100:200].sum(1), sq[:, 200:].sum(1)], dim=1).float().to(DEV)
+    stream = ResidualStream(h0.clone().to(DEV))
+    then = NormAfter(stream, rho, after)
+    y = part.forward(RawNormed(x_raw, ss, eps, H), None, then=then)
+    assert y is None and then.done and stream.pending is None
+    w = {k: v.double().cpu() for k, v in t.items()}
+    r1 = P.rms_norm(h0.double(), w1.double(), eps)
+    want_h = h0.double() + rho * P.swiglu(r1, w["f.gate_proj.weight"], w["f.up_proj.weight"], w["f.down_proj.weight"])
+    assert rel_err(stream.h.cpu().numpy(), want_h.numpy()) < 3e-3
+    left = after.add_norm(stream, raw_ok=True)
+    assert isinstance(left, RawNormed)
+    want_r = P.rms_norm(want_h, w2.double(), eps)
+    assert rel_err(left.materialize().float().cpu().numpy(), want_r.numpy()) <= TOLS[dtype]
+    # one row of it, as the last norm of a prompt asks for
+    rows_wanted = torch.tensor([rows - 1], dtype=torch.int32, device=DEV)
+    stream.normed = (after, left)
+    one = after.add_norm(stream, rows=rows_wanted)
+    assert rel_err(one.float().cpu().numpy(), want_r[rows - 1:].numpy()) <= TOLS[dtype]
+    from exl3_server_b200.ops import kernels as K
+    K.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding_and_head(dtype):
     from exl3_server_b200.parts import EmbeddingSpec, HeadSpec, NormSpec, norm_class
