@@ -826,8 +826,8 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
                                 int write_new, int head_split, cudaStream_t stream) {
   if (T == 0) return 0;
-  if (head_split != 1 && (head_split != 2 || (nkv > 0 && (nh / nkv) % 2 != 0))) {
-    set_error("attn_decode: head_split is 1, or 2 for an even number of query heads per kv head; got %d", head_split);
+  if (head_split < 1 || head_split > AD_MAX_GROUP || nkv < 1 || nh % nkv != 0 || (nh / nkv) % head_split != 0) {
+    set_error("attn_decode: head_split must divide the %d query heads of a kv head; got %d", nkv > 0 ? nh / nkv : 0, head_split);
     return ERR_BAD_ARGUMENT;
   }
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||

@@ -499,8 +499,8 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     projection, every token is its sequence's only new one and the cache holds the positions before it: the
     kernel adds the token's own key and value to its softmax and writes them to the cache.  With ``rot`` equal to
     ``head_dim`` it applies the half-split rotary encoding (``inv_freq``: head_dim / 2 float32 frequencies, or a ``rotary_table``) to
-    the queries and the new key.  ``head_split`` 2 makes two groups of work of a kv head's query heads (an even
-    number of them): twice the work items, each merge half the size; changes no result."""
+    the queries and the new key.  ``head_split`` n (a divisor of the query heads per kv head) makes n groups of work
+    of a kv head's query heads: n times the work items, each merge an n-th of the size; changes no result."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")

@@ -164,16 +164,18 @@ class Attention:
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
         """``(keys per chunk, head_split)`` for the tensor-core decode kernel: chunks of whole pages (a power of two
-        of them, at most 64 of 16 KB), and whether the query heads of a kv head are worked on as one group or as two
-        (``head_split`` 2: twice the work items, each merge half the size).  By a small model of the kernel's time,
-        its constants fitted to sweeps at four head layouts (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128) and
-        batches of 1 to 64: a warp walks its chunk at about 0.9 us per 16 KB of keys and values (1.4 us with more
-        than 8 query heads in its group); when there are more chunks than warps a warp takes several in turn; all
-        warps together cannot read faster than the memory does; and the chunks of a (token, group of heads), when
-        there is more than one, are merged by a single warp: about 4 us for the records' trip through memory and
-        the ticket, plus 0.5 us per chunk, plus 0.01 us per chunk for every group that merges at the same time,
-        twice that for groups of more than 8 heads (two passes).  So few long chunks win for wide groups (16 query
-        heads of 128 on a kv head at 2,048 tokens: 32 chunks cost 59 us, 4 cost 20), one chunk wins for short
+        of them, at most 64 of 16 KB), and into how many groups of work the query heads of a kv head are cut
+        (``head_split``: that many times the work items, each merge that much smaller, the keys and values read
+        again from L2).  By a small model of the kernel's time, its constants fitted to sweeps at four head layouts
+        (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128) and batches of 1 to 64 (to 14 % in the mean): 4 us to start;
+        a warp walks its chunk at 0.8 us per 16 KB of keys and values plus 0.02 us for every query head in its group;
+        when there are more chunks than warps a warp takes several in turn; all warps together cannot read faster
+        than the memory does (6 TB/s for what is read once, 12 TB/s from L2 for what the groups of a kv head read
+        again); and the chunks of a (token, group of heads), when there is more than one, are merged by a single
+        warp: 3 us, plus per chunk 0.05 us and 0.06 us for every head of the group, 2 % more for every group that
+        merges at the same time.  So wide groups of heads in small batches are cut into many narrow ones with a fair
+        number of chunks each, as many pieces as there are warps (one token of 32 query heads of 128 on 2 kv heads
+        at 2,048 tokens: 16 groups of 16 chunks take 13 us, one group of 8 chunks 33 us), one chunk wins for short
         contexts and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks
         only where they are needed to give every SM work.  The choice depends on the step's size, not on a token's
         position: results differ between batch sizes by rounding."""
@@ -184,21 +186,24 @@ class Attention:
         group = s.heads // s.kv_heads
         warps = 4 * K.sm_count(device)
         best = None
-        for head_split in ((1, 2) if group >= 8 and group % 2 == 0 else (1,)):
+        for head_split in (1, 2, 4, 8, 16):
+            if group % head_split:
+                continue
             g = group // head_split
             if g > 16:
                 continue
-            stage_us = 1.4 if g > 8 else 0.9
+            stage_us = 0.8 + 0.02 * g
             groups = T * s.kv_heads * head_split
-            stream_us = groups * pages_seq * wide * 16384 / 6.0e6     # all pages at 6 TB/s
+            once_us = T * s.kv_heads * pages_seq * wide * 16384 / 6.0e6
+            again_us = groups * pages_seq * wide * 16384 / 12.0e6
             per = 1
             while True:
                 n = (pages_seq + per - 1) // per
                 if n + (1 if s.window > 0 else 0) <= K.ATTN_DECODE_MAX_CHUNKS:     # a window may straddle one chunk more
                     rounds = (groups * n + warps - 1) // warps
-                    cost = max(rounds * per * wide * stage_us, stream_us)
+                    cost = 4.0 + max(rounds * per * wide * stage_us, once_us, again_us)
                     if n > 1:
-                        cost += 4.0 + n * (0.5 + 0.01 * groups) * (2.0 if g > 8 else 1.0)
+                        cost += 3.0 + n * (0.05 + 0.06 * g) * (1.0 + 0.02 * groups)
                     if best is None or cost < best[0] - 1e-9:
                         best = (cost, per, head_split)
                 if per >= pages_seq or per * wide >= 64:

@@ -580,12 +580,13 @@ def test_attn_decode(nh, nkv, hd, window, split):
         K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
                         nh, nkv, hd, 64, window, scale, split, n, scratch)
         close(out, case.reference(window, scale), 1e-2, "attn_decode")
-    if (nh // nkv) % 2 == 0:
-        # the query heads of a kv head as two groups of work: the same numbers
-        halves = torch.full_like(out, 7.0)
-        K().attn_decode(q, q.stride(0), halves, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
-                        nh, nkv, hd, 64, window, scale, split, n, scratch, head_split=2)
-        assert torch.equal(halves, out)
+    for parts in (2, 4, 8, 16):
+        if (nh // nkv) % parts == 0:
+            # the query heads of a kv head as several groups of work: the same numbers
+            halves = torch.full_like(out, 7.0)
+            K().attn_decode(q, q.stride(0), halves, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq,
+                            T, nh, nkv, hd, 64, window, scale, split, n, scratch, head_split=parts)
+            assert torch.equal(halves, out), parts
     assert K().attn_decode_status() == 0
 
 
