@@ -96,6 +96,14 @@ int exl3_gemm_skinny_split(int N, int K);
 int exl3_gemm_pair(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int epilogue,
                    const float* ss_in, int ss_blocks, float eps, float width, float* h, float rho,
                    const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out, cudaStream_t stream);
+// The q/k/v projection of heads of 64 with the half-split rotary encoding (rot 64, or 0 for none) and the cache
+// write in its epilogue: of y [M, (nh + 2 nkv) * 64] only the queries' columns are written; rotated keys and
+// values go to each token's place in the paged pools (write_kv).
+int exl3_gemm_pair_rope(const void* x, const void* w, const void* bias, void* y, int M, int K, const float* ss_in,
+                        int ss_blocks, float eps, float width, const int* tok_pos, const int* tok_seq,
+                        const int* block_table, int bt_stride, const float* inv_freq, const float* inv_freq_lo, int rot,
+                        float pos_scale, int nh, int nkv, int hd, int page, void* k_pool, void* v_pool,
+                        int64_t pool_rows, int write_kv, cudaStream_t stream);
 int exl3_gemm_pair_status();
 int exl3_gemm_pair_ss_blocks(int N);
 

@@ -31,6 +31,12 @@
 // added on top of it, and the epilogue only multiplies by rho * k, adds rho * bias and writes.  (The product is
 // therefore not rounded to bfloat16 before it is added, as it is where the addition is a separate step.)
 //
+// Epilogue 3 is the q/k/v projection of heads of 64: the output, rounded to bfloat16 as the plain epilogue would
+// store it, gets the half-split rotary encoding (queries and keys; a row's sines and cosines are computed once per
+// tile, while the products run), the queries go to y, and the keys and values go straight to the token's place in
+// the paged cache: as one TMA store where a warp's 32 rows are 32 consecutive places of one page, with 16-byte
+// stores otherwise.  The key and value columns of y are not written.
+//
 // Every wait on an mbarrier is bounded: when one runs out the kernel records a code, leaves its loops, waits
 // (bounded) for the copies it may have in flight, meets its partner at the cluster barrier that every path reaches,
 // frees its tensor memory and returns; exl3_gemm_pair_status() reads the code.
@@ -45,7 +51,7 @@ using namespace tc5;
 
 constexpr int GP_BM = 256, GP_BN = 256, GP_BK = 64;
 // Epilogue warps: four (one per 32 lanes of tensor memory), or eight, two per 32 lanes with half of the columns each.
-__host__ __device__ constexpr int gp_epi_warps(int epi) { return epi == 2 ? 4 : 8; }
+__host__ __device__ constexpr int gp_epi_warps(int epi) { return epi >= 2 ? 4 : 8; }
 __host__ __device__ constexpr int gp_threads(int epi) { return 64 + 32 * gp_epi_warps(epi); }
 constexpr uint32_t GP_STAGE_A = 128 * GP_BK * 2, GP_STAGE_B = 128 * GP_BK * 2;       // per block
 constexpr uint32_t GP_BOX = 32 * 128;                                                  // a staging tile: 32 rows x 128 bytes
@@ -95,6 +101,18 @@ struct PairArgs {
   const void* norm_w;        // [N], float32 or bfloat16
   int norm_w_f32;
   float* ss_out;             // [M, tiles of 256 columns]
+  // epilogue 3
+  const int* tok_pos;        // [M] position of each row's token
+  const int* tok_seq;        // [M] its row of the block table
+  const int* block_table;
+  int bt_stride;
+  const float* inv_freq;     // [32] rotary frequencies, or null for no rotation
+  const float* inv_freq_lo;  // what float32 lost of them, or null
+  float pos_scale;
+  int nh, nkv;               // query and key/value heads of 64
+  int write_kv;
+  __nv_bfloat16* k_pool;     // [pages, nkv, 64, 64]
+  __nv_bfloat16* v_pool;
 };
 
 template <int EPI>
@@ -102,6 +120,8 @@ __global__ void __launch_bounds__(gp_threads(EPI), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y,      // y (0, 1) or x_raw (2): bfloat16, boxes of 64 columns
                  const __grid_constant__ CUtensorMap map_h,      // 2: the float32 residual, boxes of 32 columns
+                 const __grid_constant__ CUtensorMap map_k,      // 3: the key and the value pool as rows of 64 features,
+                 const __grid_constant__ CUtensorMap map_v,      //    boxes of 32 rows
                  const PairArgs a) {
   constexpr int STAGES = gp_stages(EPI), BOXES = gp_boxes(EPI), EPI_WARPS = gp_epi_warps(EPI), EPI_THREADS = 32 * EPI_WARPS;
   extern __shared__ unsigned char gp_smem_raw[];
@@ -127,6 +147,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     prefetch_map(&map_w);
     prefetch_map(&map_y);
     if (EPI == 2) prefetch_map(&map_h);
+    if (EPI == 3) { prefetch_map(&map_k); prefetch_map(&map_v); }
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 2 * EPI_WARPS); }
     for (int i = 0; i < 16; ++i) mbar_init(hbar + i, 1);
@@ -304,6 +325,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const float k_row = (EPI == 2 ? a.rho : 1.0f) * row_factor(row);
       const float k_bias = EPI == 2 ? a.rho : 1.0f;
       const bool plain = a.bias == nullptr && a.ss_in == nullptr && EPI != 2;      // the accumulator as it is
+      // 3: the row's sines and cosines, its page, and whether the warp's rows are 32 consecutive places of one
+      // page (all of this while the tile's products run)
+      float rc[EPI == 3 ? 32 : 1], rs[EPI == 3 ? 32 : 1];
+      int my_pos = 0, my_page = -1, pos0 = 0, page0 = -1;
+      bool together = false;
+      if (EPI == 3) {
+        int my_seq = -1;
+        if (row < a.M) { my_pos = __ldg(a.tok_pos + row); my_seq = __ldg(a.tok_seq + row); }
+        const float p = (float)my_pos * a.pos_scale;
+#pragma unroll
+        for (int d = 0; d < 32; ++d) {
+          if (a.inv_freq) rope_sincos(p, __ldg(a.inv_freq + d), a.inv_freq_lo ? __ldg(a.inv_freq_lo + d) : 0.0f, &rs[d], &rc[d]);
+          else { rc[d] = 1.0f; rs[d] = 0.0f; }
+        }
+        if (a.write_kv && row < a.M) my_page = __ldg(a.block_table + (int64_t)my_seq * a.bt_stride + my_pos / 64);
+        pos0 = __shfl_sync(0xffffffffu, my_pos, 0);
+        page0 = __shfl_sync(0xffffffffu, my_page, 0);
+        const int seq0 = __shfl_sync(0xffffffffu, my_seq, 0);
+        together = __all_sync(0xffffffffu, row < a.M && my_seq == seq0 && my_pos == pos0 + lane && my_page >= 0) && (pos0 & 31) == 0;
+      }
       // (also the barrier after which the staged bias and norm weights may be read) one verdict for all epilogue
       // threads, so that they leave the loop together
       if (!gp_epilogue_all<EPI_THREADS>(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
@@ -316,7 +357,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         __syncwarp();
         tmem_ld32_issue(taddr + s * 64, r0);
         tmem_ld32_issue(taddr + s * 64 + 32, r1);
-        if (EPI == 0 || (EPI == 1 && (s & 1) == 0)) {
+        if (EPI == 0 || EPI == 3 || (EPI == 1 && (s & 1) == 0)) {
           // the store before the last one used this staging tile
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
@@ -366,6 +407,49 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             else tma_store_skip();
           }
           ++n_store;
+        } else if (EPI == 3) {
+          const int col = n0 + s * 64, head = col >> 6;
+          if (col < a.N) {                                  // (the same for the whole warp)
+            // as the plain epilogue would store it, then rotated: pairs d, d + 32
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+            if (head < a.nh + a.nkv) {
+#pragma unroll
+              for (int d = 0; d < 32; ++d) {
+                const float x0 = v[d], x1 = v[d + 32];
+                v[d] = x0 * rc[d] - x1 * rs[d];
+                v[d + 32] = x1 * rc[d] + x0 * rs[d];
+              }
+            }
+            uint4 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              o[j] = make_uint4(gp_pack(v[8 * j], v[8 * j + 1]), gp_pack(v[8 * j + 2], v[8 * j + 3]),
+                                gp_pack(v[8 * j + 4], v[8 * j + 5]), gp_pack(v[8 * j + 6], v[8 * j + 7]));
+            const bool is_q = head < a.nh;
+            const bool is_k = !is_q && head < a.nh + a.nkv;
+            const int g = is_k ? head - a.nh : head - a.nh - a.nkv;
+            if (is_q || (a.write_kv && together)) {
+              unsigned char* box = my_boxes + (n_store & 1) * GP_BOX;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) *gp_box_chunk(box, lane, j) = o[j];
+              fence_smem_to_tma();
+              __syncwarp();
+              if (lane == 0) {
+                if (is_q) {
+                  if (row0 < a.M) tma_store_2d(&map_y, box, col, row0); else tma_store_skip();
+                } else {
+                  tma_store_2d(is_k ? &map_k : &map_v, box, 0, (page0 * a.nkv + g) * 64 + (pos0 & 63));
+                }
+              }
+              ++n_store;
+            } else if (a.write_kv && row < a.M && my_page >= 0) {
+              uint4* dst = reinterpret_cast<uint4*>((is_k ? a.k_pool : a.v_pool) +
+                                                    (((int64_t)my_page * a.nkv + g) * 64 + (my_pos & 63)) * 64);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) dst[j] = o[j];
+            }
+          }
         } else if (EPI == 1) {
           // four groups of (8 gate, 8 up) -> 32 outputs: half a staging tile
           unsigned char* box = my_boxes + (n_store & 1) * GP_BOX;
@@ -471,7 +555,7 @@ static void gp_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr,
 
 // Pairs that the GPU runs at once (a pair needs two SMs of one cluster-capable group).
 static int gp_max_pairs(int epi) {
-  static int pairs[3] = {0, 0, 0};
+  static int pairs[4] = {0, 0, 0, 0};
   if (pairs[epi]) return pairs[epi];
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -482,7 +566,7 @@ static int gp_max_pairs(int epi) {
   gp_launch_config(&cfg, attr, sms & ~1, epi, nullptr);
   cfg.numAttrs = 1;
   int clusters = 0;
-  const void* fn = epi == 0 ? gp_kernel<0>() : epi == 1 ? gp_kernel<1>() : gp_kernel<2>();
+  const void* fn = epi == 0 ? gp_kernel<0>() : epi == 1 ? gp_kernel<1>() : epi == 2 ? gp_kernel<2>() : gp_kernel<3>();
   if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0 && clusters < n) n = clusters;
   cudaGetLastError();
   pairs[epi] = n > 0 ? n : 1;
@@ -501,6 +585,57 @@ extern "C" int exl3_gemm_pair_status() {
   return v;
 }
 
+// The common part of the two entry points: `a` and `pools` carry what the epilogue needs beyond y.
+static int gp_run(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int epilogue,
+                  const float* ss_in, int ss_blocks, float eps, float width, float* h, PairArgs a, int64_t pool_rows,
+                  cudaStream_t stream) {
+  if (!aligned16(x) || !aligned16(w) || (y && !aligned16(y))) { set_error("gemm_pair: x, w and y must be 16-byte aligned"); return ERR_ALIGNMENT; }
+  if (ss_in && (ss_blocks < 1 || !(width > 0.0f))) { set_error("gemm_pair: the norm's pieces need blocks >= 1 and a width"); return ERR_BAD_ARGUMENT; }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(0));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(1));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(2));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(3));
+    if (e != cudaSuccess) { set_error("gemm_pair: cannot get %u bytes of shared memory: %s", gp_smem(2), cudaGetErrorString(e)); return (int)e; }
+    configured = true;
+  }
+  CUtensorMap map_x, map_w, map_y, map_h, map_k, map_v;
+  int rc = make_map_k64(&map_x, x, M, K, 128, "gemm_pair");
+  if (rc) return rc;
+  rc = make_map_k64(&map_w, w, N, K, 128, "gemm_pair");
+  if (rc) return rc;
+  rc = make_map_128b(&map_y, y, M, epilogue == 1 ? N / 2 : N, 2, 32, "gemm_pair");
+  if (rc) return rc;
+  map_h = map_k = map_v = map_y;
+  if (epilogue == 2) {
+    rc = make_map_128b(&map_h, h, M, N, 4, 32, "gemm_pair");
+    if (rc) return rc;
+  }
+  if (epilogue == 3 && a.write_kv) {
+    rc = make_map_128b(&map_k, a.k_pool, pool_rows, 64, 2, 32, "gemm_pair");
+    if (rc) return rc;
+    rc = make_map_128b(&map_v, a.v_pool, pool_rows, 64, 2, 32, "gemm_pair");
+    if (rc) return rc;
+  }
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.M = M; a.N = N; a.K = K;
+  a.ss_in = ss_in; a.ss_blocks = ss_blocks; a.eps = eps; a.width = width;
+  const int tiles = ceil_div(M, GP_BM) * ceil_div(N, GP_BN);
+  const int max_pairs = gp_max_pairs(epilogue);
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  gp_launch_config(&cfg, attr, 2 * pairs, epilogue, stream);
+  cudaError_t e;
+  if (epilogue == 0) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<0>, map_x, map_w, map_y, map_h, map_k, map_v, a);
+  else if (epilogue == 1) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<1>, map_x, map_w, map_y, map_h, map_k, map_v, a);
+  else if (epilogue == 2) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<2>, map_x, map_w, map_y, map_h, map_k, map_v, a);
+  else e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<3>, map_x, map_w, map_y, map_h, map_k, map_v, a);
+  if (e != cudaSuccess) { set_error("gemm_pair: launch failed: %s", cudaGetErrorString(e)); return (int)e; }
+  return launch_status("gemm_pair");
+}
+
 extern "C" int exl3_gemm_pair(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                               int epilogue, const float* ss_in, int ss_blocks, float eps, float width, float* h,
                               float rho, const void* norm_w, int norm_w_dtype, void* x_raw, float* ss_out,
@@ -511,54 +646,43 @@ extern "C" int exl3_gemm_pair(const void* x, const void* w, const void* bias, vo
               M, N, K, epilogue);
     return ERR_BAD_ARGUMENT;
   }
-  if (!aligned16(x) || !aligned16(w) || (epilogue != 2 && !aligned16(y))) { set_error("gemm_pair: x, w and y must be 16-byte aligned"); return ERR_ALIGNMENT; }
-  if (ss_in && (ss_blocks < 1 || !(width > 0.0f))) { set_error("gemm_pair: the norm's pieces need blocks >= 1 and a width"); return ERR_BAD_ARGUMENT; }
+  PairArgs a = {};
   if (epilogue == 2) {
     if (!h || !norm_w || !x_raw || !ss_out || !aligned16(h) || !aligned16(x_raw) ||
         (norm_w_dtype != DT_F32 && norm_w_dtype != DT_BF16) || !(rho != 0.0f)) {
       set_error("gemm_pair: the residual epilogue needs h, norm_w (float32 or bfloat16), x_raw and ss_out, 16-byte aligned, and a scale that is not zero");
       return ERR_BAD_ARGUMENT;
     }
+    a.rho = rho; a.norm_w = norm_w; a.norm_w_f32 = norm_w_dtype == DT_F32 ? 1 : 0;
+    a.ss_out = ss_out;
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(0));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(1));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gp_smem(2));
-    if (e != cudaSuccess) { set_error("gemm_pair: cannot get %u bytes of shared memory: %s", gp_smem(2), cudaGetErrorString(e)); return (int)e; }
-    configured = true;
+  return gp_run(x, w, bias, epilogue == 2 ? x_raw : y, M, N, K, epilogue, ss_in, ss_blocks, eps, width, h, a, 0, stream);
+}
+
+// The q/k/v projection of nh query and nkv key/value heads of 64 with the rotary encoding (rot = 64, or 0 for
+// none) and the cache write in its epilogue: y is [M, (nh + 2 nkv) * 64], of which the queries' columns are written;
+// keys and values go to the pools [pool_rows / (nkv * 64) pages, nkv, 64, 64] when write_kv is set.
+extern "C" int exl3_gemm_pair_rope(const void* x, const void* w, const void* bias, void* y, int M, int K,
+                                   const float* ss_in, int ss_blocks, float eps, float width, const int* tok_pos,
+                                   const int* tok_seq, const int* block_table, int bt_stride, const float* inv_freq,
+                                   const float* inv_freq_lo, int rot, float pos_scale, int nh, int nkv, int hd,
+                                   int page, void* k_pool, void* v_pool, int64_t pool_rows, int write_kv,
+                                   cudaStream_t stream) {
+  if (M == 0) return 0;
+  if (M < 0 || K < 8 || K % 8 != 0 || nh < 1 || nkv < 1 || hd != 64 || page != 64 || (rot != 0 && rot != 64) ||
+      (rot != 0 && !inv_freq) || !tok_pos || !tok_seq || (write_kv && (!block_table || !k_pool || !v_pool || pool_rows < 64))) {
+    set_error("gemm_pair_rope: needs heads of 64 rotated as a whole or not at all, pages of 64, K a multiple of 8, positions and "
+              "(to write the cache) a block table and pools; got M=%d K=%d heads=%d kv_heads=%d head_dim=%d page=%d rot=%d",
+              M, K, nh, nkv, hd, page, rot);
+    return ERR_BAD_ARGUMENT;
   }
-  CUtensorMap map_x, map_w, map_y, map_h;
-  int rc = make_map_k64(&map_x, x, M, K, 128, "gemm_pair");
-  if (rc) return rc;
-  rc = make_map_k64(&map_w, w, N, K, 128, "gemm_pair");
-  if (rc) return rc;
-  rc = make_map_128b(&map_y, epilogue == 2 ? x_raw : y, M, epilogue == 1 ? N / 2 : N, 2, 32, "gemm_pair");
-  if (rc) return rc;
-  if (epilogue == 2) {
-    rc = make_map_128b(&map_h, h, M, N, 4, 32, "gemm_pair");
-    if (rc) return rc;
-  } else {
-    map_h = map_y;
-  }
+  if (write_kv && (!aligned16(k_pool) || !aligned16(v_pool))) { set_error("gemm_pair_rope: the pools must be 16-byte aligned"); return ERR_ALIGNMENT; }
   PairArgs a = {};
-  a.bias = static_cast<const __nv_bfloat16*>(bias);
-  a.M = M; a.N = N; a.K = K;
-  a.ss_in = ss_in; a.ss_blocks = ss_blocks; a.eps = eps; a.width = width;
-  a.rho = rho; a.norm_w = norm_w; a.norm_w_f32 = norm_w_dtype == DT_F32 ? 1 : 0;
-  a.ss_out = ss_out;
-  const int tiles = ceil_div(M, GP_BM) * ceil_div(N, GP_BN);
-  const int max_pairs = gp_max_pairs(epilogue);
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[2];
-  gp_launch_config(&cfg, attr, 2 * pairs, epilogue, stream);
-  cudaError_t e;
-  if (epilogue == 0) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<0>, map_x, map_w, map_y, map_h, a);
-  else if (epilogue == 1) e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<1>, map_x, map_w, map_y, map_h, a);
-  else e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<2>, map_x, map_w, map_y, map_h, a);
-  if (e != cudaSuccess) { set_error("gemm_pair: launch failed: %s", cudaGetErrorString(e)); return (int)e; }
-  return launch_status("gemm_pair");
+  a.tok_pos = tok_pos; a.tok_seq = tok_seq; a.block_table = block_table; a.bt_stride = bt_stride;
+  a.inv_freq = rot ? inv_freq : nullptr; a.inv_freq_lo = rot ? inv_freq_lo : nullptr; a.pos_scale = pos_scale;
+  a.nh = nh; a.nkv = nkv; a.write_kv = write_kv ? 1 : 0;
+  a.k_pool = static_cast<__nv_bfloat16*>(k_pool); a.v_pool = static_cast<__nv_bfloat16*>(v_pool);
+  return gp_run(x, w, bias, y, M, (nh + 2 * nkv) * 64, K, 3, ss_in, ss_blocks, eps, width, nullptr, a, pool_rows, stream);
 }
 
 // Tiles of 256 columns per row in ss_out of the residual epilogue.

@@ -368,6 +368,50 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+def gemm_pair_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], scale, tok_pos: torch.Tensor,
+                   tok_seq: torch.Tensor, block_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                   rot: int, pos_scale: float, heads: int, kv_heads: int, head_dim: int, page: int,
+                   k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], write_kv: bool) -> torch.Tensor:
+    """The q/k/v projection of many rows (``gemm_pair``; ``scale`` as there) with the rotary encoding and the
+    cache write of ``rope_kv_write`` in its epilogue, for heads of 64 rotated as a whole (``rot`` 64) or not at
+    all (0) and pages of 64.  Returns ``[M, (heads + 2 kv_heads) * 64]`` of which only the queries' columns are
+    written: the rotated keys and the values are in the cache (when ``write_kv``) and nowhere else."""
+    M, K = x.shape
+    N = (heads + 2 * kv_heads) * head_dim
+    if tuple(w.shape) != (N, K):
+        raise KernelLibraryError(f"gemm_pair_rope: x is {tuple(x.shape)}, w is {tuple(w.shape)}, heads need {N} rows")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelLibraryError("gemm_pair_rope: x and w must be bfloat16")
+    _contig(x, "x")
+    _contig(w, "w")
+    ss_in, ss_blocks, eps, width = None, 0, 0.0, 1.0
+    if scale is not None:
+        ss_in, eps, width = scale
+        if ss_in.dtype != torch.float32 or ss_in.dim() != 2 or ss_in.shape[0] < M:
+            raise KernelLibraryError("gemm_pair_rope: ss must be float32 [rows >= M, blocks]")
+        _contig(ss_in, "ss")
+        ss_blocks = ss_in.shape[1]
+    if tok_pos.numel() < M or tok_seq.numel() < M:
+        raise KernelLibraryError("gemm_pair_rope: a position and a sequence for every row")
+    hi, lo = _rotary_rows(inv_freq, rot, "gemm_pair_rope") if rot else (_c_void_p(0), _c_void_p(0))
+    pool_rows = 0
+    if write_kv:
+        if k_pool.dtype != torch.bfloat16 or v_pool.dtype != torch.bfloat16:
+            raise KernelLibraryError("gemm_pair_rope: the cache must be bfloat16")
+        _contig(k_pool, "k_pool")
+        _contig(v_pool, "v_pool")
+        pool_rows = k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _check(library().exl3_gemm_pair_rope(
+        _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(M), _c_int(K), _ptr(ss_in), _c_int(ss_blocks), _c_float(eps),
+        _c_float(width), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table) if write_kv else _c_void_p(0),
+        _c_int(block_table.stride(0)) if write_kv else _c_int(0), hi, lo, _c_int(rot), _c_float(pos_scale),
+        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _ptr(k_pool) if write_kv else _c_void_p(0),
+        _ptr(v_pool) if write_kv else _c_void_p(0), _c_int64(pool_rows), _c_int(1 if write_kv else 0), _stream()),
+        "gemm_pair_rope")
+    return out
+
+
 def gemm_pair_efficiency(M: int, N: int, device) -> float:
     """The share of the GPU's pairs of SMs that ``gemm_pair``'s tiles of 256 x 256 keep busy, averaged over its
     rounds of tiles: 72 tiles on 74 pairs 0.97, 32 tiles 0.43, 80 tiles (two rounds, the second nearly empty) 0.54."""

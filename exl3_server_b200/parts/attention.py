@@ -20,6 +20,8 @@ position step and the CUDA-core attention kernel.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Dict, List, Optional
 
@@ -36,6 +38,8 @@ from .spec import MixerSpec, PositionSpec
 SPLIT_KEYS = 256
 # Work items (token x kv head x chunk) beyond which the bfloat16 path doubles the chunk length.
 BUSY_ITEMS = 1776
+# Prompts: the position step inside the q/k/v projection's epilogue where the sizes allow it (0: always a kernel of its own).
+PROMPT_FUSED = os.environ.get("EXL3_PROMPT_FUSED", "1") != "0"
 
 
 class Attention:
@@ -86,6 +90,13 @@ class Attention:
         s = self.spec
         if kv is None:
             raise RuntimeError("attention needs a cache view")
+        qkv = self._prompt_fused(x, batch, kv)
+        if qkv is not None:
+            # prompts: the projection has rotated the queries and put the rotated keys and the values into the
+            # cache, from where the attention reads them
+            out = torch.empty((qkv.shape[0], s.heads * s.head_dim), dtype=qkv.dtype, device=qkv.device)
+            self.attend(qkv, out, batch, kv)
+            return self.o(out, then=then)
         qkv = self.qkv(x)
         T = qkv.shape[0]
         out = torch.empty((T, s.heads * s.head_dim), dtype=qkv.dtype, device=qkv.device)
@@ -93,6 +104,20 @@ class Attention:
             self.position.rotate_and_store(qkv, batch, kv, s.heads, s.kv_heads, s.head_dim)
             self.attend(qkv, out, batch, kv)
         return self.o(out, then=then)
+
+    def _prompt_fused(self, x, batch, kv):
+        """Prompts in bfloat16 with heads and pages of 64, enough rows for the paired GEMM and an attention kernel
+        that reads keys and values from the cache only: the q/k/v projection applies the position encoding and
+        writes the cache in its epilogue (``Linear.heads_rotated_and_cached``), so the position step is no kernel of
+        its own.  None when the step, the sizes or the position part do not allow it."""
+        s = self.spec
+        fused = getattr(self.position, "fused_rotation", None)
+        if batch.max_new <= 1 or fused is None or self.ctx.dtype != torch.bfloat16 or not batch.tiles or not PROMPT_FUSED:
+            return None
+        if not K.attn_prefill_tc_supported(torch.bfloat16, s.head_dim, kv.page_size):
+            return None
+        return self.qkv.heads_rotated_and_cached(x, s.heads, s.kv_heads, s.head_dim, kv.page_size, fused(s.head_dim),
+                                                 batch, kv)
 
     def _decode_fused(self, qkv: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
         """One token per sequence, bfloat16, heads of 64 or 128: the decode kernel rotates the queries and the new key

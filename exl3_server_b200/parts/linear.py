@@ -111,6 +111,25 @@ class Linear:
             return out
         return K.gemm_simt(x, self.weight, self.bias, out_dtype)
 
+    def heads_rotated_and_cached(self, x, heads: int, kv_heads: int, head_dim: int, page: int, rotation, batch, kv):
+        """For a weight that is a q/k/v projection: the product of many rows with the rotary encoding and the
+        cache write in its epilogue (``rotation``: a position part's ``fused_rotation``; keys and values go to
+        ``kv`` when it owns its pages).  Returns ``[rows, (heads + 2 kv_heads) * head_dim]`` with the queries'
+        columns written, or None when the sizes are not the paired GEMM's with that epilogue (heads and pages of
+        64, enough rows): the caller then projects, rotates and stores in separate steps."""
+        if rotation is None or head_dim != 64 or page != 64 or kv is None:
+            return None
+        inv_freq, rot, pos_scale = rotation
+        if rot not in (0, head_dim) or self._streaming_kernel(x.shape[0]) is not K.gemm_pair:
+            return None
+        scale = None
+        if isinstance(x, RawNormed):
+            scale, x = (x.ss, x.eps, float(x.width)), x.x_raw
+        write = bool(kv.owns)
+        return K.gemm_pair_rope(x, self.weight, self.bias, scale, batch.tok_pos, batch.tok_seq, kv.block_table,
+                                inv_freq, rot, pos_scale, heads, kv_heads, head_dim, page,
+                                kv.k if write else None, kv.v if write else None, write)
+
     def streams_weights(self, rows: int) -> bool:
         """Whether ``rows`` rows of input go through a kernel that reads the weights once."""
         return self._streaming_kernel(rows) is not None

@@ -399,6 +399,69 @@ def test_gemm_pair_folds_into_the_residual_and_prepares_the_norm(M, N, Kd, norm_
     assert K().gemm_pair_status() == 0
 
 
+@pytest.mark.parametrize("lens,starts", [([2048], [0]),               # one prompt: every warp's rows are one page's places
+                                         ([300, 64, 1, 515], [0, 0, 0, 0]),  # sequences that start anywhere in a tile
+                                         ([200, 96], [64, 1000])])           # prompts that go on from earlier tokens
+@pytest.mark.parametrize("nh,nkv", [(4, 4), (6, 2), (3, 1)])
+@pytest.mark.parametrize("rot", [64, 0])
+def test_gemm_pair_rotates_and_writes_the_cache(lens, starts, nh, nkv, rot):
+    """The q/k/v projection with the position step in its epilogue, against the projection followed by the
+    kernel of that step: the same queries, and the same keys and values at every token's place in the cache
+    (and nothing written anywhere else)."""
+    torch.manual_seed(16)
+    hd, page, Kd = 64, 64, 136
+    T = sum(lens)
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(T, Kd, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    need = [(s0 + n + page - 1) // page for s0, n in zip(starts, lens)]
+    n_pages = sum(need) + 3
+    perm = torch.randperm(n_pages).tolist()
+    table = torch.full((len(lens), max(need)), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(need):
+        table[i, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    table = table.to(DEV)
+    tok_pos = torch.cat([torch.arange(s0, s0 + n) for s0, n in zip(starts, lens)]).to(torch.int32).to(DEV)
+    tok_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).to(torch.int32).to(DEV)
+    inv_freq = K().rotary_table(torch.pow(torch.tensor(10000.0, dtype=torch.float64),
+                                          -2.0 * torch.arange(0, hd // 2, dtype=torch.float64) / hd)).to(DEV)
+    junk_k = torch.randn(n_pages, nkv, page, hd, device=DEV).bfloat16()
+    junk_v = torch.randn(n_pages, nkv, page, hd, device=DEV).bfloat16()
+    # the separate steps
+    want = K().gemm_pair(x, w, b)
+    k1, v1 = junk_k.clone(), junk_v.clone()
+    K().rope_kv_write(want, inv_freq, rot, 1.0, tok_pos, tok_seq, table, k1, v1, nh, nkv, hd, page, True)
+    for bias in (b, None):
+        if bias is None:
+            want = K().gemm_pair(x, w, None)
+            k1, v1 = junk_k.clone(), junk_v.clone()
+            K().rope_kv_write(want, inv_freq, rot, 1.0, tok_pos, tok_seq, table, k1, v1, nh, nkv, hd, page, True)
+        k2, v2 = junk_k.clone(), junk_v.clone()
+        got = K().gemm_pair_rope(x, w, bias, None, tok_pos, tok_seq, table, inv_freq, rot, 1.0, nh, nkv, hd, page,
+                                 k2, v2, True)
+        close(got[:, :nh * hd], want[:, :nh * hd].double(), 1e-2, "rotated queries")
+        close(k2, k1.double(), 1e-2, "key cache")
+        assert torch.equal(v2, v1)                       # values are copied, not computed with
+        # where no token lives, the pools are as they were
+        touched = torch.zeros(n_pages, page, dtype=torch.bool)
+        pages_of = table.cpu()
+        for p_, s_ in zip(tok_pos.tolist(), tok_seq.tolist()):
+            touched[pages_of[s_, p_ // page], p_ % page] = True
+        free = ~touched.to(DEV)
+        assert torch.equal(k2.permute(0, 2, 1, 3)[free], junk_k.permute(0, 2, 1, 3)[free])
+        assert torch.equal(v2.permute(0, 2, 1, 3)[free], junk_v.permute(0, 2, 1, 3)[free])
+        # without the cache write: the queries only
+        k3, v3 = junk_k.clone(), junk_v.clone()
+        got = K().gemm_pair_rope(x, w, bias, None, tok_pos, tok_seq, None, inv_freq, rot, 1.0, nh, nkv, hd, page,
+                                 None, None, False)
+        close(got[:, :nh * hd], want[:, :nh * hd].double(), 1e-2, "rotated queries, no cache write")
+    torch.cuda.synchronize()
+    assert K().gemm_pair_status() == 0
+
+
 def test_gemm_pair_refuses_what_it_cannot_do():
     from exl3_server_b200.ops.lib import KernelLibraryError
     x = torch.zeros(300, 64, device=DEV).bfloat16()
