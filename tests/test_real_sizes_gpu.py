@@ -48,3 +48,47 @@ def test_two_layers_of_real_sizes(tmp_path, name):
                 eng.close(s)
         del eng
         torch.cuda.empty_cache()
+
+
+def test_long_prompts_through_the_paired_projections(tmp_path, monkeypatch):
+    """Two prompts of 2,047 and 1,501 tokens in one step at the MiniCPM-2B layer sizes (a small vocabulary, so that
+    the plain implementation is done in seconds): rows enough for the paired tcgen05 GEMM with the norms, the
+    residual, the rotary encoding and the cache write in its epilogues; the second prompt starts in the middle of
+    a tile and of a warp's rows, so its keys and values go to the cache by the epilogue's other path.  Then both
+    go on token by token from that cache."""
+    from exl3_server_b200 import Engine, LlamaConfig, write_random_model
+    from exl3_server_b200.config.presets import sizes
+    from exl3_server_b200.ops import kernels as K
+    from helpers import batched_trace
+    cfg = LlamaConfig(**sizes("minicpm-2b", num_hidden_layers=2, vocab_size=1000))
+    folder = str(tmp_path / "m")
+    write_random_model(cfg, folder, seed=4, std=0.02)
+    g = torch.Generator().manual_seed(3)
+    reqs = {"a": torch.randint(0, cfg.vocab_size, (2047 + 6,), generator=g).tolist(),
+            "b": torch.randint(0, cfg.vocab_size, (1501 + 6,), generator=g).tolist()}
+    plain = PlainModel(folder)
+    want = {rid: plain.logits(t).numpy() for rid, t in reqs.items()}
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=8192)
+    calls = {"rotated": 0, "into the residual": 0, "gated": 0}
+    rope, pair = K.gemm_pair_rope, K.gemm_pair
+
+    def counted_rope(*a, **k):
+        calls["rotated"] += 1
+        return rope(*a, **k)
+
+    def counted_pair(*a, **k):
+        calls["into the residual"] += k.get("resid") is not None
+        calls["gated"] += bool(k.get("gated"))
+        return pair(*a, **k)
+
+    monkeypatch.setattr(K, "gemm_pair_rope", counted_rope)
+    monkeypatch.setattr(K, "gemm_pair", counted_pair)
+    got = run_trace(eng, batched_trace(reqs, [["a", "b"]], {"a": 2047, "b": 1501}))
+    # per layer: q/k/v with the position step, o and down into the residual (the last down has no norm after it
+    # inside the block), gate/up with the activation
+    assert calls == {"rotated": 2, "into the residual": 3, "gated": 2}, calls
+    for rid in reqs:
+        per_pos = np.max(np.abs(got[rid] - want[rid]), axis=1) / np.max(np.abs(want[rid]))
+        bad = np.nonzero(per_pos > TOL["bfloat16"])[0]
+        assert bad.size == 0, f"request {rid}: first wrong position {bad[0]}, error {per_pos[bad[0]]:.3e}"
+    K.check_status()
