@@ -29,7 +29,8 @@ from typing import Dict, List
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = "/root/reference"
+# where a checkout of muyouming/exl3-server lies: the environment says, else a sibling folder of this repository
+DEFAULT_REFERENCE = os.environ.get("EXL3_REFERENCE_DIR") or os.path.normpath(os.path.join(HERE, "..", "..", "..", "reference"))
 MASK = (1 << 64) - 1
 
 
