@@ -110,15 +110,16 @@ int exl3_gemm_pair_ss_blocks(int N);
 // Decoded tokens on the tensor cores with TMA loads from the paged cache (bfloat16, head_dim 64 or 128, pages of 64, up
 // to 16 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing
-// them to the cache itself.  head_split 2: the query heads of a kv head as two groups of work (1: one).  See
-// attention_decode.cu.
+// them to the cache itself.  head_split n (a divisor of the query heads per kv head): the query heads of a kv head
+// as n groups of work.  in_block: a block per (token, group of heads), whose warps take the item's chunks (at most 4)
+// and merge them in shared memory; no scratch then.  See attention_decode.cu.
 int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys, int max_splits);
 int exl3_attn_decode_status();
 int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
                      int64_t n_pool_rows, const int* block_table, int bt_stride, const int* tok_pos,
                      const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, float scale,
                      int split_keys, int max_splits, float* scratch, size_t scratch_bytes, const float* inv_freq,
-                     const float* inv_freq_lo, int rot, float pos_scale, int write_new, int head_split,
+                     const float* inv_freq_lo, int rot, float pos_scale, int write_new, int head_split, int in_block,
                      cudaStream_t stream);
 
 int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,

@@ -150,7 +150,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    int split_keys, int max_splits, float* __restrict__ scratch, int* __restrict__ counters,
                    const float* __restrict__ inv_freq, const float* __restrict__ inv_freq_lo, float pos_scale,
                    int rotate, int write_new,
-                   __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int kv_rep) {
+                   __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int kv_rep, int in_block) {
   // nkv counts groups of query heads that are worked on together.  With kv_rep = 2 the query heads of a kv head
   // are two such groups (g and g + 1 read kv head g / 2): twice the work items and two merges of half the size,
   // for steps with few tokens, where a single warp's merge of a wide group is what takes the time.
@@ -215,13 +215,24 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
   const int G = nh / nkv;
   const int rec = HD + 2;
-  // This warp's share: chunks i0 .. i1 - 1 of the list ordered by token, kv head, chunk.
-  const int n_chunks = nkv * s_cum[T];
-  const int n_warps = gridDim.x * AD_WARPS, gw = blockIdx.x * AD_WARPS + warp;
-  const int i0 = (int)((int64_t)gw * n_chunks / n_warps), i1 = (int)((int64_t)(gw + 1) * n_chunks / n_warps);
-
   auto chunks_of = [&](int t) { return s_cum[t + 1] - s_cum[t]; };
   auto base_of = [&](int t, int g) { return nkv * s_cum[t] + g * chunks_of(t); };   // index of chunk 0 of (t, g)
+  // This warp's share: chunks i0 .. i1 - 1 of the list ordered by token, kv head, chunk: an equal contiguous share
+  // of all of them, or (in_block: a block per (token, group of heads), at most AD_WARPS chunks each) the block's
+  // item's chunk number `warp`, so that the item's chunks meet in this block's shared memory and no record of
+  // them goes through global memory.
+  const int n_chunks = nkv * s_cum[T];
+  const int n_warps = gridDim.x * AD_WARPS, gw = blockIdx.x * AD_WARPS + warp;
+  int i0 = (int)((int64_t)gw * n_chunks / n_warps), i1 = (int)((int64_t)(gw + 1) * n_chunks / n_warps);
+  const int t_blk = in_block ? (int)blockIdx.x / nkv : 0, g_blk = in_block ? (int)blockIdx.x % nkv : 0;
+  if (in_block) {
+    i0 = base_of(t_blk, g_blk) + warp;
+    i1 = warp < chunks_of(t_blk) ? i0 + 1 : i0;
+  }
+  // in_block: chunk sp's record lies at the start of warp sp's ring of pages, which that warp no longer needs
+  // when it has walked its chunk
+  float* const rec_blk = reinterpret_cast<float*>(ad_smem_raw + ((1024u - (ad_smem_u32(ad_smem_raw) & 1023u)) & 1023u));
+  constexpr int REC_BLK_STRIDE = AD_STAGES * AD_STAGE_BYTES / 4;      // floats from one warp's ring to the next
   // the token whose chunks hold index i
   auto token_of = [&](int i) {
     int lo = 0, hi = T - 1;
@@ -704,7 +715,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             dst[16 * d + gl + 8] = __float2bfloat16(o[c][d][h + 2] * inv);
           }
         } else {
-          float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
+          float* sc = in_block ? rec_blk + sp * REC_BLK_STRIDE + n * rec
+                               : scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
 #pragma unroll
           for (int d = 0; d < NJ; ++d) {
             sc[16 * d + gl] = o[c][d][h];
@@ -731,7 +743,39 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       }
     }
   }
-  if (ok) {
+  if (in_block) {
+    if (!ok) {
+      if (lane == 0) atomicExch(&g_ad_error, 1);
+      for (; cn < pn; ++cn) {
+        if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
+      }
+    }
+    __syncthreads();                                     // every warp comes here, whatever its share and its verdict
+    const int n_rec = chunks_of(t_blk);
+    if (n_rec > 1) {
+      // the item's chunks, in chunk order; a warp takes every fourth head, a lane HD / 32 features
+      for (int n = warp; n < G; n += AD_WARPS) {
+        const float* hb = rec_blk + n * rec;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < n_rec; ++s2) M = fmaxf(M, hb[s2 * REC_BLK_STRIDE + HD]);
+        float w[AD_WARPS], ll = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < AD_WARPS; ++s2) {
+          w[s2] = s2 < n_rec ? ad_exp2(hb[s2 * REC_BLK_STRIDE + HD] - M) : 0.0f;
+          ll += s2 < n_rec ? hb[s2 * REC_BLK_STRIDE + HD + 1] * w[s2] : 0.0f;
+        }
+        __nv_bfloat16* dst = out + ((int64_t)t_blk * nh + g_blk * G + n) * HD;
+#pragma unroll
+        for (int e = 0; e < HD / 32; ++e) {
+          const int d = e * 32 + lane;
+          float acc = 0.0f;
+#pragma unroll
+          for (int s2 = 0; s2 < AD_WARPS; ++s2) acc += s2 < n_rec ? hb[s2 * REC_BLK_STRIDE + d] * w[s2] : 0.0f;
+          dst[d] = __float2bfloat16(acc / ll);
+        }
+      }
+    }
+  } else if (ok) {
     // All of this warp's records are written.  One fence for all of them, then a ticket per chunk,
     // lanes side by side; the chunks of a (token, kv head) are merged by the warp that draws the
     // last ticket.  Which warp that is varies; what it computes does not.
@@ -824,8 +868,12 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
                                 const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
                                 float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
-                                int write_new, int head_split, cudaStream_t stream) {
+                                int write_new, int head_split, int in_block, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (in_block && (max_splits < 1 || max_splits > AD_WARPS)) {
+    set_error("attn_decode: a block merges at most %d chunks of a (token, group of heads) itself, got %d", AD_WARPS, max_splits);
+    return ERR_BAD_ARGUMENT;
+  }
   if (head_split < 1 || head_split > AD_MAX_GROUP || nkv < 1 || nh % nkv != 0 || (nh / nkv) % head_split != 0) {
     set_error("attn_decode: head_split must divide the %d query heads of a kv head; got %d", nkv > 0 ? nh / nkv : 0, head_split);
     return ERR_BAD_ARGUMENT;
@@ -846,7 +894,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
     set_error("attn_decode: q, k, v and out must be 16-byte aligned with a row stride in 16-byte units");
     return ERR_ALIGNMENT;
   }
-  if (exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits) > scratch_bytes) {
+  if (!in_block && exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits) > scratch_bytes) {
     set_error("attn_decode: scratch of %zu bytes is too small, need %zu", scratch_bytes,
               exl3_attn_tokens_scratch_bytes(T, nh, hd, max_splits));
     return ERR_SCRATCH;
@@ -876,19 +924,19 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   // one block per SM as soon as there is a chunk for each: the warps' equal shares then spread few chunks over all
   // SMs (and their memory pipes) instead of filling the warps of half of them
   const int groups = nkv * head_split;                     // groups of query heads worked on together
-  if (max_splits > 1 && (int64_t)T * groups > AD_COUNTER_SLOTS) {
+  if (max_splits > 1 && !in_block && (int64_t)T * groups > AD_COUNTER_SLOTS) {
     set_error("attn_decode: %d tokens x %d groups of heads exceed the %d merge counters", T, groups, AD_COUNTER_SLOTS);
     return ERR_UNSUPPORTED;
   }
-  const int blocks = (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
-  int* counters = max_splits > 1 ? reinterpret_cast<int*>(scratch) : nullptr;
-  float* records = max_splits > 1 ? scratch + AD_COUNTER_SLOTS : nullptr;
+  const int blocks = in_block ? T * groups : (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
+  int* counters = max_splits > 1 && !in_block ? reinterpret_cast<int*>(scratch) : nullptr;
+  float* records = max_splits > 1 && !in_block ? scratch + AD_COUNTER_SLOTS : nullptr;
 #define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
   launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
-             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split)
+             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split, in_block ? 1 : 0)
   const bool wide = nh / groups > 8;                       // more than one block of 8 query heads per group
   if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2); else EXL3_AD_LAUNCH(64, 1); }
   else { if (wide) EXL3_AD_LAUNCH(128, 2); else EXL3_AD_LAUNCH(128, 1); }

@@ -134,14 +134,15 @@ class Attention:
         T = qkv.shape[0]
         if not self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             return False
-        split, head_split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+        split, head_split, in_block = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
         n = self._chunks(batch.max_kv_len, split)
         scratch = None
-        if n > 1:
+        if n > 1 and not in_block:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
         K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
-                      inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns, head_split=head_split)
+                      inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns, head_split=head_split,
+                      in_block=in_block)
         return True
 
     def _decode_kernel_takes(self, dtype: torch.dtype, T: int, page: int) -> bool:
@@ -162,14 +163,14 @@ class Attention:
             return
         if self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             # decoded tokens, heads of 64 or 128: pages by TMA, both products on the tensor cores, a warp per chunk
-            split, head_split = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+            split, head_split, in_block = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
             n = self._chunks(batch.max_kv_len, split)
             scratch = None
-            if n > 1:
+            if n > 1 and not in_block:
                 scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
             K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                           s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
-                          head_split=head_split)
+                          head_split=head_split, in_block=in_block)
             return
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
@@ -188,10 +189,12 @@ class Attention:
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
-        """``(keys per chunk, head_split)`` for the tensor-core decode kernel: chunks of whole pages (a power of two
-        of them, at most 64 of 16 KB), and into how many groups of work the query heads of a kv head are cut
+        """``(keys per chunk, head_split, in_block)`` for the tensor-core decode kernel: chunks of whole pages (a
+        power of two of them, at most 64 of 16 KB), into how many groups of work the query heads of a kv head are cut
         (``head_split``: that many times the work items, each merge that much smaller, the keys and values read
-        again from L2).  By a small model of the kernel's time, its constants fitted to sweeps at four head layouts
+        again from L2), and whether a block takes a whole (token, group of heads) and merges its up to four chunks in
+        shared memory (``in_block``) instead of warps taking equal shares of all chunks and merging through global
+        memory.  By a small model of the kernel's time, its constants fitted to sweeps at four head layouts
         (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128) and batches of 1 to 64 (to 14 % in the mean): 4 us to start;
         a warp walks its chunk at 0.8 us per 16 KB of keys and values plus 0.02 us for every query head in its group;
         when there are more chunks than warps a warp takes several in turn; all warps together cannot read faster
@@ -202,14 +205,18 @@ class Attention:
         number of chunks each, as many pieces as there are warps (one token of 32 query heads of 128 on 2 kv heads
         at 2,048 tokens: 16 groups of 16 chunks take 13 us, one group of 8 chunks 33 us), one chunk wins for short
         contexts and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks
-        only where they are needed to give every SM work.  The choice depends on the step's size, not on a token's
-        position: results differ between batch sizes by rounding."""
+        only where they are needed to give every SM work.  A block per item costs its walk (a quarter of the keys per
+        warp) plus 1.5 us for the merge in shared memory, one round of blocks per SM count; it is taken when that is
+        0.85 of the other way's cost or less: for about as many items as the GPU has SMs, each too long for one warp
+        (64 sequences of 2 kv heads with 16 query heads of 128 each at 2,048 tokens: 33 against 43 us).  The choice
+        depends on the step's size, not on a token's position: results differ between batch sizes by rounding."""
         s = self.spec
         keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
         pages_seq = max(1, (keys + page - 1) // page)
         wide = max(1, s.head_dim // 64)                     # 16 KB stages in a page
         group = s.heads // s.kv_heads
-        warps = 4 * K.sm_count(device)
+        sms = K.sm_count(device)
+        warps = 4 * sms
         best = None
         for head_split in (1, 2, 4, 8, 16):
             if group % head_split:
@@ -230,11 +237,16 @@ class Attention:
                     if n > 1:
                         cost += 3.0 + n * (0.05 + 0.06 * g) * (1.0 + 0.02 * groups)
                     if best is None or cost < best[0] - 1e-9:
-                        best = (cost, per, head_split)
+                        best = (cost, per, head_split, False)
+                    if 1 < n + (1 if s.window > 0 else 0) <= 4:
+                        rounds = (groups + sms - 1) // sms
+                        cost = (4.0 + max(rounds * per * wide * stage_us, once_us, again_us) + 1.5) / 0.85
+                        if cost < best[0] - 1e-9:
+                            best = (cost, per, head_split, True)
                 if per >= pages_seq or per * wide >= 64:
                     break
                 per *= 2
-        return page * best[1], best[2]
+        return page * best[1], best[2], best[3]
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
         """The most chunks of ``split`` keys that a token's keys can touch."""

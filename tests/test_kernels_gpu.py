@@ -653,6 +653,44 @@ def test_attn_decode(nh, nkv, hd, window, split):
     assert K().attn_decode_status() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 64), (16, 2, 64), (32, 2, 128), (12, 4, 128), (9, 1, 64), (36, 36, 64)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("split", [256, 1024])
+def test_attn_decode_merges_in_the_block(nh, nkv, hd, window, split):
+    """A block per (token, group of heads) whose warps take the item's chunks and merge them in shared memory:
+    sequences with one to four chunks (and a token whose window ends inside a chunk), with and without the query
+    heads of a kv head cut into groups, against the reference and against the merge through global memory."""
+    lens = [1000, 64, 1, 700, 257, 256, 513, 1024, 769]
+    new = [1, 1, 1, 2, 1, 1, 1, 1, 1]
+    case = PagedCase(lens=lens, new=new, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    scale = 0.7 / math.sqrt(hd)
+    n = (max(lens) + split - 1) // split
+    if window > 0:
+        n = min(n, (window + split - 2) // split + 1)
+    assert n <= 4
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    want = case.reference(window, scale)
+    through_memory = torch.full_like(q, 7.0)
+    K().attn_decode(q, q.stride(0), through_memory, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                    nh, nkv, hd, 64, window, scale, split, n, scratch)
+    for parts in (1, 2, 4):
+        if (nh // nkv) % parts:
+            continue
+        for _ in range(2):
+            out = torch.full_like(q, 7.0)
+            K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                            nh, nkv, hd, 64, window, scale, split, n, None, head_split=parts, in_block=True)
+            close(out, want, 1e-2, f"attn_decode, merged in the block, {parts} groups per kv head")
+            close(out, through_memory.double(), 1e-2, "the two ways of merging")
+    assert K().attn_decode_status() == 0
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    with pytest.raises(KernelLibraryError, match="at most 4 chunks"):
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, 0, scale, 64, 16, None, in_block=True)
+
+
 @pytest.mark.parametrize("hd", [64, 128])
 def test_attn_decode_many_items_per_warp(hd):
     # more work items than the grid has warps: every warp's ring of pages runs across the ends of items,
