@@ -381,6 +381,12 @@ def main() -> int:
         # the other contexts the baseline's table names
         for b, c in ((1, 128), (8, 128), (1, 2048), (8, 2048), (64, 2048)):
             point(f"decode_b{b}_ctx{c}", rig.decode_point(f"2B b{b} ctx {c}", b, c, min(st, c - 16), 3, hbm_gbs))
+        # longer contexts: a prompt of 8,192 tokens, and decoding at 16,384 tokens (the cache is then 0.9 of the bytes)
+        if big * C >= 8 * 16384 + 8192:
+            point("decode_b8_ctx16384", rig.decode_point("2B b8 ctx 16384", 8, 16384, 16, 3, hbm_gbs, repeats=1))
+            ms_long = rig.prefill(8192, repeats=2, warm=1)
+            point("prefill_8192", (8192 / (ms_long / 1e3),
+                                   rig.prefill_flops([8192]) / (ms_long / 1e3) / 1e12 / bf16_tf))
     layers_run, layers_full = rig.layers, rig.layers_full
     del engine, model
     rig.close()
