@@ -88,6 +88,7 @@ int exl3_gemm_skinny(const void* x, const void* w, const void* bias, void* y, in
 int exl3_gemm_skinny_status();
 int exl3_gemm_skinny_max_rows();
 int exl3_gemm_skinny_split(int N, int K);
+int exl3_gemm_skinny_max_clusters(int s);
 
 // Projections of many rows with two blocks of a cluster as one tensor core (tcgen05.mma.cta_group::2, tiles of
 // 256 x 256): input and epilogues as exl3_gemm_skinny's (0 plain, 1 gated, 2 residual and the next norm's pieces),

@@ -426,11 +426,23 @@ static int sk_map(CUtensorMap* out, const void* p, int64_t rows, int K, int box)
 // costs its full length), at most 8 and at least two 64-wide steps per block.  Measured at 2304 x 2304 ... 11520 x
 // 2304 with 8 and 64 rows: 5 cuts for 54 tiles, 3 for 90, 8 for 18.  From N and K only, so that a result never
 // depends on the batch.
+// Clusters of s blocks that run at once with two blocks to an SM.  A cluster's blocks must find their SMs in one
+// of the GPU's parts, of which a B200 has eight of 18 or 19 SMs (36 places for blocks): 32 clusters of 8 run at
+// once and 36 do not (4608 x 4096 at 64 rows: 16.2 us in 8 cuts, 11.4 us in 7), 54 clusters of 5 do, 90 of 3 do.
+// From the SM count only: the answer must not depend on the batch, or a row's result would depend on its batch.
+static int sk_max_clusters(int s) {
+  if (s < 1) return 0;
+  const int per_part = 2 * (sk_sm_count() / 8);
+  return 8 * (per_part / s);
+}
+
 static int sk_auto_split(int N, int K) {
   const int n_tiles = ceil_div(N, SK_BM), ksteps = ceil_div(K, SK_BK);
   int s = 2 * sk_sm_count() / n_tiles;
   if (s > SK_MAX_SPLIT) s = SK_MAX_SPLIT;
   while (s > 1 && ksteps / s < 2) --s;
+  // fewer cuts when the tiles' clusters would not all run at once (a second round of clusters costs its full length)
+  while (s > 1 && n_tiles > sk_max_clusters(s)) --s;
   return s < 1 ? 1 : s;
 }
 
@@ -481,6 +493,9 @@ extern "C" int exl3_gemm_skinny_status() {
 }
 
 extern "C" int exl3_gemm_skinny_max_rows() { return SK_MAX_ROWS; }
+
+// Clusters of s blocks that run at once (two blocks an SM): what the choice of cuts rests on.
+extern "C" int exl3_gemm_skinny_max_clusters(int s) { return sk_max_clusters(s); }
 
 // The split that split = 0 chooses for a weight matrix [N, K].
 extern "C" int exl3_gemm_skinny_split(int N, int K) { return sk_auto_split(N, K); }
