@@ -203,8 +203,12 @@ class Rig:
                 best = (rate, gbs / hbm_gbs)
         return best
 
-    def prefill(self, tokens, repeats=3, warm=2):
-        """Milliseconds of one step with one prompt of ``tokens`` tokens (best repeat; each is printed)."""
+    def prefill(self, tokens, repeats=4, warm=3):
+        """Milliseconds of one step with one prompt of ``tokens`` tokens (best repeat; each is printed).  Every
+        other timed step starts after a quarter of a second of idling: back to back the steps of the larger sizes
+        run into the power cap and each is slower than the one before, after idling the clocks of the smaller
+        sizes' short step have to come up again; the burst rate they are compared with was measured on a kernel
+        in isolation."""
         torch, E, eng = self.torch, self.E, self.engine
         toks = self.prompts(1, tokens)[0]
         times = []
@@ -212,6 +216,8 @@ class Rig:
             s = eng.open()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            if i >= warm and (i - warm) % 2 == 1:
+                time.sleep(0.25)
             e0.record()
             eng.step([E.StepEntry(s, toks, "last")])
             e1.record()
