@@ -395,7 +395,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
   // ---- merging the chunks of a (token, kv head): the same sums in chunk order, whoever does it --
   // HG query heads of the group side by side, 32 / HG lanes each: the warp waits for memory once for all the
-  // chunks' maxima and sums and once per MB chunks of accumulators, however many heads the group has.
+  // chunks' maxima and sums together with the first MB chunks of accumulators, and once per MB chunks after
+  // them, however many heads the group has.
   auto merge_heads = [&](auto hg_c, int mt, int mg, int n0) {
     constexpr int HG = decltype(hg_c)::value;
     constexpr int LPH = 32 / HG;                         // lanes of a head
@@ -408,14 +409,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const int heads = min(HG, G - n0);
     const float* base = scratch + ((int64_t)mt * nh + mg * G + n0) * max_splits * rec;   // a head's records: max_splits of them
     const int n_pairs = heads * n_rec;
+    const int nn = lane / LPH, lih = lane % LPH;
+    const float* hb = base + (int64_t)nn * max_splits * rec;
+    float2 v[MB][F2];
+    auto ask = [&](int s0) {                             // the accumulators of chunks s0 .. s0 + MB - 1
+#pragma unroll
+      for (int u = 0; u < MB; ++u) {
+        const float2* r = reinterpret_cast<const float2*>(hb + (int64_t)(s0 + u) * rec);
+        const bool in = nn < heads && s0 + u < n_rec;
+#pragma unroll
+        for (int i = 0; i < F2; ++i) v[u][i] = in ? __ldcg(r + i * LPH + lih) : make_float2(0.0f, 0.0f);
+      }
+    };
     for (int p = lane; p < n_pairs; p += 32) {
       const int n = p / n_rec, s2 = p - n * n_rec;
       const float* r = base + ((int64_t)n * max_splits + s2) * rec + HD;
       wv[p] = __ldcg(r);
       lv[p] = __ldcg(r + 1);
     }
+    ask(0);                                              // on their way while the weights are worked out
     __syncwarp();
-    const int nn = lane / LPH, lih = lane % LPH;
     float my_ll = 1.0f;
 #pragma unroll
     for (int n = 0; n < HG; ++n) {
@@ -435,20 +448,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
     __syncwarp();
     if (nn < heads) {
-      const float* hb = base + (int64_t)nn * max_splits * rec;
       const float* wn = wv + nn * n_rec;
       float acc[DPL];
 #pragma unroll
       for (int e = 0; e < DPL; ++e) acc[e] = 0.0f;
       for (int s0 = 0; s0 < n_rec; s0 += MB) {
-        float2 v[MB][F2];
-#pragma unroll
-        for (int u = 0; u < MB; ++u) {
-          const float2* r = reinterpret_cast<const float2*>(hb + (int64_t)(s0 + u) * rec);
-          const bool in = s0 + u < n_rec;
-#pragma unroll
-          for (int i = 0; i < F2; ++i) v[u][i] = in ? __ldcg(r + i * LPH + lih) : make_float2(0.0f, 0.0f);
-        }
+        if (s0 > 0) ask(s0);
 #pragma unroll
         for (int u = 0; u < MB; ++u) {
           const float w = s0 + u < n_rec ? wn[s0 + u] : 0.0f;

@@ -205,10 +205,14 @@ class Attention:
         number of chunks each, as many pieces as there are warps (one token of 32 query heads of 128 on 2 kv heads
         at 2,048 tokens: 16 groups of 16 chunks take 13 us, one group of 8 chunks 33 us), one chunk wins for short
         contexts and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks
-        only where they are needed to give every SM work.  A block per item costs its walk (a quarter of the keys per
-        warp) plus 1.5 us for the merge in shared memory, one round of blocks per SM count; it is taken when that is
-        0.85 of the other way's cost or less: for about as many items as the GPU has SMs, each too long for one warp
-        (64 sequences of 2 kv heads with 16 query heads of 128 each at 2,048 tokens: 33 against 43 us).  The choice
+        only where they are needed to give every SM work.  A block per item costs, for every round of as many
+        blocks as the GPU has SMs, 5.5 us (start and the merge in shared memory) and its walk (a quarter of the keys
+        per warp), and not less than the memory's time, which its rounds stream some 5 % faster at the price of
+        1.5 us between rounds; it is taken when that is below 0.95 of the other way's cost: for up to about as many
+        items as the GPU has SMs, each too long for one warp (64 sequences of 2 kv heads with 16 query heads of 128
+        each at 2,048 tokens: 33 against 47 us; four sequences of 36 heads at 4,096 tokens: 30 against 33 us), and
+        for several rounds of long items (eight sequences of 36 heads at 16,384 tokens: 181 against 191 us), not
+        for many rounds of short ones (64 sequences of 36 heads at 512 tokens: 123 against 58 us).  The choice
         depends on the step's size, not on a token's position: results differ between batch sizes by rounding."""
         s = self.spec
         keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
@@ -217,7 +221,8 @@ class Attention:
         group = s.heads // s.kv_heads
         sms = K.sm_count(device)
         warps = 4 * sms
-        best = None
+        best = None                                          # warps share all chunks
+        best_blk = None                                      # a block per item
         for head_split in (1, 2, 4, 8, 16):
             if group % head_split:
                 continue
@@ -240,12 +245,15 @@ class Attention:
                         best = (cost, per, head_split, False)
                     if 1 < n + (1 if s.window > 0 else 0) <= 4:
                         rounds = (groups + sms - 1) // sms
-                        cost = (4.0 + max(rounds * per * wide * stage_us, once_us, again_us) + 1.5) / 0.85
-                        if cost < best[0] - 1e-9:
-                            best = (cost, per, head_split, True)
+                        cost = max(rounds * (5.5 + per * wide * stage_us),
+                                   5.5 + max(once_us, again_us) / 1.05 + 1.5 * (rounds - 1))
+                        if best_blk is None or cost < best_blk[0] - 1e-9:
+                            best_blk = (cost, per, head_split, True)
                 if per >= pages_seq or per * wide >= 64:
                     break
                 per *= 2
+        if best_blk is not None and best_blk[0] < 0.95 * best[0]:
+            best = best_blk
         return page * best[1], best[2], best[3]
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
