@@ -57,8 +57,8 @@ size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_splits);
 
 size_t exl3_argmax_scratch_bytes(int R, int V);
 // Whole prompts on tcgen05 tensor cores with TMA loads from the paged cache (bfloat16, heads of 64 or 128, pages
-// of 64, tiles of 128 queries); variant 0: chosen by the number of blocks, 1: two blocks an SM, 2: four (heads of 64);
-// see attention_prefill_tc.cu.
+// of 64, tiles of 128 queries); variant 0: chosen by the number of blocks, 1: a tile a block, 2: four blocks an SM
+// (heads of 64), 3: two tiles a block (the first of the list with the last, and so on); see attention_prefill_tc.cu.
 int exl3_attn_prefill_tc_supported(int dtype, int hd, int page);
 int exl3_attn_prefill_tc_status();
 int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,

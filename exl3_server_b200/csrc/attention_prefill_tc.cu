@@ -6,12 +6,20 @@
 // 576-578).  A block owns 128 consecutive queries of one sequence and one head
 // and walks the key pages its queries may see:
 //
-//   warp 4     issues everything asynchronous: TMA copies of the Q tile and of
-//              K and V pages (straight from the paged cache, 128B-swizzled),
-//              S = Q K^T and O += P V as tcgen05.mma with accumulators in tensor
-//              memory (two S buffers of 64 columns, O in head_dim columns, two P buffers
-//              of 32); a head of 128 is two boxes of 64 features for every copy, two
-//              groups of four instructions for S and two halves of O
+//   warp 5     TMA copies of the Q tile and of K and V pages (straight from the paged
+//              cache, 128B-swizzled) into a ring of stages, each as soon as the products
+//              that read the stage's page before are done, and S = Q K^T as tcgen05.mma
+//              into one of two S buffers of 64 columns in tensor memory, up to two pages
+//              ahead of the softmax
+//   warp 4     O += P V as tcgen05.mma (P read from tensor memory, two buffers of 32
+//              columns; O in head_dim columns) as soon as a P is handed over.
+//              A head of 128 is two boxes of 64 features for every copy, two groups of
+//              four instructions for S and two halves of O.  An instruction of 64 columns
+//              holds its issuing thread for some 49 cycles when the SM's other block issues
+//              none (measured: 47 cycles at least whatever the width, 64.5 at 128 columns,
+//              128 at 256), about 100 when it does, and a wait on an mbarrier that is
+//              already complete another 100: with one warp for everything a page's sixteen
+//              issues and waits took as long as its softmax, and each waited for the other.
 //   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It reads its row
 //              of S with tcgen05.ld (no shuffles: the whole row is in its
 //              registers), masks, takes 2^(s * scale - m) with one multiply-add
@@ -34,15 +42,16 @@
 namespace exl3 {
 
 constexpr int FA_BQ = 128, FA_BK = 64;
-constexpr int FA_THREADS = 160;
-constexpr int FA_KV_STAGES = 5;
+constexpr int FA_THREADS = 160;                              // the four-blocks-an-SM kernel: softmax warps and one issuer
+constexpr int FA_THREADS_MAIN = 192;                         // the kernel below: softmax warps, an MMA warp, a copy warp
+constexpr int FA_KV_STAGES = 4;
 // Tensor memory columns: S0 (64) | S1 (64) | O (head_dim) | P0 (32) | P1 (32); an allocation is a power of two.
 __host__ __device__ constexpr int fa_tmem_cols(int hd) { return hd == 64 ? 256 : 512; }
 __host__ __device__ constexpr uint32_t fa_q_bytes(int hd) { return FA_BQ * hd * 2; }
 __host__ __device__ constexpr uint32_t fa_kv_bytes(int hd) { return FA_BK * hd * 2; }
-__host__ __device__ constexpr uint32_t fa_smem(int hd) { return fa_q_bytes(hd) + 2 * FA_KV_STAGES * fa_kv_bytes(hd) + 1024 + 256; }
+__host__ __device__ constexpr uint32_t fa_smem(int hd) { return 2 * fa_q_bytes(hd) + 2 * FA_KV_STAGES * fa_kv_bytes(hd) + 1024 + 256; }
 constexpr uint32_t FA_QBOX_BYTES = FA_BQ * 128, FA_KVBOX_BYTES = FA_BK * 128;   // a box of 64 features
-constexpr uint32_t FA_WAIT_LIMIT = 1u << 24;   // polls of a few tens of cycles: a fraction of a second
+constexpr uint64_t FA_WAIT_NS = 250000000ull;     // a wait gives up after a quarter of a second
 constexpr float FA_RESCALE_STEP = 8.0f;           // in base-2 units
 
 static __device__ int g_fa_error = 0;
@@ -57,18 +66,36 @@ __device__ inline void fa_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ inline void fa_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem_u32(bar)) : "memory");
 }
+// A bounded wait.  mbarrier.try_wait lets the hardware suspend the thread until the phase completes or a time
+// limit of the system's runs out, so a waiting warp takes no issue slots from the warps that compute (with
+// test_wait in a loop the two waiting warps of a block took every second or third slot of their schedulers and
+// a softmax warp stood some hundred cycles between any two of its instructions' groups).  After a try that ran
+// out the loop looks at the clock and gives up FA_WAIT_NS after it began.
 __device__ inline bool fa_mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = fa_smem_u32(bar);
-  for (uint32_t i = 0; i < FA_WAIT_LIMIT; ++i) {
+  uint64_t t0 = 0;
+  for (;;) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
+    uint64_t now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (t0 == 0) t0 = now;
+    else if (now - t0 > FA_WAIT_NS) return false;
   }
-  return false;
+}
+__device__ inline bool fa_mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(fa_smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
 }
 __device__ inline void fa_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
@@ -139,24 +166,54 @@ __device__ inline uint32_t fa_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// What a block needs to know of a tile of 128 queries.
+struct FaTile {
+  int row0;        // the tile's first row of q and out
+  int rows;        // its queries
+  int p_first, p_last;   // their positions
+  int page_lo;     // the first page they may see
+  int n_pages;     // pages to walk
+  const int* bt;   // the sequence's page table
+};
+__device__ inline FaTile fa_tile(int tile, const int* block_table, int bt_stride, const int* row_start,
+                                 const int* row_pos0, const int* tile_seq, const int* tile_q0, int window) {
+  FaTile t;
+  const int b = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = row_start[b + 1] - row_start[b];
+  t.row0 = row_start[b] + q0;
+  t.rows = min(FA_BQ, n_new - q0);
+  t.p_first = row_pos0[b] + q0;
+  t.p_last = t.p_first + t.rows - 1;
+  const int k_lo = (window > 0 && t.p_first - window + 1 > 0) ? t.p_first - window + 1 : 0;
+  t.page_lo = k_lo / FA_BK;
+  t.n_pages = t.p_last / FA_BK - t.page_lo + 1;
+  t.bt = block_table + (int64_t)b * bt_stride;
+  return t;
+}
+
+// fold = 0: block (head, y) owns tile y.  fold = 1: it owns tiles y and n_tiles - 1 - y of the caller's list
+// (heaviest first), one after the other, so that all blocks have about the same number of pages to walk; the
+// pages of both run through the same rings and buffers as one sequence of pages, the second tile's Q in a buffer
+// of its own from the start, its first S products issued while the first tile's last softmax and epilogue run.
 template <int FA_HD>
-__global__ void __launch_bounds__(FA_THREADS, FA_HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(FA_THREADS_MAIN, FA_HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                        const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
-                       const int* __restrict__ tile_q0, int nh, int nkv, int window, float scale_log2) {
+                       const int* __restrict__ tile_q0, int n_tiles, int fold, int nh, int nkv, int window,
+                       float scale_log2) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int NB = FA_HD / 64;                             // boxes of 64 features (128-byte lines) in a head
   constexpr uint32_t FA_Q_BYTES = fa_q_bytes(FA_HD), FA_KV_BYTES = fa_kv_bytes(FA_HD);
   constexpr int FA_TMEM_COLS = fa_tmem_cols(FA_HD);
-  unsigned char* sQ = base;                                  // [boxes][128][64] bf16
-  unsigned char* sK = sQ + FA_Q_BYTES;                       // [stages][boxes][64][64]
+  unsigned char* sQ = base;                                  // [2 tiles][boxes][128][64] bf16
+  unsigned char* sK = sQ + 2 * FA_Q_BYTES;                   // [stages][boxes][64][64]
   unsigned char* sV = sK + FA_KV_STAGES * FA_KV_BYTES;       // [stages][boxes][64][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + FA_KV_STAGES * FA_KV_BYTES);
-  uint64_t* q_full = bars;                        // Q tile landed
-  uint64_t* kv_full = bars + 1;                   // [stages] K and V page landed
+  uint64_t* q_full = bars;                        // [2] Q tile landed
+  uint64_t* kv_full = bars + 2;                   // [stages] K and V page landed
   uint64_t* kv_free = kv_full + FA_KV_STAGES;     // [stages] the products that read the stage are done
   uint64_t* s_full = kv_free + FA_KV_STAGES;      // [2] S buffer written by the tensor core
   uint64_t* s_free = s_full + 2;                  // [2] S buffer read by all 128 softmax threads
@@ -166,20 +223,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the caller lists the tiles with the most keys to visit first
-  const int head = blockIdx.x, tile = blockIdx.y;   // blocks start in this order: all heads of tile 0, then tile 1, ...
-  const int b = tile_seq[tile], q0 = tile_q0[tile];
-  const int n_new = row_start[b + 1] - row_start[b];
-  const int pos0 = row_pos0[b];
+  const int head = blockIdx.x;                      // blocks start in this order: all heads of y = 0, then y = 1, ...
   const int g = head / (nh / nkv);
-  const int rows = min(FA_BQ, n_new - q0);
-  const int p_first = pos0 + q0, p_last = pos0 + q0 + rows - 1;
-  const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-  const int page_lo = k_lo / FA_BK, page_hi = p_last / FA_BK;
-  const int n_blocks = page_hi - page_lo + 1;
-  const int* bt = block_table + (int64_t)b * bt_stride;
+  const int other = n_tiles - 1 - (int)blockIdx.y;
+  const int n_own = (fold && other > (int)blockIdx.y) ? 2 : 1;
+  auto tile_of = [&](int w) {                       // the block's first (w = 0) or second tile
+    return fa_tile(w ? other : (int)blockIdx.y, block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, window);
+  };
 
   if (threadIdx.x == 0) {
     fa_mbar_init(q_full, 1);
+    fa_mbar_init(q_full + 1, 1);
     for (int i = 0; i < FA_KV_STAGES; ++i) {
       fa_mbar_init(kv_full + i, 1);
       fa_mbar_init(kv_free + i, 1);
@@ -209,16 +263,61 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   bool ok = true;
 
   if (warp == 4) {
-    // ---- issuer: TMA and MMA -----------------------------------------------------------
-    if (lane == 0) {
-      fa_mbar_expect_tx(q_full, FA_Q_BYTES);
+    // ---- second product: O += P_f V_f as soon as the softmax threads hand P_f over -------
+    const int n0 = tile_of(0).n_pages;
+    const int n_total = n0 + (n_own == 2 ? tile_of(1).n_pages : 0);   // the block's pages, numbered through both tiles
+    for (int f = 0; f < n_total && ok; ++f) {
+      const int sb = f & 1;
+      if (!fa_mbar_wait(p_full + sb, (f >> 1) & 1)) { ok = false; break; }
+      fa_fence_after();
+      if (lane == 0) {
+        const int st = f % FA_KV_STAGES;
+        // a tile's first product starts O afresh (the softmax threads hand over P only after they have read
+        // the tile before out of O)
+        const bool first = f == 0 || f == n0;
 #pragma unroll
-      for (int x = 0; x < NB; ++x)
-        fa_tma_2d(sQ + x * FA_QBOX_BYTES, &map_q, q_full, head * FA_HD + 64 * x, row_start[b] + q0);
+        for (int x = 0; x < NB; ++x) {                       // 64 features of O at a time
+          const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
+#pragma unroll
+          for (int k = 0; k < FA_BK / 16; ++k)              // 16 keys: 8 columns of P, 16 rows of V
+            fa_umma_ts(tmem_o + 64 * x, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (!first || k > 0) ? 1u : 0u);
+        }
+        fa_commit(pv_done + sb);
+        fa_commit(kv_free + st);
+      }
+      __syncwarp();
     }
-    auto load_kv = [&](int j) {                             // page j of this block's walk -> stage j % 3
-      const int st = j % FA_KV_STAGES;
-      const int pg = bt[page_lo + j];
+    if (!ok && lane == 0) atomicExch(&g_fa_error, 1);
+  } else if (warp == 5) {
+    // ---- copies and the first product ------------------------------------------------------
+    // The Q tiles, then K and V page after page as stages come free, and S_f = Q K_f^T as soon as page f has
+    // landed and the softmax threads have read S_(f-2) out of the buffer: up to two pages ahead of the softmax,
+    // whatever the other product's warp is waiting for.  Page numbers come 32 at a time, lane i holding the
+    // number of page c0 + i of the block's walk, a batch ahead (a page number's trip from memory is in no
+    // page's chain of issues).
+    const FaTile ta = tile_of(0), tb = n_own == 2 ? tile_of(1) : ta;
+    const int n0 = ta.n_pages;
+    const int n_total = n0 + (n_own == 2 ? tb.n_pages : 0);
+    if (lane == 0) {
+      for (int w = 0; w < n_own; ++w) {
+        fa_mbar_expect_tx(q_full + w, FA_Q_BYTES);
+#pragma unroll
+        for (int x = 0; x < NB; ++x)
+          fa_tma_2d(sQ + w * FA_Q_BYTES + x * FA_QBOX_BYTES, &map_q, q_full + w, head * FA_HD + 64 * x, w ? tb.row0 : ta.row0);
+      }
+    }
+    auto numbers = [&](int c0) {                             // this lane's page number of the 32 from c0
+      const int c = c0 + lane;
+      if (c >= n_total) return 0;
+      return c >= n0 ? tb.bt[tb.page_lo + c - n0] : ta.bt[ta.page_lo + c];
+    };
+    int pgs = numbers(0), pgs_next = numbers(32);
+    int copied = 0;                                          // pages whose copies were asked for
+    auto copy_next = [&]() {                                 // its stage is known to be free
+      const int c = copied++;
+      if ((c & 31) == 0 && c > 0) { pgs = pgs_next; pgs_next = numbers(c + 32); }
+      const int st = c % FA_KV_STAGES;
+      const int pg = __shfl_sync(0xffffffffu, pgs, c & 31);
       if (lane == 0) {
         fa_mbar_expect_tx(kv_full + st, 2 * FA_KV_BYTES);
 #pragma unroll
@@ -227,13 +326,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           fa_tma_2d(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES, &map_v, kv_full + st, 64 * x, (pg * nkv + g) * FA_BK);
         }
       }
+      __syncwarp();
     };
-    auto issue_s = [&](int j) {                             // S[j & 1] = Q K_j^T
-      const int sb = j & 1, st = j % FA_KV_STAGES;
+    int q_seen = 0;                                          // Q tiles known to have landed
+    for (int f = 0; f < n_total && ok; ++f) {
+      // every copy whose stage is free, without waiting for one that is not; page f itself at any rate
+      while (copied < n_total &&
+             (copied < FA_KV_STAGES ||
+              fa_mbar_test(kv_free + copied % FA_KV_STAGES, ((copied - FA_KV_STAGES) / FA_KV_STAGES) & 1)))
+        copy_next();
+      while (copied <= f && ok) {
+        if (!fa_mbar_wait(kv_free + copied % FA_KV_STAGES, ((copied - FA_KV_STAGES) / FA_KV_STAGES) & 1)) { ok = false; break; }
+        copy_next();
+      }
+      if (!ok) break;
+      const int sb = f & 1, st = f % FA_KV_STAGES;
+      const int w = f >= n0 ? 1 : 0;
+      if (q_seen <= w) {
+        if (!fa_mbar_wait(q_full + w, 0)) { ok = false; break; }
+        q_seen = w + 1;
+      }
+      if (!fa_mbar_wait(kv_full + st, (f / FA_KV_STAGES) & 1)) { ok = false; break; }
+      if (f >= 2 && !fa_mbar_wait(s_free + sb, ((f >> 1) - 1) & 1)) { ok = false; break; }
+      fa_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int x = 0; x < NB; ++x) {                       // 64 features of the sum at a time
-          const uint64_t da = fa_desc(fa_smem_u32(sQ + x * FA_QBOX_BYTES));
+          const uint64_t da = fa_desc(fa_smem_u32(sQ + w * FA_Q_BYTES + x * FA_QBOX_BYTES));
           const uint64_t db = fa_desc(fa_smem_u32(sK + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
 #pragma unroll
           for (int k = 0; k < 4; ++k) fa_umma(tmem_base + sb * 64, da + 2 * k, db + 2 * k, FA_IDESC_S, (x | k) > 0);
@@ -241,66 +360,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         fa_commit(s_full + sb);
       }
       __syncwarp();
-    };
-    int loaded = 0;                                          // pages whose copies were started
-    for (; loaded < FA_KV_STAGES && loaded < n_blocks; ++loaded) load_kv(loaded);
-    ok = fa_mbar_wait(q_full, 0) && fa_mbar_wait(kv_full + 0, 0);
-    if (ok) { fa_fence_after(); issue_s(0); }
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int sb = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      // S of the next page while the softmax of this one runs
-      if (j + 1 < n_blocks) {
-        if (!fa_mbar_wait(kv_full + (j + 1) % FA_KV_STAGES, ((j + 1) / FA_KV_STAGES) & 1)) { ok = false; break; }
-        if (j + 1 >= 2 && !fa_mbar_wait(s_free + (sb ^ 1), (((j + 1) >> 1) - 1) & 1)) { ok = false; break; }
-        fa_fence_after();
-        issue_s(j + 1);
-      }
-      // O += P_j V_j
-      if (!fa_mbar_wait(p_full + sb, ph)) { ok = false; break; }
-      fa_fence_after();
-      if (lane == 0) {
-        const int st = j % FA_KV_STAGES;
-#pragma unroll
-        for (int x = 0; x < NB; ++x) {                       // 64 features of O at a time
-          const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
-#pragma unroll
-          for (int k = 0; k < FA_BK / 16; ++k)              // 16 keys: 8 columns of P, 16 rows of V
-            fa_umma_ts(tmem_o + 64 * x, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
-        }
-        fa_commit(pv_done + sb);
-        fa_commit(kv_free + st);
-      }
-      __syncwarp();
-      // Refill, off the critical path: the stage of page j - 1 was released a whole softmax
-      // ago, so this wait is over at once; waiting for page j's own products here would put
-      // the tensor core's latency into every iteration.
-      if (j >= 1 && loaded < n_blocks && loaded - FA_KV_STAGES <= j - 1) {
-        const int f = loaded - FA_KV_STAGES;                 // the page whose stage is reused
-        if (!fa_mbar_wait(kv_free + f % FA_KV_STAGES, (f / FA_KV_STAGES) & 1)) { ok = false; break; }
-        load_kv(loaded++);
-      }
     }
     if (!ok) {
-      // copies still in flight must land before the block's shared memory goes away
-      for (int j = max(0, loaded - FA_KV_STAGES); j < loaded; ++j)
-        fa_mbar_wait(kv_full + j % FA_KV_STAGES, (j / FA_KV_STAGES) & 1);
+      // a wait ran out: say so; the copies already asked for must land before the block's shared memory goes
+      // away (when all is well every one of them has been waited for above)
+      for (int u = max(0, copied - FA_KV_STAGES); u < copied; ++u)
+        fa_mbar_wait(kv_full + u % FA_KV_STAGES, (u / FA_KV_STAGES) & 1);
+      for (int w = q_seen; w < n_own; ++w) fa_mbar_wait(q_full + w, 0);
+      if (lane == 0) atomicExch(&g_fa_error, 3);
     }
-    if (!ok && lane == 0) atomicExch(&g_fa_error, 1);
   } else {
     // ---- softmax and epilogue: thread r = query row r = TMEM lane r ---------------------
     const int r = threadIdx.x;                               // 0..127
-    const int p = p_first + r;                               // this row's position
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    int fb = 0;                                              // a tile's first page in the block's numbering
+    for (int w = 0; w < n_own && ok; ++w) {
+    const FaTile tw = tile_of(w);
+    const int p_first = tw.p_first, p_last = tw.p_last, n_blocks = tw.n_pages, page_lo = tw.page_lo, rows = tw.rows;
+    const int p = p_first + r;                               // this row's position
     float m_used = -INFINITY, l_run = 0.0f;
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!fa_mbar_wait(s_full + st, ph)) { ok = false; break; }
+    // The row of S_f is asked for as soon as the row of P_(f-1) is on its way into tensor memory (the first of a
+    // tile: here), so that the load's latency and the store's pass together.
+    uint32_t sr[2][32];
+    auto ask_s = [&](int f) -> bool {
+      const int st = f & 1;
+      if (!fa_mbar_wait(s_full + st, (f >> 1) & 1)) return false;
       fa_fence_after();
-      uint32_t sr[2][32];
       fa_ld32(tmem_base + lane_addr + st * 64, sr[0]);
       fa_ld32(tmem_base + lane_addr + st * 64 + 32, sr[1]);
+      return true;
+    };
+    ok = ask_s(fb);
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int f = fb + j;
+      const int st = f & 1;
       fa_wait_ld();
       fa_fence_before();
       fa_mbar_arrive(s_free + st);
@@ -334,7 +427,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float corr = (m_used == -INFINITY) ? 0.0f : fa_exp2(m_used - m_new);   // 1 for rows that keep theirs
         if (j > 0) {
           // every earlier product must have landed in O before it is rewritten
-          if (!fa_mbar_wait(pv_done + (st ^ 1), ((j - 1) >> 1) & 1)) { ok = false; break; }
+          if (!fa_mbar_wait(pv_done + (st ^ 1), ((f - 1) >> 1) & 1)) { ok = false; break; }
           fa_fence_after();
 #pragma unroll
           for (int h2 = 0; h2 < FA_HD / 64; ++h2) {          // 64 columns at a time
@@ -357,7 +450,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
       // the P buffer of two pages ago must have been consumed
-      if (j >= 2 && !fa_mbar_wait(pv_done + st, ((j - 2) >> 1) & 1)) { ok = false; break; }
+      if (f >= 2 && !fa_mbar_wait(pv_done + st, ((f - 2) >> 1) & 1)) { ok = false; break; }
       uint32_t pw[32];
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -370,18 +463,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run += sum;
       fa_st32(tmem_p + lane_addr + st * 32, pw);
+      if (j + 1 < n_blocks && !ask_s(f + 1)) ok = false;   // the tile's next row of S while P is being stored
       fa_wait_st();
       fa_fence_before();
       fa_mbar_arrive(p_full + st);
     }
     if (ok) {
       // last product done -> O complete
-      const int jl = n_blocks - 1;
-      ok = fa_mbar_wait(pv_done + (jl & 1), (jl >> 1) & 1);
+      const int fl = fb + n_blocks - 1;
+      ok = fa_mbar_wait(pv_done + (fl & 1), (fl >> 1) & 1);
       if (ok) {
         fa_fence_after();
         const float inv = 1.0f / l_run;
-        __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * FA_HD;
+        __nv_bfloat16* dst = out + ((int64_t)(tw.row0 + r) * nh + head) * FA_HD;
 #pragma unroll
         for (int h2 = 0; h2 < FA_HD / 64; ++h2) {            // 64 columns at a time (every thread reads: the load is the warp's)
           uint32_t o[2][32];
@@ -391,18 +485,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (r < rows) {
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
-              uint4 w;
+              uint4 wd;
               const int c = ch * 8;
-              w.x = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 0]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
-              w.y = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
-              w.z = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
-              w.w = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + 64 * h2 + c) = w;
+              wd.x = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 0]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 1]) * inv);
+              wd.y = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 2]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 3]) * inv);
+              wd.z = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 4]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 5]) * inv);
+              wd.w = fa_pack(__uint_as_float(o[c >> 5][(c & 31) + 6]) * inv, __uint_as_float(o[c >> 5][(c & 31) + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + 64 * h2 + c) = wd;
             }
           }
         }
+        fa_fence_before();                                 // O is read: the next tile's first product may write it
       }
     }
+    fb += n_blocks;
+    }
+    if (!ok) fa_wait_ld();                                   // a row of S may still be on its way
     if (!ok && lane == 0) atomicExch(&g_fa_error, 2);
   }
 
@@ -700,8 +798,8 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
     set_error("attn_prefill_tc: needs bfloat16, head_dim 64 or 128 and pages of 64, got head_dim %d page %d", hd, page);
     return ERR_UNSUPPORTED;
   }
-  if (variant < 0 || variant > 2 || (variant == 2 && hd != 64)) {
-    set_error("attn_prefill_tc: variant is 0 (chosen), 1 (two blocks an SM) or 2 (four blocks an SM, heads of 64), got %d", variant);
+  if (variant < 0 || variant > 3 || (variant == 2 && hd != 64)) {
+    set_error("attn_prefill_tc: variant is 0 (chosen), 1 (a tile a block), 2 (four blocks an SM, heads of 64) or 3 (two tiles a block), got %d", variant);
     return ERR_BAD_ARGUMENT;
   }
   if (n_tiles < 0 || T < 1 || nh < 1 || nkv < 1 || nh % nkv != 0 || n_tiles > 65535 || window < 0 || q_row_stride % 8 != 0) {
@@ -734,19 +832,23 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   if (rc) return rc;
   rc = fa_make_map(&map_v, v_pool, n_pool_rows, hd, hd, FA_BK);
   if (rc) return rc;
-  dim3 grid(nh, n_tiles);
-  // four blocks an SM when there are more blocks than that holds at once
-  const bool four = hd == 64 && (variant == 2 || (variant == 0 && (int64_t)n_tiles * nh > 4 * (int64_t)sms));
+  // Four blocks an SM when there are more blocks than that holds at once.  Two tiles a block (the heaviest with
+  // the lightest, and so on) when a tile a block would need a second round of blocks and two tiles a block need
+  // none: then every block walks about the same number of pages and the kernel ends with all of them.
+  const int64_t blocks = (int64_t)n_tiles * nh, at_once = (int64_t)sms * (hd == 64 ? 2 : 1);
+  const bool four = hd == 64 && (variant == 2 || (variant == 0 && blocks > 4 * (int64_t)sms));
+  const int fold = (variant == 3 || (variant == 0 && !four && blocks > at_once && (int64_t)((n_tiles + 1) / 2) * nh <= at_once)) ? 1 : 0;
+  dim3 grid(nh, fold ? (n_tiles + 1) / 2 : n_tiles);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const float scale_log2 = scale * 1.4426950408889634f;
   if (four)
     launch_pdl(attn_prefill_tc4_kernel, grid, dim3(FA_THREADS), F4_SMEM, stream, map_q, map_k, map_v, o, block_table,
                bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
   else if (hd == 64)
-    launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(FA_THREADS), fa_smem(64), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
+    launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(FA_THREADS_MAIN), fa_smem(64), stream, map_q, map_k, map_v, o,
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, scale_log2);
   else
-    launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(FA_THREADS), fa_smem(128), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, scale_log2);
+    launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(FA_THREADS_MAIN), fa_smem(128), stream, map_q, map_k, map_v, o,
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, scale_log2);
   return launch_status("attn_prefill_tc");
 }

@@ -8,7 +8,7 @@ copy.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -62,8 +62,13 @@ class StepBatch:
     workspace: Workspace
     # per tile size (128 queries): (int32 [tiles] batch row, int32 [tiles] first new token, count)
     tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
+    # per tile size, on the host and in the tiles' order: the position after each tile's last query (the keys its
+    # queries may see when no window cuts them)
+    tile_keys: Dict[int, List[int]] = field(default_factory=dict)
     host_slots: List[int] = field(default_factory=list)
     host_new: List[int] = field(default_factory=list)
+    # what a part has worked out for this step and wants to find again in the next layer (keyed as it likes)
+    memo: Dict[Any, Any] = field(default_factory=dict)
 
     @property
     def is_decode(self) -> bool:
@@ -89,6 +94,7 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
     pieces = [tok, pos, seq, np.asarray(slots, np.int64), row_start, np.asarray(starts, np.int64),
               np.asarray(wanted, np.int64)]
     tile_counts = []
+    tile_keys = {}
     for size in QUERY_TILES:
         # the tiles with the most keys to visit come first: the attention kernels start them first, so
         # that the long ones do not run alone at the end
@@ -98,6 +104,7 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
         tile_first = [a for _, _, a in order]
         pieces += [np.asarray(tile_rows, np.int64), np.asarray(tile_first, np.int64)]
         tile_counts.append(len(tile_rows))
+        tile_keys[size] = [k for k, _, _ in order]
     n_fixed = len(pieces)
     widths = []
     for g in tables:
@@ -124,4 +131,5 @@ def pack_step(slots: Sequence[int], starts: Sequence[int], tokens: Sequence[Sequ
         n_tokens=T, n_rows=B, token_ids=view(0), tok_pos=view(1), tok_seq=view(2), slot_ids=view(3),
         row_start=view(4), row_pos0=view(5), want_rows=view(6) if wanted else None, n_wanted=len(wanted),
         block_tables=bts, max_kv_len=max([s + c for s, c in zip(starts, counts)] + [0]),
-        max_new=max(counts + [0]), workspace=workspace, tiles=tiles, host_slots=list(slots), host_new=counts)
+        max_new=max(counts + [0]), workspace=workspace, tiles=tiles, tile_keys=tile_keys, host_slots=list(slots),
+        host_new=counts)

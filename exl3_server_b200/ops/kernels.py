@@ -491,8 +491,9 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                     head_dim: int, page: int, window: int, scale: float, variant: int = 0) -> torch.Tensor:
     """Causal attention of whole prompts on tcgen05 tensor cores (tiles of 128 queries; see
     attention_prefill_tc.cu).  ``k_pool`` / ``v_pool``: one layer's ``[pages, kv_heads, 64, head_dim]``.
-    ``variant``: 0 lets the kernel choose between two and four blocks per SM (heads of 64) by the number of
-    blocks; 1 and 2 force the one or the other (the same numbers either way)."""
+    ``variant``: 0 lets the kernel choose by the number of blocks between a tile a block, four blocks per SM (heads
+    of 64) and two tiles a block (the list's first with its last, and so on: list the tiles with the most keys
+    to visit first); 1, 2 and 3 force one of them (the same numbers every way)."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_prefill_tc: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")

@@ -20,9 +20,9 @@ position step and the CUDA-core attention kernel.
 """
 from __future__ import annotations
 
-import os
-
+import heapq
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -157,9 +157,13 @@ class Attention:
             # prompts, heads of 64 or 128: streaming softmax with both products on tcgen05 tensor cores,
             # TMA loads straight from the paged cache, a block per 128 queries
             tile_seq, tile_q0, n_tiles = batch.tiles[128]
+            key = ("attn_prefill_variant", s.heads, s.head_dim, s.window)
+            variant = batch.memo.get(key)
+            if variant is None:
+                variant = batch.memo[key] = self._prefill_variant(batch.tile_keys.get(128), kv.page_size, qkv.device)
             K.attn_prefill_tc(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0,
                               tile_seq, tile_q0, n_tiles, s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window,
-                              self.scale)
+                              self.scale, variant=variant)
             return
         if self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             # decoded tokens, heads of 64 or 128: pages by TMA, both products on the tensor cores, a warp per chunk
@@ -187,6 +191,45 @@ class Attention:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
         K.attn_tokens(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch)
+
+    def _prefill_variant(self, tile_keys, page: int, device: torch.device) -> int:
+        """Which form of the tensor-core prompt kernel a step's tiles get (``K.attn_prefill_tc``'s ``variant``): a
+        tile a block (1), or two tiles a block, the list's first with its last and so on (3), when that ends
+        sooner; 0 leaves it to the kernel, which then takes four blocks an SM for heads of 64 with more blocks than
+        four per SM.  A block's time is taken as its pages to walk plus two pages' worth for every tile (its start
+        and its end), and the blocks as started in launch order on two slots an SM (heads of 64; one for heads of
+        128), each on the slot that comes free first.  One prompt of 2,048 tokens with 36 heads of 64: two tiles a
+        block 41 us, one 44.5 us; 1,536 tokens: 34.5 against 30 us (the heaviest tile alone is the kernel's
+        length there, and a second tile behind it only adds to it)."""
+        s = self.spec
+        if not tile_keys:
+            return 0
+        sms = K.sm_count(device)
+        slots = sms * (2 if s.head_dim == 64 else 1)
+        n = len(tile_keys)
+        if s.head_dim == 64 and n * s.heads > 4 * sms:
+            return 0
+        size = 128
+        pages = [((min(k, s.window + size) if s.window > 0 else k) + page - 1) // page for k in tile_keys]
+        each = 2                                                # a tile's start and end, in pages
+
+        def makespan(times):
+            if len(times) * s.heads <= slots:
+                return max(times)
+            free = [0] * slots
+            heapq.heapify(free)
+            end = 0
+            for t in times:
+                for _ in range(s.heads):
+                    at = heapq.heappop(free) + t
+                    heapq.heappush(free, at)
+                    end = max(end, at)
+            return end
+
+        one = makespan([p + each for p in pages])
+        half = (n + 1) // 2
+        two = makespan([pages[i] + each + (pages[n - 1 - i] + each if n - 1 - i > i else 0) for i in range(half)])
+        return 3 if two <= one else 1
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
         """``(keys per chunk, head_split, in_block)`` for the tensor-core decode kernel: chunks of whole pages (a

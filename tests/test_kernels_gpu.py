@@ -846,19 +846,20 @@ def test_attn_prefill_tc(nh, nkv, hd, window):
     torch.cuda.synchronize()
     assert K().attn_prefill_tc_status() == 0
     close(out, case.reference(window, scale), 1e-2, "attn_prefill_tc")
-    if hd == 64:
-        # two blocks per SM with two S buffers, or four with one: the same arithmetic in the same order
-        outs = []
-        for variant in (1, 2):
-            o = torch.full_like(out, 3.0)
-            K().attn_prefill_tc(buf, buf.stride(0), o, case.k_pool, case.v_pool, case.table, case.row_start,
-                                case.row_pos0, tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale,
-                                variant=variant)
-            close(o, case.reference(window, scale), 1e-2, f"attn_prefill_tc variant {variant}")
-            outs.append(o)
-        assert torch.equal(outs[0], outs[1])
-        torch.cuda.synchronize()
-        assert K().attn_prefill_tc_status() == 0
+    # a tile a block, four blocks per SM with one S buffer (heads of 64), or two tiles a block (the list's first with
+    # its last, and so on): the same arithmetic in the same order
+    outs = []
+    for variant in ((1, 2, 3) if hd == 64 else (1, 3)):
+        o = torch.full_like(out, 3.0)
+        K().attn_prefill_tc(buf, buf.stride(0), o, case.k_pool, case.v_pool, case.table, case.row_start,
+                            case.row_pos0, tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale,
+                            variant=variant)
+        close(o, case.reference(window, scale), 1e-2, f"attn_prefill_tc variant {variant}")
+        outs.append(o)
+    for o in outs[1:]:
+        assert torch.equal(outs[0], o)
+    torch.cuda.synchronize()
+    assert K().attn_prefill_tc_status() == 0
 
 
 @pytest.mark.parametrize("hd", [64, 128])
@@ -879,7 +880,7 @@ def test_attn_prefill_tc_moves_its_reference_maximum(hd):
     out = torch.empty(T, nh * hd, device=DEV, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(hd)
     tile_seq, tile_q0 = case.tiles(128)
-    for variant in ((1, 2) if hd == 64 else (0,)):
+    for variant in ((1, 2, 3) if hd == 64 else (1, 3)):
         out.fill_(3.0)
         K().attn_prefill_tc(buf, buf.stride(0), out, case.k_pool, case.v_pool, case.table, case.row_start,
                             case.row_pos0, tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, 0, scale,

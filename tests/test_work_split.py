@@ -1,0 +1,81 @@
+"""How the attention part cuts a step's work for its kernels: decisions made on the host from the step's sizes alone,
+so they are checked without a GPU (the number of SMs is given)."""
+from types import SimpleNamespace
+from unittest import mock
+
+import pytest
+import torch
+
+from exl3_server_b200.engine.batch import Workspace, pack_step
+from exl3_server_b200.ops import kernels as K
+from exl3_server_b200.parts.attention import Attention
+
+
+def mixer(heads, kv_heads, head_dim, window=0):
+    a = Attention.__new__(Attention)
+    a.spec = SimpleNamespace(heads=heads, kv_heads=kv_heads, head_dim=head_dim, window=window)
+    return a
+
+
+def tile_keys(lens, size=128):
+    return sorted((min(a + size, n) for n in lens for a in range(0, n, size)), reverse=True)
+
+
+@pytest.fixture(autouse=True)
+def gpu_of_148_sms():
+    with mock.patch.object(K, "sm_count", lambda device: 148):
+        yield
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(36, 36, 64), (16, 2, 64), (32, 8, 128), (32, 2, 128), (6, 3, 80)])
+@pytest.mark.parametrize("window", [0, 700])
+def test_decode_chunks_are_whole_pages_and_groups_divide_the_heads(heads, kv_heads, head_dim, window):
+    a = mixer(heads, kv_heads, head_dim, window)
+    for T in (1, 2, 3, 8, 17, 64, 200):
+        for keys in (1, 63, 64, 65, 500, 2048, 4096, 16384, 100000):
+            split, head_split, in_block = a._decode_split(T, keys, 64, None)
+            assert split >= 64 and split % 64 == 0
+            assert (heads // kv_heads) % head_split == 0 and (heads // kv_heads) // head_split <= 16
+            n = a._chunks(keys, split)
+            assert 1 <= n <= K.ATTN_DECODE_MAX_CHUNKS
+            if in_block:
+                assert 1 < n <= 4
+
+
+def test_decode_choices_at_sizes_that_were_measured():
+    two_b = mixer(36, 36, 64)
+    assert two_b._decode_split(1, 4096, 64, None) == (512, 1, False)     # 8 chunks for each of 36 heads: 288 warps
+    assert two_b._decode_split(8, 4096, 64, None) == (4096, 1, False)    # a warp per (token, head), no merge
+    assert two_b._decode_split(4, 4096, 64, None) == (1024, 1, True)     # 144 blocks, four chunks each
+    assert two_b._decode_split(8, 16384, 64, None) == (4096, 1, True)    # two rounds of long items
+    assert two_b._decode_split(64, 512, 64, None)[2] is False            # sixteen rounds of short ones
+    eight_b = mixer(32, 2, 128)
+    assert eight_b._decode_split(1, 2048, 64, None) == (128, 16, False)  # every query head a group of its own
+    assert eight_b._decode_split(64, 2048, 64, None) == (512, 1, True)
+
+
+def test_prompt_kernel_form():
+    two_b = mixer(36, 36, 64)
+    assert two_b._prefill_variant(tile_keys([2048]), 64, None) == 3      # 576 blocks: two rounds, or one of pairs
+    assert two_b._prefill_variant(tile_keys([1536]), 64, None) == 1      # the heaviest tile is the kernel's length
+    assert two_b._prefill_variant(tile_keys([1024]), 64, None) == 1      # all blocks at once
+    assert two_b._prefill_variant(tile_keys([8192]), 64, None) == 0      # many rounds: the kernel's four-block form
+    assert two_b._prefill_variant([], 64, None) == 0
+    assert mixer(16, 2, 64)._prefill_variant(tile_keys([2048]), 64, None) == 1
+    assert mixer(32, 2, 128)._prefill_variant(tile_keys([2048]), 64, None) in (1, 3)
+    # a window bounds what a tile walks
+    assert mixer(36, 36, 64, window=256)._prefill_variant(tile_keys([2048]), 64, None) in (1, 3)
+
+
+def test_a_step_lists_its_tiles_heaviest_first_with_their_keys():
+    ws = Workspace(torch.device("cpu"))
+    b = pack_step([0, 1, 2], [0, 100, 640], [list(range(300)), list(range(20)), list(range(130))], [[], [], []],
+                  [[[0] * 16] * 3], ws, "cpu")
+    seq, q0, n = b.tiles[128]
+    keys = b.tile_keys[128]
+    assert n == len(keys) == 3 + 1 + 2
+    assert keys == sorted(keys, reverse=True)
+    starts, counts = [0, 100, 640], [300, 20, 130]
+    for i in range(n):
+        r, a = int(seq[i]), int(q0[i])
+        assert keys[i] == starts[r] + min(a + 128, counts[r])
