@@ -6,20 +6,21 @@
 // 576-578).  A block owns 128 consecutive queries of one sequence and one head
 // and walks the key pages its queries may see:
 //
-//   warp 5     TMA copies of the Q tile and of K and V pages (straight from the paged
-//              cache, 128B-swizzled) into a ring of stages, each as soon as the products
-//              that read the stage's page before are done, and S = Q K^T as tcgen05.mma
-//              into one of two S buffers of 64 columns in tensor memory, up to two pages
-//              ahead of the softmax
-//   warp 4     O += P V as tcgen05.mma (P read from tensor memory, two buffers of 32
-//              columns; O in head_dim columns) as soon as a P is handed over.
+//   warp 5     S = Q K^T as tcgen05.mma into one of two S buffers of 64 columns in tensor
+//              memory, as soon as a page has landed and the buffer has been read: up to two
+//              pages ahead of the softmax
+//   warp 4     TMA copies of the Q tile and of K and V pages (straight from the paged
+//              cache, 128B-swizzled) into a ring of stages, and O += P V as tcgen05.mma
+//              (P read from tensor memory, two buffers of 32 columns; O in head_dim
+//              columns) as soon as a P is handed over; the page that comes into a stage
+//              next is asked for when the product that read the stage is done.
 //              A head of 128 is two boxes of 64 features for every copy, two groups of
 //              four instructions for S and two halves of O.  An instruction of 64 columns
 //              holds its issuing thread for some 49 cycles when the SM's other block issues
 //              none (measured: 47 cycles at least whatever the width, 64.5 at 128 columns,
-//              128 at 256), about 100 when it does, and a wait on an mbarrier that is
-//              already complete another 100: with one warp for everything a page's sixteen
-//              issues and waits took as long as its softmax, and each waited for the other.
+//              128 at 256), about 100 when it does, and asking for a copy some hundred
+//              more: with one warp for everything a page's issues and waits took as long
+//              as its softmax, and each waited for the other.
 //   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It reads its row
 //              of S with tcgen05.ld (no shuffles: the whole row is in its
 //              registers), masks, takes 2^(s * scale - m) with one multiply-add
@@ -263,41 +264,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   bool ok = true;
 
   if (warp == 4) {
-    // ---- second product: O += P_f V_f as soon as the softmax threads hand P_f over -------
-    const int n0 = tile_of(0).n_pages;
-    const int n_total = n0 + (n_own == 2 ? tile_of(1).n_pages : 0);   // the block's pages, numbered through both tiles
-    for (int f = 0; f < n_total && ok; ++f) {
-      const int sb = f & 1;
-      if (!fa_mbar_wait(p_full + sb, (f >> 1) & 1)) { ok = false; break; }
-      fa_fence_after();
-      if (lane == 0) {
-        const int st = f % FA_KV_STAGES;
-        // a tile's first product starts O afresh (the softmax threads hand over P only after they have read
-        // the tile before out of O)
-        const bool first = f == 0 || f == n0;
-#pragma unroll
-        for (int x = 0; x < NB; ++x) {                       // 64 features of O at a time
-          const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
-#pragma unroll
-          for (int k = 0; k < FA_BK / 16; ++k)              // 16 keys: 8 columns of P, 16 rows of V
-            fa_umma_ts(tmem_o + 64 * x, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (!first || k > 0) ? 1u : 0u);
-        }
-        fa_commit(pv_done + sb);
-        fa_commit(kv_free + st);
-      }
-      __syncwarp();
-    }
-    if (!ok && lane == 0) atomicExch(&g_fa_error, 1);
-  } else if (warp == 5) {
-    // ---- copies and the first product ------------------------------------------------------
-    // The Q tiles, then K and V page after page as stages come free, and S_f = Q K_f^T as soon as page f has
-    // landed and the softmax threads have read S_(f-2) out of the buffer: up to two pages ahead of the softmax,
-    // whatever the other product's warp is waiting for.  Page numbers come 32 at a time, lane i holding the
-    // number of page c0 + i of the block's walk, a batch ahead (a page number's trip from memory is in no
-    // page's chain of issues).
+    // ---- copies and the second product ---------------------------------------------------
+    // The Q tiles and the first pages' K and V at once; then O += P_f V_f as soon as the softmax threads hand P_f
+    // over, and, once that product is done with its stage of the ring, the copy of the page that comes into the
+    // stage next.  This warp has most of a page's time to spare; the first product's warp has not (a copy asked
+    // for there delayed S by more than it cost here).  Page numbers come 32 at a time, lane i holding the number of
+    // page c0 + i of the block's walk, a batch ahead.
     const FaTile ta = tile_of(0), tb = n_own == 2 ? tile_of(1) : ta;
     const int n0 = ta.n_pages;
-    const int n_total = n0 + (n_own == 2 ? tb.n_pages : 0);
+    const int n_total = n0 + (n_own == 2 ? tb.n_pages : 0);   // the block's pages, numbered through both tiles
     if (lane == 0) {
       for (int w = 0; w < n_own; ++w) {
         fa_mbar_expect_tx(q_full + w, FA_Q_BYTES);
@@ -328,18 +303,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       __syncwarp();
     };
-    int q_seen = 0;                                          // Q tiles known to have landed
+    while (copied < FA_KV_STAGES && copied < n_total) copy_next();
     for (int f = 0; f < n_total && ok; ++f) {
-      // every copy whose stage is free, without waiting for one that is not; page f itself at any rate
-      while (copied < n_total &&
-             (copied < FA_KV_STAGES ||
-              fa_mbar_test(kv_free + copied % FA_KV_STAGES, ((copied - FA_KV_STAGES) / FA_KV_STAGES) & 1)))
-        copy_next();
-      while (copied <= f && ok) {
-        if (!fa_mbar_wait(kv_free + copied % FA_KV_STAGES, ((copied - FA_KV_STAGES) / FA_KV_STAGES) & 1)) { ok = false; break; }
+      const int sb = f & 1, st = f % FA_KV_STAGES;
+      if (!fa_mbar_wait(p_full + sb, (f >> 1) & 1)) { ok = false; break; }
+      fa_fence_after();
+      if (lane == 0) {
+        // a tile's first product starts O afresh (the softmax threads hand over P only after they have read
+        // the tile before out of O)
+        const bool first = f == 0 || f == n0;
+#pragma unroll
+        for (int x = 0; x < NB; ++x) {                       // 64 features of O at a time
+          const uint64_t db = fa_desc(fa_smem_u32(sV + st * FA_KV_BYTES + x * FA_KVBOX_BYTES));
+#pragma unroll
+          for (int k = 0; k < FA_BK / 16; ++k)              // 16 keys: 8 columns of P, 16 rows of V
+            fa_umma_ts(tmem_o + 64 * x, tmem_p + sb * 32 + 8 * k, db + 128 * k, FA_IDESC_PV, (!first || k > 0) ? 1u : 0u);
+        }
+        fa_commit(pv_done + sb);
+        fa_commit(kv_free + st);
+      }
+      __syncwarp();
+      if (copied < n_total) {                                // page f + stages into the stage that page f leaves
+        if (!fa_mbar_wait(kv_free + st, (f / FA_KV_STAGES) & 1)) { ok = false; break; }
         copy_next();
       }
-      if (!ok) break;
+    }
+    if (!ok) {
+      // a wait ran out: say so; the copies already asked for must land before the block's shared memory goes
+      // away (when all is well the other product's warp has waited for every one of them)
+      for (int u = max(0, copied - FA_KV_STAGES); u < copied; ++u)
+        fa_mbar_wait(kv_full + u % FA_KV_STAGES, (u / FA_KV_STAGES) & 1);
+      for (int w = 0; w < n_own; ++w) fa_mbar_wait(q_full + w, 0);
+      if (lane == 0) atomicExch(&g_fa_error, 1);
+    }
+  } else if (warp == 5) {
+    // ---- first product: S_f = Q K_f^T as soon as page f has landed and the softmax threads have read S_(f-2) out
+    // of the buffer: up to two pages ahead of the softmax -------------------------------------
+    const int n0 = tile_of(0).n_pages;
+    const int n_total = n0 + (n_own == 2 ? tile_of(1).n_pages : 0);
+    int q_seen = 0;                                          // Q tiles known to have landed
+    for (int f = 0; f < n_total && ok; ++f) {
       const int sb = f & 1, st = f % FA_KV_STAGES;
       const int w = f >= n0 ? 1 : 0;
       if (q_seen <= w) {
@@ -361,14 +364,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       __syncwarp();
     }
-    if (!ok) {
-      // a wait ran out: say so; the copies already asked for must land before the block's shared memory goes
-      // away (when all is well every one of them has been waited for above)
-      for (int u = max(0, copied - FA_KV_STAGES); u < copied; ++u)
-        fa_mbar_wait(kv_full + u % FA_KV_STAGES, (u / FA_KV_STAGES) & 1);
-      for (int w = q_seen; w < n_own; ++w) fa_mbar_wait(q_full + w, 0);
-      if (lane == 0) atomicExch(&g_fa_error, 3);
-    }
+    if (!ok && lane == 0) atomicExch(&g_fa_error, 3);
   } else {
     // ---- softmax and epilogue: thread r = query row r = TMEM lane r ---------------------
     const int r = threadIdx.x;                               // 0..127
