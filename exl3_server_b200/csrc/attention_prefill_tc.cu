@@ -4,7 +4,8 @@
 // Same mathematics as attention_simt.cu (the
 // reference's masked scaled-dot-product attention, src/model.cpp:539-548,
 // 576-578).  A block owns 128 consecutive queries of one sequence and one head
-// and walks the key pages its queries may see:
+// (or two such tiles, one after the other: see the kernel) and walks the key pages
+// its queries may see:
 //
 //   warp 5     S = Q K^T as tcgen05.mma into one of two S buffers of 64 columns in tensor
 //              memory, as soon as a page has landed and the buffer has been read: up to two
@@ -67,11 +68,9 @@ __device__ inline void fa_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ inline void fa_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_smem_u32(bar)) : "memory");
 }
-// A bounded wait.  mbarrier.try_wait lets the hardware suspend the thread until the phase completes or a time
-// limit of the system's runs out, so a waiting warp takes no issue slots from the warps that compute (with
-// test_wait in a loop the two waiting warps of a block took every second or third slot of their schedulers and
-// a softmax warp stood some hundred cycles between any two of its instructions' groups).  After a try that ran
-// out the loop looks at the clock and gives up FA_WAIT_NS after it began.
+// A bounded wait: mbarrier.try_wait (which the hardware may hold for a while before it answers; a try that
+// cannot succeed came back within a few cycles when measured) in a loop that looks at the clock after every
+// try that failed and gives up FA_WAIT_NS after the first.
 __device__ inline bool fa_mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = fa_smem_u32(bar);
   uint64_t t0 = 0;
@@ -88,15 +87,6 @@ __device__ inline bool fa_mbar_wait(uint64_t* bar, uint32_t parity) {
     if (t0 == 0) t0 = now;
     else if (now - t0 > FA_WAIT_NS) return false;
   }
-}
-__device__ inline bool fa_mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(fa_smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
 }
 __device__ inline void fa_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
