@@ -169,6 +169,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   __shared__ __align__(16) float2 s_rot[AD_WARPS][64];   // a token's rotary angles (cos, sin), one table per warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gl = lane >> 2, tl = lane & 3;
+  const int kv_heads = nkv / kv_rep;                     // key/value heads in the cache
   const uint32_t ring = ((ad_smem_u32(ad_smem_raw) + 1023u) & ~1023u) + warp * (AD_STAGES * AD_STAGE_BYTES);
   uint64_t* bars = full[warp];
   if (lane == 0) {
@@ -264,7 +265,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   // The chunks of one (token, kv head) that this warp holds are neighbours, and so are their
   // pages: a run.  Page numbers come 32 at a time (lane i holds page0 + i), one batch ahead.  The unit
   // of copying is a stage's worth of keys (KS: a page, or half of one).
-  struct Batch { int t, g, page0, sub_a, sub_b; bool some; };   // stages sub_a .. sub_b of the run are still ahead
+  struct Batch { int t, g, gk, page0, sub_a, sub_b; bool some; };   // stages sub_a .. sub_b of the run are still ahead; gk: the kv head of group g
   auto run_of = [&](int t, int g, Batch& bt) {           // the pages of (t, g) inside i0 .. i1
     const int base = base_of(t, g);
     const int sp_a = max(i0 - base, 0), sp_b = min(i1 - base, chunks_of(t)) - 1;
@@ -276,6 +277,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     bt.sub_b = (c_hi + KS - 1) / KS - 1;                 // below sub_a when the run holds no cached key
     bt.t = t;
     bt.g = g;
+    bt.gk = g / kv_rep;
     bt.some = true;
   };
   auto batch_after = [&](const Batch& cur, Batch& nx) {
@@ -319,7 +321,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (lane == 0) {
       const uint32_t s = pn % AD_STAGES;
       const uint32_t dst = ring + s * AD_STAGE_BYTES;
-      const int row = (pg * (nkv / kv_rep) + cur_b.g / kv_rep) * AD_PAGE + (p_pi % SPP) * KS;
+      const int row = (pg * kv_heads + cur_b.gk) * AD_PAGE + (p_pi % SPP) * KS;   // no division here: this runs once a stage
       ad_mbar_expect_tx(bars + s, AD_STAGE_BYTES);
 #pragma unroll
       for (int b = 0; b < NBOX; ++b) {
