@@ -92,3 +92,35 @@ def test_long_prompts_through_the_paired_projections(tmp_path, monkeypatch):
         bad = np.nonzero(per_pos > TOL["bfloat16"])[0]
         assert bad.size == 0, f"request {rid}: first wrong position {bad[0]}, error {per_pos[bad[0]]:.3e}"
     K.check_status()
+
+
+@pytest.mark.parametrize("name,tokens,form", [("minicpm-2b", 2048, 3), ("minicpm-2b", 1536, 1), ("minicpm4-8b", 1100, None)])
+def test_a_long_prompt_in_each_form_of_the_prompt_attention(tmp_path, monkeypatch, name, tokens, form):
+    """One prompt whose tiles the tensor-core attention walks two a block (2,048 tokens at the MiniCPM-2B sizes: 576
+    blocks would be two rounds) or one a block (1,536 tokens: the heaviest tile is the kernel's length anyway), and
+    one with heads of 128: every logit against the plain implementation, and the form that the attention part
+    asked for."""
+    from exl3_server_b200 import Engine, LlamaConfig, write_random_model
+    from exl3_server_b200.config.presets import sizes
+    from exl3_server_b200.ops import kernels as K
+    cfg = LlamaConfig(**sizes(name, num_hidden_layers=2, vocab_size=1000))
+    folder = str(tmp_path / "m")
+    write_random_model(cfg, folder, seed=6, std=0.02)
+    g = torch.Generator().manual_seed(8)
+    toks = torch.randint(0, cfg.vocab_size, (tokens,), generator=g).tolist()
+    want = PlainModel(folder).logits(toks).numpy()
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=4096)
+    asked = []
+    kernel = K.attn_prefill_tc
+
+    def watched(*a, **k):
+        asked.append(k.get("variant", 0))
+        return kernel(*a, **k)
+
+    monkeypatch.setattr(K, "attn_prefill_tc", watched)
+    got = run_trace(eng, whole_trace({"r0": toks}))["r0"]
+    assert len(asked) == 2 and (form is None or asked == [form, form]), asked
+    assert K.attn_prefill_tc_status() == 0
+    per_pos = np.max(np.abs(got - want), axis=1) / np.max(np.abs(want))
+    bad = np.nonzero(per_pos > TOL["bfloat16"])[0]
+    assert bad.size == 0, f"first wrong position {bad[0]}, error {per_pos[bad[0]]:.3e}"
