@@ -88,6 +88,21 @@ __device__ inline bool fa_mbar_wait(uint64_t* bar, uint32_t parity) {
     else if (now - t0 > FA_WAIT_NS) return false;
   }
 }
+// One look at a phase: whether it has completed.
+__device__ inline bool fa_mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(fa_smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ inline float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ inline void fa_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -368,21 +383,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // The row of S_f is asked for as soon as the row of P_(f-1) is on its way into tensor memory (the first of a
     // tile: here), so that the load's latency and the store's pass together.
     uint32_t sr[2][32];
-    auto ask_s = [&](int f) -> bool {
+    auto ask_s = [&](int f, bool there) -> bool {           // there: the barrier is known to have flipped
       const int st = f & 1;
-      if (!fa_mbar_wait(s_full + st, (f >> 1) & 1)) return false;
+      if (!there && !fa_mbar_wait(s_full + st, (f >> 1) & 1)) return false;
       fa_fence_after();
       fa_ld32(tmem_base + lane_addr + st * 64, sr[0]);
       fa_ld32(tmem_base + lane_addr + st * 64 + 32, sr[1]);
       return true;
     };
-    ok = ask_s(fb);
+    ok = ask_s(fb, false);
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int f = fb + j;
       const int st = f & 1;
       fa_wait_ld();
       fa_fence_before();
       fa_mbar_arrive(s_free + st);
+      // The two barriers this page still needs (the P buffer free again, the next S written) are looked at now:
+      // both have almost always flipped a page ago, and the looks' trips to shared memory pass under the
+      // arithmetic below instead of standing in front of the store of P and the load of S.
+      const bool p_free = f < 2 || fa_mbar_test(pv_done + st, ((f - 2) >> 1) & 1);
+      const bool s_there = j + 1 < n_blocks && fa_mbar_test(s_full + (st ^ 1), ((f + 1) >> 1) & 1);
       const int key0 = (page_lo + j) * FA_BK;
       const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window);
       // four independent chains for the maximum (and below for the sum): the row is long and
@@ -403,7 +423,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
+        for (int c = 0; c < 32; c += 2)                      // two scores an instruction
+          mx4[(c >> 1) & 3] = fa_max3(mx4[(c >> 1) & 3], __uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1]));
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= scale_log2;                                      // scale > 0: max and scale commute
       // lazy rescale: move the reference maximum only when it is far behind
@@ -436,7 +457,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       const float mref = (m_used == -INFINITY) ? 0.0f : m_used;
       // the P buffer of two pages ago must have been consumed
-      if (f >= 2 && !fa_mbar_wait(pv_done + st, ((f - 2) >> 1) & 1)) { ok = false; break; }
+      if (!p_free && !fa_mbar_wait(pv_done + st, ((f - 2) >> 1) & 1)) { ok = false; break; }
       uint32_t pw[32];
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -449,7 +470,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run += sum;
       fa_st32(tmem_p + lane_addr + st * 32, pw);
-      if (j + 1 < n_blocks && !ask_s(f + 1)) ok = false;   // the tile's next row of S while P is being stored
+      if (j + 1 < n_blocks && !ask_s(f + 1, s_there)) ok = false;   // the tile's next row of S while P is being stored
       fa_wait_st();
       fa_fence_before();
       fa_mbar_arrive(p_full + st);
