@@ -25,6 +25,7 @@ import math
 import os
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..ops import kernels as K
@@ -194,42 +195,58 @@ class Attention:
 
     def _prefill_variant(self, tile_keys, page: int, device: torch.device) -> int:
         """Which form of the tensor-core prompt kernel a step's tiles get (``K.attn_prefill_tc``'s ``variant``): a
-        tile a block (1), or two tiles a block, the list's first with its last and so on (3), when that ends
-        sooner; 0 leaves it to the kernel, which then takes four blocks an SM for heads of 64 with more blocks than
-        four per SM.  A block's time is taken as its pages to walk plus two pages' worth for every tile (its start
-        and its end), and the blocks as started in launch order on two slots an SM (heads of 64; one for heads of
-        128), each on the slot that comes free first.  One prompt of 2,048 tokens with 36 heads of 64: two tiles a
-        block 41 us, one 44.5 us; 1,536 tokens: 34.5 against 30 us (the heaviest tile alone is the kernel's
-        length there, and a second tile behind it only adds to it)."""
+        tile a block (1); two tiles a block, the list's first with its last and so on (3); or, for heads of 64, the
+        kernel with four blocks an SM (2).  All three are simulated from the list of tiles: a block's time is its
+        pages to walk plus three pages' worth for every tile (its start and its end), a page taking 0.9 us on one
+        of the two slots an SM has for the first two forms (one slot for heads of 128) and 1.5 us on one of the four
+        of the third; the tiles' heads run side by side on as many slots, and a tile goes to the slots that come
+        free first, in the list's order.  Constants fitted to thirteen measured workloads (to 9 % in the mean; us
+        for forms 1 / 2 / 3, 36 heads of 64 unless said): one prompt of 2,048 tokens 41.9 / 59.1 / 40.2, of 1,536
+        28.5 / 39.3 / 34.0, of 8,192 442 / 429 / 455, 24 prompts of 16 to 2,048 tokens 447 / 392 / 470, one of 5,000
+        with 16 heads 88.8 / 130 / 130.  The four-block kernel is taken when the better of the others is not
+        below 0.93 of it (the model flatters them where tiles are short)."""
         s = self.spec
         if not tile_keys:
             return 0
         sms = K.sm_count(device)
-        slots = sms * (2 if s.head_dim == 64 else 1)
         n = len(tile_keys)
-        if s.head_dim == 64 and n * s.heads > 4 * sms:
-            return 0
         size = 128
         pages = [((min(k, s.window + size) if s.window > 0 else k) + page - 1) // page for k in tile_keys]
-        each = 2                                                # a tile's start and end, in pages
+        each = 3                                                # a tile's start and end, in pages
 
-        def makespan(times):
+        def makespan(times, slots):
             if len(times) * s.heads <= slots:
                 return max(times)
-            free = [0] * slots
-            heapq.heapify(free)
-            end = 0
+            if len(times) <= 64 and s.heads <= slots:
+                # every block on the slot that comes free first: a tile's heads take the slots that are free soonest
+                free = np.zeros(slots)
+                for t in times:
+                    free[np.argpartition(free, s.heads - 1)[:s.heads]] += t
+                return float(free.max())
+            # many tiles: groups of slots as wide as a tile has heads, what the division leaves over given back as
+            # capacity
+            groups = slots // s.heads
+            if groups == 0:
+                return sum(times) * s.heads / slots
+            free = [0.0] * groups
+            end = 0.0
             for t in times:
-                for _ in range(s.heads):
-                    at = heapq.heappop(free) + t
-                    heapq.heappush(free, at)
-                    end = max(end, at)
-            return end
+                at = heapq.heappop(free) + t
+                heapq.heappush(free, at)
+                end = max(end, at)
+            return max(max(times), end * groups * s.heads / slots)
 
-        one = makespan([p + each for p in pages])
+        slots = sms * (2 if s.head_dim == 64 else 1)
+        one = 0.9 * makespan([p + each for p in pages], slots)
         half = (n + 1) // 2
-        two = makespan([pages[i] + each + (pages[n - 1 - i] + each if n - 1 - i > i else 0) for i in range(half)])
-        return 3 if two <= one else 1
+        two = 0.9 * makespan([pages[i] + each + (pages[n - 1 - i] + each if n - 1 - i > i else 0) for i in range(half)],
+                             slots)
+        best = 3 if two <= one else 1
+        if s.head_dim == 64:
+            four = 1.5 * makespan([p + each for p in pages], 4 * sms)
+            if min(one, two) >= 0.93 * four:
+                return 2
+        return best
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
         """``(keys per chunk, head_split, in_block)`` for the tensor-core decode kernel: chunks of whole pages (a

@@ -59,12 +59,18 @@ def test_prompt_kernel_form():
     assert two_b._prefill_variant(tile_keys([2048]), 64, None) == 3      # 576 blocks: two rounds, or one of pairs
     assert two_b._prefill_variant(tile_keys([1536]), 64, None) == 1      # the heaviest tile is the kernel's length
     assert two_b._prefill_variant(tile_keys([1024]), 64, None) == 1      # all blocks at once
-    assert two_b._prefill_variant(tile_keys([8192]), 64, None) == 0      # many rounds: the kernel's four-block form
+    assert two_b._prefill_variant(tile_keys([8192]), 64, None) == 2      # many rounds: four blocks an SM
+    assert two_b._prefill_variant(tile_keys([16, 300, 1000, 2048]), 64, None) == 2
     assert two_b._prefill_variant([], 64, None) == 0
-    assert mixer(16, 2, 64)._prefill_variant(tile_keys([2048]), 64, None) == 1
-    assert mixer(32, 2, 128)._prefill_variant(tile_keys([2048]), 64, None) in (1, 3)
-    # a window bounds what a tile walks
-    assert mixer(36, 36, 64, window=256)._prefill_variant(tile_keys([2048]), 64, None) in (1, 3)
+    half_b = mixer(16, 2, 64)
+    assert half_b._prefill_variant(tile_keys([2048]), 64, None) == 1
+    assert half_b._prefill_variant(tile_keys([5000]), 64, None) == 1     # 640 blocks: a few more than four an SM hold
+    assert half_b._prefill_variant(tile_keys(list(range(16, 2048, 32))), 64, None) == 2
+    # heads of 128 have no four-block kernel; a window bounds what a tile walks
+    assert mixer(32, 2, 128)._prefill_variant(tile_keys([2048]), 64, None) == 1
+    assert mixer(32, 2, 128)._prefill_variant(tile_keys([8192]), 64, None) in (1, 3)
+    assert mixer(36, 36, 64, window=256)._prefill_variant(tile_keys([2048]), 64, None) in (1, 2, 3)
+    assert mixer(200, 200, 64)._prefill_variant(tile_keys([4096]), 64, None) in (1, 2, 3)   # more heads than slots
 
 
 def test_a_step_lists_its_tiles_heaviest_first_with_their_keys():
