@@ -60,7 +60,8 @@
 
 namespace exl3 {
 
-constexpr int AD_WARPS = 4;
+constexpr int AD_WARPS = 4;                                // warps that compute; each has a warp that copies for it
+constexpr int AD_THREADS = 2 * AD_WARPS * 32;
 constexpr int AD_PAGE = 64;
 constexpr int AD_MAX_GROUP = 16;                           // query heads per kv head: one or two blocks of 8 instruction columns
 // A stage holds the keys, then the values, of one page of one kv head (heads of 64) or of half a page (heads of
@@ -96,6 +97,25 @@ __device__ inline bool ad_mbar_wait(uint64_t* bar, uint32_t parity) {
     if (ok) return true;
   }
   return false;
+}
+// The same for a warp that has nothing else to do: it sleeps between looks, so that it takes no issue slots
+// from the warps that compute.
+__device__ inline bool ad_mbar_wait_idle(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = ad_smem_u32(bar);
+  for (uint32_t i = 0; i < AD_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    __nanosleep(40);
+  }
+  return false;
+}
+__device__ inline void ad_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ad_smem_u32(bar)) : "memory");
 }
 __device__ inline void ad_tma_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
@@ -142,7 +162,7 @@ __device__ inline uint32_t ad_pack(float lo, float hi) {
 // NC: blocks of 8 query heads of a kv head's group (the columns of an instruction): 1 for groups of up to 8, 2 for
 // up to 16.  Both blocks use the same key and value fragments, so a page is read from shared memory once.
 template <int HD, int NC>
-__global__ void __launch_bounds__(AD_WARPS * 32, 1)
+__global__ void __launch_bounds__(AD_THREADS, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
@@ -162,18 +182,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   constexpr int BOX_BYTES = KS * 128;
   static_assert(KS * HD * 2 == AD_TILE_BYTES, "a stage is 8 KB of keys and 8 KB of values");
   extern __shared__ unsigned char ad_smem_raw[];
-  __shared__ uint64_t full[AD_WARPS][AD_STAGES];
+  __shared__ uint64_t full[AD_WARPS][AD_STAGES];         // a stage's copies have landed
+  __shared__ uint64_t empty[AD_WARPS][AD_STAGES];        // the computing warp has read the stage
+  __shared__ volatile unsigned s_asked[AD_WARPS];        // stages a ring's copier has asked for so far
   __shared__ int s_pos[AD_MAX_TOKENS], s_seq[AD_MAX_TOKENS];
   __shared__ int s_cum[AD_MAX_TOKENS + 1];               // chunks of the tokens before this one (per kv head)
   __shared__ float s_w[AD_WARPS][AD_MAX_SPLITS], s_l[AD_WARPS][AD_MAX_SPLITS];   // a merge's weights and sums
   __shared__ __align__(16) float2 s_rot[AD_WARPS][64];   // a token's rotary angles (cos, sin), one table per warp
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Warps 0 .. AD_WARPS - 1 compute; warp AD_WARPS + w asks for the copies into warp w's ring (asked for by the
+  // computing warp itself, between two stages, they took 200 to 400 of a stage's 1,100 to 1,300 cycles).
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = wid % AD_WARPS;                       // the ring, and its computing warp
+  const bool copier = wid >= AD_WARPS;
   const int gl = lane >> 2, tl = lane & 3;
   const int kv_heads = nkv / kv_rep;                     // key/value heads in the cache
   const uint32_t ring = ((ad_smem_u32(ad_smem_raw) + 1023u) & ~1023u) + warp * (AD_STAGES * AD_STAGE_BYTES);
   uint64_t* bars = full[warp];
-  if (lane == 0) {
-    for (int s = 0; s < AD_STAGES; ++s) ad_mbar_init(bars + s, 1);
+  uint64_t* gone = empty[warp];
+  if (lane == 0 && !copier) {
+    for (int s = 0; s < AD_STAGES; ++s) { ad_mbar_init(bars + s, 1); ad_mbar_init(gone + s, 1); }
+    s_asked[warp] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -198,7 +226,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   }
   if (threadIdx.x == 0) s_cum[0] = 0;
   __syncthreads();
-  if (warp == 0) {
+  if (wid == 0) {
     const int per = (T + 31) / 32;                       // each lane sums a stretch of tokens, then the stretches are chained
     const int a = min(lane * per, T), b = min(a + per, T);
     int sum = 0;
@@ -307,9 +335,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   }
   nxt_pages = fetch(nxt_b);
   uint32_t pn = 0;                                       // pages asked for
-  auto produce = [&]() {
+  auto produce = [&]() -> bool {
     while (p_pi > p_end) {
-      if (!nxt_b.some) return;                           // no page left for this warp
+      if (!nxt_b.some) return false;                     // no page left for this ring
       cur_b = nxt_b;
       cur_pages = nxt_pages;
       p_pi = cur_b.sub_a;
@@ -331,9 +359,23 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
     ++p_pi;
     ++pn;
+    if (lane == 0) s_asked[warp] = pn;
+    return true;
   };
-#pragma unroll 1
-  for (int s = 0; s < AD_STAGES; ++s) produce();
+  if (copier) {
+    // ---- a ring's copies: a stage as soon as the computing warp is done with what was in it ----
+    bool fine = true;
+    for (;;) {
+      if (pn >= AD_STAGES && !ad_mbar_wait_idle(gone + pn % AD_STAGES, ((pn / AD_STAGES) - 1) & 1)) { fine = false; break; }
+      if (!produce()) break;
+    }
+    if (!fine) {
+      // the computing warp never came: say so, and give the copies in flight a bounded time to land
+      if (lane == 0) atomicExch(&g_ad_error, 1);
+      for (uint32_t u = pn > (uint32_t)AD_STAGES ? pn - AD_STAGES : 0; u < pn; ++u)
+        if (!ad_mbar_wait(bars + u % AD_STAGES, (u / AD_STAGES) & 1)) break;
+    }
+  }
 
   // Q^T as the right operand: column gl of block c is query head 8 c + gl of the group, zero beyond the group
   auto load_q = [&](int t, int g, bool some, uint32_t (&qq)[NC][NJ][2]) {
@@ -495,6 +537,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   uint32_t qb[NC][NJ][2], qn[NC][NJ][2];
   int nt = 0, ng = 0;
   bool nsome = false;
+  if (!copier) {
   if (rotate && i0 < i1) angles_of(t0);                  // positions are the step's inputs
   if (write_new) pdl_wait();                             // from here on the projection's output is read
   if (i0 < i1) {
@@ -639,8 +682,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         }
       }
       __syncwarp();                                      // every lane has read the stage
+      if (lane == 0) ad_mbar_arrive(gone + st);          // its copier may ask for the stage AD_STAGES ahead
       ++cn;
-      produce();                                         // refill it with the stage AD_STAGES ahead
     }
     if (!ok) break;
     if (has_new) {
@@ -750,16 +793,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       }
     }
   }
+  }
   if (in_block) {
-    if (!ok) {
+    if (!copier && !ok) {
       if (lane == 0) atomicExch(&g_ad_error, 1);
-      for (; cn < pn; ++cn) {
+      for (; cn < s_asked[warp]; ++cn) {
         if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
       }
     }
     __syncthreads();                                     // every warp comes here, whatever its share and its verdict
     const int n_rec = chunks_of(t_blk);
-    if (n_rec > 1) {
+    if (n_rec > 1 && !copier) {
       // the item's chunks, in chunk order; a warp takes every fourth head, a lane HD / 32 features
       for (int n = warp; n < G; n += AD_WARPS) {
         const float* hb = rec_blk + n * rec;
@@ -782,6 +826,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         }
       }
     }
+  } else if (copier) {
+    // nothing left to do: the ring's copies are asked for, and the computing warp waits for each of them
   } else if (ok) {
     // All of this warp's records are written.  One fence for all of them, then a ticket per chunk,
     // lanes side by side; the chunks of a (token, kv head) are merged by the warp that draws the
@@ -809,7 +855,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     // A copy did not land in time: say so, and give the copies still in flight a bounded time to
     // land before the block's shared memory goes away.
     if (lane == 0) atomicExch(&g_ad_error, 1);
-    for (; cn < pn; ++cn) {
+    for (; cn < s_asked[warp]; ++cn) {
       if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
     }
   }
@@ -939,7 +985,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   int* counters = max_splits > 1 && !in_block ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 && !in_block ? scratch + AD_COUNTER_SLOTS : nullptr;
 #define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
-  launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_WARPS * 32), (size_t)AD_SMEM, stream, map_k, map_v,  \
+  launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_THREADS), (size_t)AD_SMEM, stream, map_k, map_v,     \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
