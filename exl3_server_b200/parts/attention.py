@@ -254,26 +254,24 @@ class Attention:
         (``head_split``: that many times the work items, each merge that much smaller, the keys and values read
         again from L2), and whether a block takes a whole (token, group of heads) and merges its up to four chunks in
         shared memory (``in_block``) instead of warps taking equal shares of all chunks and merging through global
-        memory.  By a small model of the kernel's time, its constants fitted to sweeps at four head layouts
-        (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128) and batches of 1 to 64 (to 14 % in the mean): 4 us to start;
-        a warp walks its chunk at 0.8 us per 16 KB of keys and values plus 0.02 us for every query head in its group;
-        when there are more chunks than warps a warp takes several in turn; all warps together cannot read faster
-        than the memory does (6 TB/s for what is read once, 12 TB/s from L2 for what the groups of a kv head read
-        again); and the chunks of a (token, group of heads), when there is more than one, are merged by a single
-        warp: 3 us, plus per chunk 0.05 us and 0.06 us for every head of the group, 2 % more for every group that
-        merges at the same time.  So wide groups of heads in small batches are cut into many narrow ones with a fair
-        number of chunks each, as many pieces as there are warps (one token of 32 query heads of 128 on 2 kv heads
-        at 2,048 tokens: 16 groups of 16 chunks take 13 us, one group of 8 chunks 33 us), one chunk wins for short
-        contexts and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks
-        only where they are needed to give every SM work.  A block per item costs, for every round of as many
-        blocks as the GPU has SMs, 5.5 us (start and the merge in shared memory) and its walk (a quarter of the keys
-        per warp), and not less than the memory's time, which its rounds stream some 5 % faster at the price of
-        1.5 us between rounds; it is taken when that is below 0.95 of the other way's cost: for up to about as many
-        items as the GPU has SMs, each too long for one warp (64 sequences of 2 kv heads with 16 query heads of 128
-        each at 2,048 tokens: 33 against 47 us; four sequences of 36 heads at 4,096 tokens: 30 against 33 us), and
-        for several rounds of long items (eight sequences of 36 heads at 16,384 tokens: 181 against 191 us), not
-        for many rounds of short ones (64 sequences of 36 heads at 512 tokens: 123 against 58 us).  The choice
-        depends on the step's size, not on a token's position: results differ between batch sizes by rounding."""
+        memory.  By a small model of the kernel's time, its constants fitted to a sweep of every chunking at four
+        head layouts (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128), contexts of 128 to 16,384 tokens and batches of
+        1 to 64 (some 4,000 timings; what the model picks is 1.6 % slower in the mean than the best of a case, and
+        more than 10 % slower in 3 of 137 cases): 5.5 us to start; a warp walks its chunk at 0.6 us per 16 KB of keys
+        and values (0.9 us with more than 8 query heads in its group: two blocks of instruction columns); when there
+        are more chunks than warps a warp takes several in turn; all warps together cannot read faster than the
+        memory does (6.6 TB/s for what is read once, 12 TB/s from L2 for what the groups of a kv head read again);
+        and the chunks of a (token, group of heads), when there is more than one, are merged by a single warp:
+        3.5 us, plus per chunk 0.03 us and 0.05 us for every head of the group, 1 % more for every group that merges
+        at the same time.  So wide groups of heads in small batches are cut into many narrow ones with a fair number
+        of chunks each, one chunk wins for short contexts and for batches with a warp's worth of work per sequence
+        (no merge at all), and many short chunks only where they are needed to give every SM work.  A block per
+        item costs, for every round of as many blocks as the GPU has SMs, 5 us (start and the merge in shared
+        memory) and its walk (a quarter of the keys per warp), and not less than the memory's time, which its rounds
+        stream some 5 % faster at the price of 1 us between rounds; it is taken when that is below 0.95 of the other
+        way's cost: for up to about as many items as the GPU has SMs, each too long for one warp, and for several
+        rounds of long items, not for many rounds of short ones.  The choice depends on the step's size, not on a
+        token's position: results differ between batch sizes by rounding."""
         s = self.spec
         keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
         pages_seq = max(1, (keys + page - 1) // page)
@@ -289,24 +287,24 @@ class Attention:
             g = group // head_split
             if g > 16:
                 continue
-            stage_us = 0.8 + 0.02 * g
+            stage_us = 0.6 if g <= 8 else 0.9
             groups = T * s.kv_heads * head_split
-            once_us = T * s.kv_heads * pages_seq * wide * 16384 / 6.0e6
+            once_us = T * s.kv_heads * pages_seq * wide * 16384 / 6.6e6
             again_us = groups * pages_seq * wide * 16384 / 12.0e6
             per = 1
             while True:
                 n = (pages_seq + per - 1) // per
                 if n + (1 if s.window > 0 else 0) <= K.ATTN_DECODE_MAX_CHUNKS:     # a window may straddle one chunk more
                     rounds = (groups * n + warps - 1) // warps
-                    cost = 4.0 + max(rounds * per * wide * stage_us, once_us, again_us)
+                    cost = 5.5 + max(rounds * per * wide * stage_us, once_us, again_us)
                     if n > 1:
-                        cost += 3.0 + n * (0.05 + 0.06 * g) * (1.0 + 0.02 * groups)
+                        cost += 3.5 + n * (0.03 + 0.05 * g) * (1.0 + 0.01 * groups)
                     if best is None or cost < best[0] - 1e-9:
                         best = (cost, per, head_split, False)
                     if 1 < n + (1 if s.window > 0 else 0) <= 4:
                         rounds = (groups + sms - 1) // sms
-                        cost = max(rounds * (5.5 + per * wide * stage_us),
-                                   5.5 + max(once_us, again_us) / 1.05 + 1.5 * (rounds - 1))
+                        cost = max(rounds * (5.0 + per * wide * stage_us),
+                                   5.0 + max(once_us, again_us) / 1.05 + 1.0 * (rounds - 1))
                         if best_blk is None or cost < best_blk[0] - 1e-9:
                             best_blk = (cost, per, head_split, True)
                 if per >= pages_seq or per * wide >= 64:
