@@ -801,7 +801,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
       }
     }
-    __syncthreads();                                     // every warp comes here, whatever its share and its verdict
+    __syncthreads();                                     // every warp comes here, whatever its share and its outcome
     const int n_rec = chunks_of(t_blk);
     if (n_rec > 1 && !copier) {
       // the item's chunks, in chunk order; a warp takes every fourth head, a lane HD / 32 features

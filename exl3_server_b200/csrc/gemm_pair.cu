@@ -313,7 +313,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t buf = tcount & 1;
       const int row = row0 + lane;
       // the tile's bias and norm weights, once for all rows (the previous tile's readers are past their last read:
-      // they have met at the barrier after it); every thread comes here, whatever its verdict so far
+      // they have met at the barrier after it); every thread comes here, whatever its outcome so far
       if (!gp_epilogue_all<EPI_THREADS>(ok)) { ok = false; break; }
       for (int c = t; c < GP_BN; c += EPI_THREADS) {
         const int n = n0 + c;
@@ -345,7 +345,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int seq0 = __shfl_sync(0xffffffffu, my_seq, 0);
         together = __all_sync(0xffffffffu, row < a.M && my_seq == seq0 && my_pos == pos0 + lane && my_page >= 0) && (pos0 & 31) == 0;
       }
-      // (also the barrier after which the staged bias and norm weights may be read) one verdict for all epilogue
+      // (also the barrier after which the staged bias and norm weights may be read) one outcome for all epilogue
       // threads, so that they leave the loop together
       if (!gp_epilogue_all<EPI_THREADS>(mbar_wait(acc_full + buf, (tcount >> 1) & 1))) { ok = false; break; }
       fence_after();
