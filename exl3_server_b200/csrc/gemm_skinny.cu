@@ -143,9 +143,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       for (int i = 0; i < pre; ++i) tma_load_2d(sX + (size_t)i * stage_x, &map_x, full + i, (ks0 + i) * SK_BK, 0);
     __syncwarp();
     int issued = pre;
+    // the ring's stage and round of step i, counted along (a division by the run-time stage count in every step
+    // is part of what the one issuing thread pays per step)
+    int s = pre % a.stages, round = pre / a.stages;
     for (int i = pre; i < nk; ++i) {
-      const int s = i % a.stages;
-      if (!mbar_wait(empty + s, ((i / a.stages) & 1) ^ 1)) { ok = false; break; }
+      if (!mbar_wait(empty + s, (round & 1) ^ 1)) { ok = false; break; }
       if (lane == 0) {
         mbar_expect_tx(full + s, STAGE_W + stage_x);
         tma_load_2d(sW + (size_t)s * STAGE_W, &map_w, full + s, (ks0 + i) * SK_BK, n0);
@@ -153,6 +155,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
       __syncwarp();
       issued = i + 1;
+      if (++s == a.stages) { s = 0; ++round; }
     }
     if (!ok) {
       if (lane == 0) atomicExch(&g_sk_error, 1);
@@ -165,9 +168,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------------------
     const uint32_t idesc = idesc_bf16(SK_BM, a.MP);
+    int s = 0, round = 0;
     for (int i = 0; i < nk; ++i) {
-      const int s = i % a.stages;
-      if (!mbar_wait(full + s, (i / a.stages) & 1)) { ok = false; break; }
+      if (!mbar_wait(full + s, round & 1)) { ok = false; break; }
       fence_after();
       if (lane == 0) {
         const uint64_t db = smem_desc_k128(smem_u32(sX + (size_t)s * stage_x));
@@ -181,6 +184,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         mma_commit(empty + s);
       }
       __syncwarp();
+      if (++s == a.stages) { s = 0; ++round; }
     }
     if (ok) {
       if (lane == 0) mma_commit(acc_full);
