@@ -447,14 +447,29 @@ static int sk_auto_split(int N, int K) {
   while (s > 1 && ksteps / s < 2) --s;
   // fewer cuts when the tiles' clusters would not all run at once (a second round of clusters costs its full length)
   while (s > 1 && n_tiles > sk_max_clusters(s)) --s;
-  return s < 1 ? 1 : s;
+  if (s < 1) s = 1;
+  // More tiles than SMs, and no cut: the cuts that pairs of tiles would get when a block takes two (as it does
+  // for few rows, below): 32768 x 4096 at 1 to 32 rows 42.9-46.2 us with two tiles a block and two cuts against
+  // 45.3-48.2 us with one and none; at 48 and 64 rows, a tile a block, the two cuts cost 1 us of 50.
+  if (s == 1 && n_tiles > sk_sm_count()) {
+    const int pairs = ceil_div(n_tiles, 2);
+    int s2 = 2 * sk_sm_count() / pairs;
+    if (s2 > SK_MAX_SPLIT) s2 = SK_MAX_SPLIT;
+    while (s2 > 1 && (ksteps / s2 < 2 || pairs > sk_max_clusters(s2))) --s2;
+    if (s2 >= 2) s = s2;
+  }
+  return s;
 }
 
-// Two tiles per block (the block's piece of x is then read once for twice the weights) only where there are
-// many times more tiles than SMs, as in an output head; with fewer, one tile per block and two blocks per SM
-// were faster at every size measured.  Changes no result (the cuts of K stay what N and K say).
-static int sk_auto_tiles(int N, int split) {
-  return ceil_div(N, SK_BM) * split >= 8 * sk_sm_count() ? 2 : 1;
+// Two tiles per block (the block's piece of x is then read once for twice the weights) where there are more
+// tiles than SMs and the blocks of two tiles still fill the GPU one and a half times, for up to 32 rows (an
+// output head of 122753 x 2304: 87.8 / 90.5 / 93.3 / 97.7 us at 1 / 8 / 16 / 32 rows against 95.1 / 97.5 / 100.5 /
+// 105.1 with a tile a block, but 132.6 against 114.2 at 64 rows); for more rows only with many times more tiles
+// than SMs.  Changes no result (the cuts of K stay what N and K say).
+static int sk_auto_tiles(int N, int split, int M) {
+  const int n_tiles = ceil_div(N, SK_BM), sms = sk_sm_count();
+  if (M <= 32) return n_tiles > sms && 2 * ceil_div(n_tiles, 2) * split >= 3 * sms ? 2 : 1;
+  return n_tiles * split >= 8 * sms ? 2 : 1;
 }
 
 template <int EPI, bool SCALE, int R>
@@ -546,7 +561,7 @@ extern "C" int exl3_gemm_skinny(const void* x, const void* w, const void* bias, 
   const int ksteps = ceil_div(K, SK_BK);
   a.split = split > 0 ? split : sk_auto_split(N, K);
   if (a.split > ksteps) a.split = ksteps;
-  const int R = tiles > 0 ? tiles : sk_auto_tiles(N, a.split);
+  const int R = tiles > 0 ? tiles : sk_auto_tiles(N, a.split, M);
   a.rows_per = ceil_div(a.MP, a.split);
   const int cols = R * a.MP;
   a.tmem_cols = cols <= 32 ? 32 : (cols <= 64 ? 64 : (cols <= 128 ? 128 : 256));
