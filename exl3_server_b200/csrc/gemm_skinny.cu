@@ -430,14 +430,45 @@ static int sk_map(CUtensorMap* out, const void* p, int64_t rows, int K, int box)
 // costs its full length), at most 8 and at least two 64-wide steps per block.  Measured at 2304 x 2304 ... 11520 x
 // 2304 with 8 and 64 rows: 5 cuts for 54 tiles, 3 for 90, 8 for 18.  From N and K only, so that a result never
 // depends on the batch.
-// Clusters of s blocks that run at once with two blocks to an SM.  A cluster's blocks must find their SMs in one
-// of the GPU's parts, of which a B200 has eight of 18 or 19 SMs (36 places for blocks): 32 clusters of 8 run at
-// once and 36 do not (4608 x 4096 at 64 rows: 16.2 us in 8 cuts, 11.4 us in 7), 54 clusters of 5 do, 90 of 3 do.
-// From the SM count only: the answer must not depend on the batch, or a row's result would depend on its batch.
+// Clusters of s blocks that run at once with two blocks to an SM, as the driver counts them for this kernel's
+// block (192 threads, some 100 KB of shared memory).  A cluster's blocks must find their SMs in one of the GPU's
+// parts, and the parts are not equal: on the B200 measured, 296 / 148 / 93 / 71 / 56 / 45 / 37 / 33 clusters of 1
+// to 8 (a kernel whose blocks wait 20 us takes 20 us up to these counts and 40 us from one more: the same numbers).
+// One cluster too many costs a second round of its full length: 6144 x 4096 in 6 cuts (48 clusters) 15.6 us, in 5
+// cuts 10.7 us; 4608 x 4096 in 8 cuts 12.9 us, in 7 cuts 8.8 us.  From the device only: the answer must not depend
+// on the batch, or a row's result would depend on its batch.
+// never launched: a block of this kernel's shape for the driver's count
+__global__ void __launch_bounds__(SK_THREADS) sk_block_shape_kernel() {}
+
 static int sk_max_clusters(int s) {
-  if (s < 1) return 0;
-  const int per_part = 2 * (sk_sm_count() / 8);
-  return 8 * (per_part / s);
+  static int cache[SK_MAX_SPLIT + 1] = {};
+  if (s < 1 || s > SK_MAX_SPLIT) return 0;
+  if (cache[s] == 0) {
+    int n = 0;
+    const int smem = 100 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(sk_block_shape_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(8 * s));
+      cfg.blockDim = dim3(SK_THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = (unsigned)s;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      e = cudaOccupancyMaxActiveClusters(&n, sk_block_shape_kernel, &cfg);
+    }
+    if (e != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 8 * ((2 * (sk_sm_count() / 8)) / s);             // eight equal parts: a little too many for some s
+      if (n < 1) n = 1;
+    }
+    cache[s] = n;
+  }
+  return cache[s];
 }
 
 static int sk_auto_split(int N, int K) {
