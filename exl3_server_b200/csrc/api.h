@@ -112,8 +112,9 @@ int exl3_gemm_pair_ss_blocks(int N);
 // to 16 query heads per kv head, 1024 tokens, 256 chunks); arguments and scratch as exl3_attn_tokens; optionally
 // it applies the rotary encoding and takes each token's own key and value from the projection's output, writing
 // them to the cache itself.  head_split n (a divisor of the query heads per kv head): the query heads of a kv head
-// as n groups of work.  in_block: a block per (token, group of heads), whose warps take the item's chunks (at most 4)
-// and merge them in shared memory; no scratch then.  See attention_decode.cu.
+// as n groups of work.  in_block 1: a block per (token, group of heads), whose warps take the item's chunks (at most
+// 4) and merge them in shared memory; 2: a cluster of two blocks (at most 8 chunks, the first block merging, the
+// second one's records read out of its shared memory); no scratch in either.  See attention_decode.cu.
 int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys, int max_splits);
 int exl3_attn_decode_status();
 int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,

@@ -117,6 +117,23 @@ __device__ inline bool ad_mbar_wait_idle(uint64_t* bar, uint32_t parity) {
 __device__ inline void ad_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ad_smem_u32(bar)) : "memory");
 }
+// Thread-block clusters: a block's rank, a barrier over all threads of the cluster's blocks (release / acquire), and
+// a float read from the same place in another block's shared memory.
+__device__ inline uint32_t ad_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ inline void ad_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ inline float ad_ld_peer(const float* mine, uint32_t rank) {
+  uint32_t addr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(ad_smem_u32(mine)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
 __device__ inline void ad_tma_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -253,10 +270,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int n_chunks = nkv * s_cum[T];
   const int n_warps = gridDim.x * AD_WARPS, gw = blockIdx.x * AD_WARPS + warp;
   int i0 = (int)((int64_t)gw * n_chunks / n_warps), i1 = (int)((int64_t)(gw + 1) * n_chunks / n_warps);
-  const int t_blk = in_block ? (int)blockIdx.x / nkv : 0, g_blk = in_block ? (int)blockIdx.x % nkv : 0;
+  // in_block = 2: the item belongs to a cluster of two blocks, whose eight computing warps take its up to eight
+  // chunks; the first block merges, reading the second one's records out of its shared memory.
+  const int pair = in_block == 2 ? 2 : 1;
+  const uint32_t crank = pair == 2 ? ad_cluster_rank() : 0u;
+  const int item = in_block ? (int)blockIdx.x / pair : 0;
+  const int t_blk = item / nkv, g_blk = item % nkv;
   if (in_block) {
-    i0 = base_of(t_blk, g_blk) + warp;
-    i1 = warp < chunks_of(t_blk) ? i0 + 1 : i0;
+    const int mine = (int)crank * AD_WARPS + warp;       // this warp's chunk of the item
+    i0 = base_of(t_blk, g_blk) + mine;
+    i1 = mine < chunks_of(t_blk) ? i0 + 1 : i0;
   }
   // in_block: chunk sp's record lies at the start of warp sp's ring of pages, which that warp no longer needs
   // when it has walked its chunk
@@ -765,7 +788,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             dst[16 * d + gl + 8] = __float2bfloat16(o[c][d][h + 2] * inv);
           }
         } else {
-          float* sc = in_block ? rec_blk + sp * REC_BLK_STRIDE + n * rec
+          float* sc = in_block ? rec_blk + (sp % AD_WARPS) * REC_BLK_STRIDE + n * rec
                                : scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
 #pragma unroll
           for (int d = 0; d < NJ; ++d) {
@@ -801,19 +824,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         if (!ad_mbar_wait(bars + cn % AD_STAGES, (cn / AD_STAGES) & 1)) break;
       }
     }
-    __syncthreads();                                     // every warp comes here, whatever its share and its outcome
+    // every warp comes here, whatever its share and its outcome
+    if (pair == 2) ad_cluster_sync(); else __syncthreads();
     const int n_rec = chunks_of(t_blk);
-    if (n_rec > 1 && !copier) {
+    if (n_rec > 1 && !copier && crank == 0) {
+      // chunks 4 .. 7 lie in the cluster's other block (fetching them all in one trip before the merge, instead of
+      // a remote read per use, changed nothing: 13.5 against 13.4 us)
+      auto rec_at = [&](const float* hb, int s2, int d) {
+        const float* p = hb + (s2 % AD_WARPS) * REC_BLK_STRIDE + d;
+        return s2 < AD_WARPS ? *p : ad_ld_peer(p, 1);
+      };
       // the item's chunks, in chunk order; a warp takes every fourth head, a lane HD / 32 features
       for (int n = warp; n < G; n += AD_WARPS) {
         const float* hb = rec_blk + n * rec;
         float M = -INFINITY;
-        for (int s2 = 0; s2 < n_rec; ++s2) M = fmaxf(M, hb[s2 * REC_BLK_STRIDE + HD]);
-        float w[AD_WARPS], ll = 0.0f;
+        for (int s2 = 0; s2 < n_rec; ++s2) M = fmaxf(M, rec_at(hb, s2, HD));
+        float w[2 * AD_WARPS], ll = 0.0f;
 #pragma unroll
-        for (int s2 = 0; s2 < AD_WARPS; ++s2) {
-          w[s2] = s2 < n_rec ? ad_exp2(hb[s2 * REC_BLK_STRIDE + HD] - M) : 0.0f;
-          ll += s2 < n_rec ? hb[s2 * REC_BLK_STRIDE + HD + 1] * w[s2] : 0.0f;
+        for (int s2 = 0; s2 < 2 * AD_WARPS; ++s2) {
+          w[s2] = s2 < n_rec ? ad_exp2(rec_at(hb, s2, HD) - M) : 0.0f;
+          ll += s2 < n_rec ? rec_at(hb, s2, HD + 1) * w[s2] : 0.0f;
         }
         __nv_bfloat16* dst = out + ((int64_t)t_blk * nh + g_blk * G + n) * HD;
 #pragma unroll
@@ -821,11 +851,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
           const int d = e * 32 + lane;
           float acc = 0.0f;
 #pragma unroll
-          for (int s2 = 0; s2 < AD_WARPS; ++s2) acc += s2 < n_rec ? hb[s2 * REC_BLK_STRIDE + d] * w[s2] : 0.0f;
+          for (int s2 = 0; s2 < 2 * AD_WARPS; ++s2) acc += s2 < n_rec ? rec_at(hb, s2, d) * w[s2] : 0.0f;
           dst[d] = __float2bfloat16(acc / ll);
         }
       }
     }
+    if (pair == 2) ad_cluster_sync();                    // the other block's records stay until they are read
   } else if (copier) {
     // nothing left to do: the ring's copies are asked for, and the computing warp waits for each of them
   } else if (ok) {
@@ -923,8 +954,9 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
                                 int write_new, int head_split, int in_block, cudaStream_t stream) {
   if (T == 0) return 0;
-  if (in_block && (max_splits < 1 || max_splits > AD_WARPS)) {
-    set_error("attn_decode: a block merges at most %d chunks of a (token, group of heads) itself, got %d", AD_WARPS, max_splits);
+  if (in_block < 0 || in_block > 2 || (in_block && (max_splits < 1 || max_splits > in_block * AD_WARPS))) {
+    set_error("attn_decode: in_block is 0, 1 (a block merges up to %d chunks of a (token, group of heads) itself) or 2 "
+              "(a cluster of two blocks, up to %d); got %d with %d chunks", AD_WARPS, 2 * AD_WARPS, in_block, max_splits);
     return ERR_BAD_ARGUMENT;
   }
   if (head_split < 1 || head_split > AD_MAX_GROUP || nkv < 1 || nh % nkv != 0 || (nh / nkv) % head_split != 0) {
@@ -981,15 +1013,16 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
     set_error("attn_decode: %d tokens x %d groups of heads exceed the %d merge counters", T, groups, AD_COUNTER_SLOTS);
     return ERR_UNSUPPORTED;
   }
-  const int blocks = in_block ? T * groups : (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
+  const int blocks = in_block ? T * groups * (in_block == 2 ? 2 : 1) : (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
   int* counters = max_splits > 1 && !in_block ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 && !in_block ? scratch + AD_COUNTER_SLOTS : nullptr;
 #define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
-  launch_pdl(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_THREADS), (size_t)AD_SMEM, stream, map_k, map_v,     \
+  launch_pdl_clusters(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_THREADS), in_block == 2 ? 2u : 1u,        \
+             (size_t)AD_SMEM, stream, map_k, map_v,                                                                \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
-             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split, in_block ? 1 : 0)
+             static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split, in_block)
   const bool wide = nh / groups > 8;                       // more than one block of 8 query heads per group
   if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2); else EXL3_AD_LAUNCH(64, 1); }
   else { if (wide) EXL3_AD_LAUNCH(128, 2); else EXL3_AD_LAUNCH(128, 1); }

@@ -170,4 +170,25 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);     // errors are read by launch_status()
 }
 
+// The same with the grid's blocks in thread-block clusters of `cluster` along x.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster, size_t smem,
+                                cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);     // errors are read by launch_status()
+}
+
 }  // namespace exl3

@@ -539,7 +539,7 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
                 kv_heads: int, head_dim: int, page: int, window: int, scale: float, split_keys: int,
                 max_splits: int, scratch: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor] = None,
                 rot: int = 0, pos_scale: float = 1.0, write_new: bool = False, head_split: int = 1,
-                in_block: bool = False) -> torch.Tensor:
+                in_block: int = 0) -> torch.Tensor:
     """Attention of T query tokens over the paged cache on the tensor cores (see attention_decode.cu);
     arguments and scratch as ``attn_tokens``.  With ``write_new``, ``q`` is the fused q|k|v output of the
     projection, every token is its sequence's only new one and the cache holds the positions before it: the
@@ -547,9 +547,10 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     ``head_dim`` it applies the half-split rotary encoding (``inv_freq``: head_dim / 2 float32 frequencies, or a ``rotary_table``) to
     the queries and the new key.  ``head_split`` n (a divisor of the query heads per kv head) makes n groups of work
     of a kv head's query heads: n times the work items, each merge an n-th of the size; changes no result.
-    ``in_block``: one block per (token, group of heads), whose four warps take the item's chunks (``max_splits`` at
-    most 4) and merge them in shared memory: no scratch, no tickets; results differ from the other way's by
-    rounding (another order of the same sums)."""
+    ``in_block`` 1 (or True): one block per (token, group of heads), whose four warps take the item's chunks
+    (``max_splits`` at most 4) and merge them in shared memory; 2: a cluster of two blocks per item (at most 8
+    chunks; the first block merges and reads the second one's records out of its shared memory): no scratch, no
+    tickets; results differ from the other way's by rounding (another order of the same sums)."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
@@ -566,7 +567,7 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T), _c_int(heads),
         _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
         _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), hi, lo, _c_int(rot),
-        _c_float(pos_scale), _c_int(1 if write_new else 0), _c_int(head_split), _c_int(1 if in_block else 0),
+        _c_float(pos_scale), _c_int(1 if write_new else 0), _c_int(head_split), _c_int(int(in_block)),
         _stream()), "attn_decode")
     return out
 

@@ -249,29 +249,34 @@ class Attention:
         return best
 
     def _decode_split(self, T: int, max_kv_len: int, page: int, device: torch.device):
-        """``(keys per chunk, head_split, in_block)`` for the tensor-core decode kernel: chunks of whole pages (a
-        power of two of them, at most 64 of 16 KB), into how many groups of work the query heads of a kv head are cut
+        """``(keys per chunk, head_split, in_block)`` (``in_block``: 0, 1 or 2) for the tensor-core decode kernel:
+        chunks of whole pages (a power of two of them, at most 64 of 16 KB), into how many groups of work the query
+        heads of a kv head are cut
         (``head_split``: that many times the work items, each merge that much smaller, the keys and values read
         again from L2), and whether a block takes a whole (token, group of heads) and merges its up to four chunks in
         shared memory (``in_block``) instead of warps taking equal shares of all chunks and merging through global
         memory.  By a small model of the kernel's time, its constants fitted to a sweep of every chunking at four
         head layouts (36/36 x 64, 16/2 x 64, 32/8 x 128, 32/2 x 128), contexts of 128 to 16,384 tokens and batches of
-        1 to 64 (some 4,000 timings; what the model picks is 1.6 % slower in the mean than the best of a case, and
-        more than 10 % slower in 3 of 137 cases): 5.5 us to start; a warp walks its chunk at 0.6 us per 16 KB of keys
-        and values (0.9 us with more than 8 query heads in its group: two blocks of instruction columns); when there
-        are more chunks than warps a warp takes several in turn; all warps together cannot read faster than the
-        memory does (6.6 TB/s for what is read once, 12 TB/s from L2 for what the groups of a kv head read again);
-        and the chunks of a (token, group of heads), when there is more than one, are merged by a single warp:
-        3.5 us, plus per chunk 0.03 us and 0.05 us for every head of the group, 1 % more for every group that merges
-        at the same time.  So wide groups of heads in small batches are cut into many narrow ones with a fair number
-        of chunks each, one chunk wins for short contexts and for batches with a warp's worth of work per sequence
-        (no merge at all), and many short chunks only where they are needed to give every SM work.  A block per
-        item costs, for every round of as many blocks as the GPU has SMs, 5 us (start and the merge in shared
-        memory) and its walk (a quarter of the keys per warp), and not less than the memory's time, which its rounds
-        stream some 5 % faster at the price of 1 us between rounds; it is taken when that is below 0.95 of the other
-        way's cost: for up to about as many items as the GPU has SMs, each too long for one warp, and for several
-        rounds of long items, not for many rounds of short ones.  The choice depends on the step's size, not on a
-        token's position: results differ between batch sizes by rounding."""
+        1 to 64 (some 5,000 timings; what the model picks is 0.9 % slower in the mean than the best of a case):
+        6 us to start; a warp walks its chunk at 0.55 us per 16 KB of keys and values (0.9 us with more than 8 query
+        heads in its group: two blocks of instruction columns); when there are more chunks than warps a warp takes
+        several in turn; all warps together cannot read faster than the memory does (6.6 TB/s for what is read once,
+        12 TB/s from L2 for what the groups of a kv head read again); and the chunks of a (token, group of heads),
+        when there is more than one, are merged by a single warp: 3 us, plus per chunk 0.03 us and 0.04 us for every
+        head of the group, 2 % more for every group that merges at the same time.  So wide groups of heads in small
+        batches are cut into many narrow ones with a fair number of chunks each, one chunk wins for short contexts
+        and for batches with a warp's worth of work per sequence (no merge at all), and many short chunks only where
+        they are needed to give every SM work.  A block per item costs, for every round of as many blocks as the GPU
+        has SMs, 5.5 us and 0.1 us a head of the group (start and the merge in shared memory) and its walk (a
+        quarter of the keys per warp), and not less than the memory's time, which its rounds stream some 5 % faster
+        at the price of 1 us between rounds; it is taken when that is below 0.95 of the other way's cost: for up to
+        about as many items as the GPU has SMs, each too long for one warp, and for several rounds of long items,
+        not for many rounds of short ones.  A cluster of two blocks per item (``in_block`` 2: eight warps, five to
+        eight chunks, merged by the first block) costs 7 us and 0.1 us a head, an eighth of the keys' walk, and 3 us
+        between rounds of half as many clusters as the GPU has SMs: for one sequence of 36 heads at 4,096 tokens
+        13.6 us against 14.9 us with a block per item, at 8,192 tokens 19.0 against 23.1; for 8 sequences of 2 kv
+        heads with 16 query heads each at 2,048 tokens 14.4 against 16.0.  The choice depends on the step's
+        size, not on a token's position: results differ between batch sizes by rounding."""
         s = self.spec
         keys = min(max_kv_len, s.window) if s.window > 0 else max_kv_len
         pages_seq = max(1, (keys + page - 1) // page)
@@ -287,7 +292,7 @@ class Attention:
             g = group // head_split
             if g > 16:
                 continue
-            stage_us = 0.6 if g <= 8 else 0.9
+            stage_us = 0.55 if g <= 8 else 0.9
             groups = T * s.kv_heads * head_split
             once_us = T * s.kv_heads * pages_seq * wide * 16384 / 6.6e6
             again_us = groups * pages_seq * wide * 16384 / 12.0e6
@@ -296,17 +301,25 @@ class Attention:
                 n = (pages_seq + per - 1) // per
                 if n + (1 if s.window > 0 else 0) <= K.ATTN_DECODE_MAX_CHUNKS:     # a window may straddle one chunk more
                     rounds = (groups * n + warps - 1) // warps
-                    cost = 5.5 + max(rounds * per * wide * stage_us, once_us, again_us)
+                    cost = 6.0 + max(rounds * per * wide * stage_us, once_us, again_us)
                     if n > 1:
-                        cost += 3.5 + n * (0.03 + 0.05 * g) * (1.0 + 0.01 * groups)
+                        cost += 3.0 + n * (0.03 + 0.04 * g) * (1.0 + 0.02 * groups)
                     if best is None or cost < best[0] - 1e-9:
-                        best = (cost, per, head_split, False)
+                        best = (cost, per, head_split, 0)
                     if 1 < n + (1 if s.window > 0 else 0) <= 4:
                         rounds = (groups + sms - 1) // sms
-                        cost = max(rounds * (5.0 + per * wide * stage_us),
-                                   5.0 + max(once_us, again_us) / 1.05 + 1.0 * (rounds - 1))
+                        fixed = 5.5 + 0.1 * g                                # start, and a warp merges a head at a time
+                        cost = max(rounds * (fixed + per * wide * stage_us),
+                                   fixed + max(once_us, again_us) / 1.05 + 1.0 * (rounds - 1))
                         if best_blk is None or cost < best_blk[0] - 1e-9:
-                            best_blk = (cost, per, head_split, True)
+                            best_blk = (cost, per, head_split, 1)
+                    elif 4 < n + (1 if s.window > 0 else 0) <= 8:
+                        rounds = (groups + sms // 2 - 1) // (sms // 2)       # clusters of two, a block an SM
+                        fixed = 7.0 + 0.1 * g
+                        cost = max(rounds * (fixed + per * wide * stage_us),
+                                   fixed + max(once_us, again_us) / 1.05 + 3.0 * (rounds - 1))
+                        if best_blk is None or cost < best_blk[0] - 1e-9:
+                            best_blk = (cost, per, head_split, 2)
                 if per >= pages_seq or per * wide >= 64:
                     break
                 per *= 2

@@ -686,9 +686,49 @@ def test_attn_decode_merges_in_the_block(nh, nkv, hd, window, split):
             close(out, through_memory.double(), 1e-2, "the two ways of merging")
     assert K().attn_decode_status() == 0
     from exl3_server_b200.ops.lib import KernelLibraryError
-    with pytest.raises(KernelLibraryError, match="at most 4 chunks"):
+    with pytest.raises(KernelLibraryError, match="up to 4 chunks"):
         K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
                         nh, nkv, hd, 64, 0, scale, 64, 16, None, in_block=True)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 4, 64), (16, 2, 64), (32, 2, 128), (12, 4, 128), (36, 36, 64)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("split", [128, 256])
+def test_attn_decode_merges_in_a_cluster_of_two_blocks(nh, nkv, hd, window, split):
+    """A cluster of two blocks per (token, group of heads): eight warps take the item's up to eight chunks, and the
+    first block merges them, reading the second one's records out of its shared memory.  Sequences with one to eight
+    chunks (the ones with at most four leave the second block nothing to do), against the reference and against
+    the merge through global memory."""
+    lens = [1000, 64, 1, 700, 257, 256, 513, 1024, 769, 2 * split + 1, 6 * split]
+    lens = [min(n, 8 * split) for n in lens]
+    new = [1, 1, 1, 2, 1, 1, 1, 1, 1, 1, 1]
+    case = PagedCase(lens=lens, new=new, nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16, seed=nh + split + 1)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    scale = 0.7 / math.sqrt(hd)
+    n = (max(lens) + split - 1) // split
+    if window > 0:
+        n = min(n, (window + split - 2) // split + 1)
+    assert n <= 8
+    scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+    want = case.reference(window, scale)
+    through_memory = torch.full_like(q, 7.0)
+    K().attn_decode(q, q.stride(0), through_memory, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                    nh, nkv, hd, 64, window, scale, split, n, scratch)
+    for parts in (1, 2, 4):
+        if (nh // nkv) % parts:
+            continue
+        for _ in range(2):
+            out = torch.full_like(q, 7.0)
+            K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                            nh, nkv, hd, 64, window, scale, split, n, None, head_split=parts, in_block=2)
+            close(out, want, 1e-2, f"attn_decode, merged in a cluster, {parts} groups per kv head")
+            close(out, through_memory.double(), 1e-2, "the two ways of merging")
+    assert K().attn_decode_status() == 0
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    with pytest.raises(KernelLibraryError, match="up to 8"):
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, 0, scale, 64, 16, None, in_block=2)
 
 
 @pytest.mark.parametrize("hd", [64, 128])

@@ -38,20 +38,23 @@ def test_decode_chunks_are_whole_pages_and_groups_divide_the_heads(heads, kv_hea
             assert (heads // kv_heads) % head_split == 0 and (heads // kv_heads) // head_split <= 16
             n = a._chunks(keys, split)
             assert 1 <= n <= K.ATTN_DECODE_MAX_CHUNKS
+            assert in_block in (0, 1, 2)
             if in_block:
-                assert n <= 4                              # a block merges at most four chunks of an item itself
+                assert n <= 4 * in_block                   # a block merges four chunks of an item itself, a cluster eight
 
 
 def test_decode_choices_at_sizes_that_were_measured():
     two_b = mixer(36, 36, 64)
-    assert two_b._decode_split(1, 4096, 64, None) == (1024, 1, True)     # 36 blocks, four chunks each: 14.5 us
-    assert two_b._decode_split(8, 4096, 64, None) == (4096, 1, False)    # a warp per (token, head), no merge
-    assert two_b._decode_split(4, 4096, 64, None) == (1024, 1, True)     # 144 blocks, four chunks each
-    assert two_b._decode_split(8, 16384, 64, None) == (4096, 1, True)    # two rounds of long items
-    assert two_b._decode_split(64, 512, 64, None)[2] is False            # sixteen rounds of short ones
+    assert two_b._decode_split(1, 4096, 64, None) == (512, 1, 2)         # 36 clusters, eight chunks each: 13.6 us
+    assert two_b._decode_split(1, 8192, 64, None) == (1024, 1, 2)        # 19.0 us against 23.1 with a block an item
+    assert two_b._decode_split(8, 4096, 64, None) == (4096, 1, 0)        # a warp per (token, head), no merge
+    assert two_b._decode_split(4, 4096, 64, None) == (1024, 1, 1)        # 144 blocks, four chunks each
+    assert two_b._decode_split(8, 16384, 64, None) == (4096, 1, 1)       # two rounds of long items
+    assert two_b._decode_split(64, 512, 64, None)[2] == 0                # sixteen rounds of short ones
     eight_b = mixer(32, 2, 128)
-    assert eight_b._decode_split(1, 2048, 64, None) == (128, 16, False)  # every query head a group of its own
-    assert eight_b._decode_split(64, 2048, 64, None) == (512, 1, True)
+    assert eight_b._decode_split(1, 2048, 64, None) == (256, 16, 2)      # every query head a group of its own
+    assert eight_b._decode_split(8, 2048, 64, None) == (256, 2, 2)       # 14.4 us against 16.0 with a block an item
+    assert eight_b._decode_split(64, 2048, 64, None) == (512, 1, 1)
 
 
 def test_prompt_kernel_form():
