@@ -114,7 +114,9 @@ int exl3_gemm_pair_ss_blocks(int N);
 // them to the cache itself.  head_split n (a divisor of the query heads per kv head): the query heads of a kv head
 // as n groups of work.  in_block 1: a block per (token, group of heads), whose warps take the item's chunks (at most
 // 4) and merge them in shared memory; 2: a cluster of two blocks (at most 8 chunks, the first block merging, the
-// second one's records read out of its shared memory); no scratch in either.  See attention_decode.cu.
+// second one's records read out of its shared memory); no scratch in either.  twins 2 (with in_block 1 or 2, an even
+// head_split and groups of up to 8 heads): two groups of query heads of a kv head per block, walking the same pages
+// out of the same rings, 8 computing warps.  See attention_decode.cu.
 int exl3_attn_decode_supported(int dtype, int T, int nh, int nkv, int hd, int page, int split_keys, int max_splits);
 int exl3_attn_decode_status();
 int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_pool, void* v_pool,
@@ -122,7 +124,7 @@ int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, void* k_poo
                      const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window, float scale,
                      int split_keys, int max_splits, float* scratch, size_t scratch_bytes, const float* inv_freq,
                      const float* inv_freq_lo, int rot, float pos_scale, int write_new, int head_split, int in_block,
-                     cudaStream_t stream);
+                     int twins, cudaStream_t stream);
 
 int exl3_argmax(const float* logits, int* out, int R, int V, void* scratch, size_t scratch_bytes,
                 cudaStream_t stream);

@@ -61,7 +61,7 @@
 namespace exl3 {
 
 constexpr int AD_WARPS = 4;                                // warps that compute; each has a warp that copies for it
-constexpr int AD_THREADS = 2 * AD_WARPS * 32;
+constexpr int AD_MAX_TWINS = 2;                            // computing warps that share a ring (see TW below)
 constexpr int AD_PAGE = 64;
 constexpr int AD_MAX_GROUP = 16;                           // query heads per kv head: one or two blocks of 8 instruction columns
 // A stage holds the keys, then the values, of one page of one kv head (heads of 64) or of half a page (heads of
@@ -178,8 +178,12 @@ __device__ inline uint32_t ad_pack(float lo, float hi) {
 // behind, and one fence at the end of the warp's work covers them all before it draws tickets.
 // NC: blocks of 8 query heads of a kv head's group (the columns of an instruction): 1 for groups of up to 8, 2 for
 // up to 16.  Both blocks use the same key and value fragments, so a page is read from shared memory once.
-template <int HD, int NC>
-__global__ void __launch_bounds__(AD_THREADS, 1)
+// TW: computing warps of a ring.  With TW = 2 (in_block forms, NC = 1, kv_rep even) a block takes two groups of query
+// heads of the same kv head: warp w and warp AD_WARPS + w walk the same chunk out of the same ring of pages, each
+// with its own group's queries, so that a page comes into shared memory once for both and a scheduler has two
+// warps to issue from.  A stage is free when both have read it (the barrier counts TW arrivals).
+template <int HD, int NC, int TW>
+__global__ void __launch_bounds__((TW + 1) * AD_WARPS * 32, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, __nv_bfloat16* __restrict__ out,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
@@ -205,19 +209,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   __shared__ int s_pos[AD_MAX_TOKENS], s_seq[AD_MAX_TOKENS];
   __shared__ int s_cum[AD_MAX_TOKENS + 1];               // chunks of the tokens before this one (per kv head)
   __shared__ float s_w[AD_WARPS][AD_MAX_SPLITS], s_l[AD_WARPS][AD_MAX_SPLITS];   // a merge's weights and sums
-  __shared__ __align__(16) float2 s_rot[AD_WARPS][64];   // a token's rotary angles (cos, sin), one table per warp
-  // Warps 0 .. AD_WARPS - 1 compute; warp AD_WARPS + w asks for the copies into warp w's ring (asked for by the
-  // computing warp itself, between two stages, they took 200 to 400 of a stage's 1,100 to 1,300 cycles).
+  __shared__ __align__(16) float2 s_rot[TW * AD_WARPS][64];   // a token's rotary angles (cos, sin), one table per computing warp
+  // Warps 0 .. TW * AD_WARPS - 1 compute (warp w and, with TW = 2, warp AD_WARPS + w on ring w); the last AD_WARPS
+  // warps ask for the copies into the rings (asked for by the computing warp itself, between two stages, they took
+  // 200 to 400 of a stage's 1,100 to 1,300 cycles).
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warp = wid % AD_WARPS;                       // the ring, and its computing warp
-  const bool copier = wid >= AD_WARPS;
+  const int warp = wid % AD_WARPS;                       // the ring
+  const bool copier = wid >= TW * AD_WARPS;
+  const int tw = copier ? 0 : wid / AD_WARPS;            // which of the ring's computing warps
   const int gl = lane >> 2, tl = lane & 3;
   const int kv_heads = nkv / kv_rep;                     // key/value heads in the cache
   const uint32_t ring = ((ad_smem_u32(ad_smem_raw) + 1023u) & ~1023u) + warp * (AD_STAGES * AD_STAGE_BYTES);
   uint64_t* bars = full[warp];
   uint64_t* gone = empty[warp];
-  if (lane == 0 && !copier) {
-    for (int s = 0; s < AD_STAGES; ++s) { ad_mbar_init(bars + s, 1); ad_mbar_init(gone + s, 1); }
+  if (lane == 0 && wid < AD_WARPS) {
+    for (int s = 0; s < AD_STAGES; ++s) { ad_mbar_init(bars + s, 1); ad_mbar_init(gone + s, TW); }
     s_asked[warp] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -275,7 +281,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int pair = in_block == 2 ? 2 : 1;
   const uint32_t crank = pair == 2 ? ad_cluster_rank() : 0u;
   const int item = in_block ? (int)blockIdx.x / pair : 0;
-  const int t_blk = item / nkv, g_blk = item % nkv;
+  const int t_blk = item / (nkv / TW), g_blk = item % (nkv / TW) * TW + tw;   // a ring's copier: as its first computing warp
   if (in_block) {
     const int mine = (int)crank * AD_WARPS + warp;       // this warp's chunk of the item
     i0 = base_of(t_blk, g_blk) + mine;
@@ -428,7 +434,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   // pieces j and j + NJ / 2.
   // A token's HD / 2 angles are computed once, two or so per lane, and kept in the warp's table (cos, sin):
   // the token's query heads of every kv head and its own key all turn by them.
-  float2* rot_tab = s_rot[warp];
+  float2* rot_tab = s_rot[copier ? 0 : wid];
   int rot_t = -1;                                        // the token whose angles the table holds
   auto angles_of = [&](int t) {
     if (t == rot_t) return;
@@ -708,6 +714,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (lane == 0) ad_mbar_arrive(gone + st);          // its copier may ask for the stage AD_STAGES ahead
       ++cn;
     }
+    // the ring's other computing warp may still read the stage where this one's record goes
+    if (TW == 2) asm volatile("bar.sync %0, 64;" ::"r"(1 + warp) : "memory");
     if (!ok) break;
     if (has_new) {
       if (rotate) rotate_at(t, kf);
@@ -788,7 +796,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             dst[16 * d + gl + 8] = __float2bfloat16(o[c][d][h + 2] * inv);
           }
         } else {
-          float* sc = in_block ? rec_blk + (sp % AD_WARPS) * REC_BLK_STRIDE + n * rec
+          float* sc = in_block ? rec_blk + (sp % AD_WARPS) * REC_BLK_STRIDE + (tw * G + n) * rec
                                : scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
 #pragma unroll
           for (int d = 0; d < NJ; ++d) {
@@ -836,7 +844,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       };
       // the item's chunks, in chunk order; a warp takes every fourth head, a lane HD / 32 features
       for (int n = warp; n < G; n += AD_WARPS) {
-        const float* hb = rec_blk + n * rec;
+        const float* hb = rec_blk + (tw * G + n) * rec;
         float M = -INFINITY;
         for (int s2 = 0; s2 < n_rec; ++s2) M = fmaxf(M, rec_at(hb, s2, HD));
         float w[2 * AD_WARPS], ll = 0.0f;
@@ -952,7 +960,7 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
                                 const int* tok_seq, int T, int nh, int nkv, int hd, int page, int window,
                                 float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
                                 const float* inv_freq, const float* inv_freq_lo, int rot, float pos_scale,
-                                int write_new, int head_split, int in_block, cudaStream_t stream) {
+                                int write_new, int head_split, int in_block, int twins, cudaStream_t stream) {
   if (T == 0) return 0;
   if (in_block < 0 || in_block > 2 || (in_block && (max_splits < 1 || max_splits > in_block * AD_WARPS))) {
     set_error("attn_decode: in_block is 0, 1 (a block merges up to %d chunks of a (token, group of heads) itself) or 2 "
@@ -961,6 +969,12 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   }
   if (head_split < 1 || head_split > AD_MAX_GROUP || nkv < 1 || nh % nkv != 0 || (nh / nkv) % head_split != 0) {
     set_error("attn_decode: head_split must divide the %d query heads of a kv head; got %d", nkv > 0 ? nh / nkv : 0, head_split);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (twins != 1 && (twins != AD_MAX_TWINS || !in_block || head_split % twins != 0 || nh / (nkv * head_split) > 8)) {
+    set_error("attn_decode: twins is 1 or %d (two groups of up to 8 query heads of a kv head in one block: in_block 1 or 2 "
+              "and an even head_split); got %d with in_block %d, head_split %d, %d heads a group", AD_MAX_TWINS, twins,
+              in_block, head_split, nh / (nkv * head_split));
     return ERR_BAD_ARGUMENT;
   }
   if (nh < 1 || nkv < 1 || window < 0 || !(scale > 0.0f) ||
@@ -986,13 +1000,17 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
   }
   static int sms = 0;
   if (!sms) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+      e = cudaFuncSetAttribute(attn_decode_kernel<128, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+      e = cudaFuncSetAttribute(attn_decode_kernel<64, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_decode_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+      e = cudaFuncSetAttribute(attn_decode_kernel<128, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_kernel<64, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_kernel<128, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AD_SMEM);
     if (e != cudaSuccess) { set_error("attn_decode: cannot get %u bytes of shared memory: %s", AD_SMEM, cudaGetErrorString(e)); return (int)e; }
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1013,19 +1031,21 @@ extern "C" int exl3_attn_decode(const void* q, int64_t q_row_stride, void* out, 
     set_error("attn_decode: %d tokens x %d groups of heads exceed the %d merge counters", T, groups, AD_COUNTER_SLOTS);
     return ERR_UNSUPPORTED;
   }
-  const int blocks = in_block ? T * groups * (in_block == 2 ? 2 : 1) : (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
+  const int blocks = in_block ? T * (groups / twins) * (in_block == 2 ? 2 : 1)
+                              : (int)std::min<int64_t>(sms, (int64_t)T * groups * max_splits);
   int* counters = max_splits > 1 && !in_block ? reinterpret_cast<int*>(scratch) : nullptr;
   float* records = max_splits > 1 && !in_block ? scratch + AD_COUNTER_SLOTS : nullptr;
-#define EXL3_AD_LAUNCH(HD_, NC_)                                                                                  \
-  launch_pdl_clusters(attn_decode_kernel<HD_, NC_>, dim3(blocks), dim3(AD_THREADS), in_block == 2 ? 2u : 1u,        \
+#define EXL3_AD_LAUNCH(HD_, NC_, TW_)                                                                             \
+  launch_pdl_clusters(attn_decode_kernel<HD_, NC_, TW_>, dim3(blocks), dim3((TW_ + 1) * AD_WARPS * 32),            \
+             in_block == 2 ? 2u : 1u,                                                                              \
              (size_t)AD_SMEM, stream, map_k, map_v,                                                                \
              static_cast<const __nv_bfloat16*>(q), q_row_stride, static_cast<__nv_bfloat16*>(out), block_table,  \
              bt_stride, tok_pos, tok_seq, T, nh, groups, window, scale * 1.4426950408889634f, split_keys,        \
              max_splits, records, counters, inv_freq, inv_freq_lo, pos_scale, rot != 0 ? 1 : 0, write_new ? 1 : 0,            \
              static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), head_split, in_block)
   const bool wide = nh / groups > 8;                       // more than one block of 8 query heads per group
-  if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2); else EXL3_AD_LAUNCH(64, 1); }
-  else { if (wide) EXL3_AD_LAUNCH(128, 2); else EXL3_AD_LAUNCH(128, 1); }
+  if (hd == 64) { if (wide) EXL3_AD_LAUNCH(64, 2, 1); else if (twins == 2) EXL3_AD_LAUNCH(64, 1, 2); else EXL3_AD_LAUNCH(64, 1, 1); }
+  else { if (wide) EXL3_AD_LAUNCH(128, 2, 1); else if (twins == 2) EXL3_AD_LAUNCH(128, 1, 2); else EXL3_AD_LAUNCH(128, 1, 1); }
 #undef EXL3_AD_LAUNCH
   return launch_status("attn_decode");
 }

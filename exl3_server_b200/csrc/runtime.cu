@@ -40,7 +40,7 @@ int launch_status(const char* what) {
 }  // namespace exl3
 
 extern "C" const char* exl3_last_error() { return exl3::g_error; }
-extern "C" int exl3_abi_version() { return 4; }
+extern "C" int exl3_abi_version() { return 5; }
 // Kernel launches made through this library since it was loaded (launches
 // recorded into a CUDA graph count once, when they are captured).
 extern "C" long long exl3_launch_count() { return exl3::g_launches.load(std::memory_order_relaxed); }

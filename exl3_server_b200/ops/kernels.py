@@ -539,7 +539,7 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
                 kv_heads: int, head_dim: int, page: int, window: int, scale: float, split_keys: int,
                 max_splits: int, scratch: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor] = None,
                 rot: int = 0, pos_scale: float = 1.0, write_new: bool = False, head_split: int = 1,
-                in_block: int = 0) -> torch.Tensor:
+                in_block: int = 0, twins: int = 1) -> torch.Tensor:
     """Attention of T query tokens over the paged cache on the tensor cores (see attention_decode.cu);
     arguments and scratch as ``attn_tokens``.  With ``write_new``, ``q`` is the fused q|k|v output of the
     projection, every token is its sequence's only new one and the cache holds the positions before it: the
@@ -550,7 +550,9 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
     ``in_block`` 1 (or True): one block per (token, group of heads), whose four warps take the item's chunks
     (``max_splits`` at most 4) and merge them in shared memory; 2: a cluster of two blocks per item (at most 8
     chunks; the first block merges and reads the second one's records out of its shared memory): no scratch, no
-    tickets; results differ from the other way's by rounding (another order of the same sums)."""
+    tickets; results differ from the other way's by rounding (another order of the same sums).  ``twins`` 2 (with
+    ``in_block`` 1 or 2, an even ``head_split`` and groups of up to 8 heads): a block takes two groups of query heads
+    of a kv head, whose warps walk the same pages out of the same rings; changes no result."""
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_decode: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
@@ -568,7 +570,7 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
         _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale), _c_int(split_keys),
         _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), hi, lo, _c_int(rot),
         _c_float(pos_scale), _c_int(1 if write_new else 0), _c_int(head_split), _c_int(int(in_block)),
-        _stream()), "attn_decode")
+        _c_int(int(twins)), _stream()), "attn_decode")
     return out
 
 

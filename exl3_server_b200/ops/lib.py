@@ -30,7 +30,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
 ]
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 class KernelLibraryError(RuntimeError):

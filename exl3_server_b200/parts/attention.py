@@ -136,6 +136,7 @@ class Attention:
         if not self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             return False
         split, head_split, in_block = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+        head_split, twins = self._decode_twins(head_split, in_block)
         n = self._chunks(batch.max_kv_len, split)
         scratch = None
         if n > 1 and not in_block:
@@ -143,7 +144,7 @@ class Attention:
         K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                       s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
                       inv_freq=inv_freq, rot=rot, pos_scale=pos_scale, write_new=kv.owns, head_split=head_split,
-                      in_block=in_block)
+                      in_block=in_block, twins=twins)
         return True
 
     def _decode_kernel_takes(self, dtype: torch.dtype, T: int, page: int) -> bool:
@@ -169,13 +170,14 @@ class Attention:
         if self._decode_kernel_takes(qkv.dtype, T, kv.page_size):
             # decoded tokens, heads of 64 or 128: pages by TMA, both products on the tensor cores, a warp per chunk
             split, head_split, in_block = self._decode_split(T, batch.max_kv_len, kv.page_size, qkv.device)
+            head_split, twins = self._decode_twins(head_split, in_block)
             n = self._chunks(batch.max_kv_len, split)
             scratch = None
             if n > 1 and not in_block:
                 scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, s.heads, s.head_dim, n) // 4)
             K.attn_decode(qkv, qkv.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T,
                           s.heads, s.kv_heads, s.head_dim, kv.page_size, s.window, self.scale, split, n, scratch,
-                          head_split=head_split, in_block=in_block)
+                          head_split=head_split, in_block=in_block, twins=twins)
             return
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:
@@ -326,6 +328,18 @@ class Attention:
         if best_blk is not None and best_blk[0] < 0.95 * best[0]:
             best = best_blk
         return page * best[1], best[2], best[3]
+
+    def _decode_twins(self, head_split: int, in_block: int):
+        """``(head_split, twins)``: where a block (or a cluster) per item would take a group of 10 to 16 query heads
+        as two blocks of instruction columns in one warp, the group is cut in two and the halves go to two warps
+        that walk the same pages out of the same ring (``twins`` 2): the same work on twice the warps.  The matrix
+        instruction is what such a warp waits for (some 22 to 25 cycles each, 128 of them for 16 KB of keys and
+        values of 16 heads of 128); 64 sequences of 2,048 tokens with 32 query heads on 2 kv heads of 128: 32.0
+        against 33.4 us, of 4,096 tokens 50.6 against 52.5, of 512 tokens 15.8 against 16.8."""
+        g = self.spec.heads // self.spec.kv_heads // head_split
+        if in_block and g > 8 and g % 2 == 0:
+            return 2 * head_split, 2
+        return head_split, 1
 
     def _chunks(self, max_kv_len: int, split: int) -> int:
         """The most chunks of ``split`` keys that a token's keys can touch."""

@@ -731,6 +731,50 @@ def test_attn_decode_merges_in_a_cluster_of_two_blocks(nh, nkv, hd, window, spli
                         nh, nkv, hd, 64, 0, scale, 64, 16, None, in_block=2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(16, 2, 64), (32, 2, 128), (12, 2, 128), (8, 1, 64), (4, 2, 64), (16, 1, 128)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("in_block", [1, 2])
+def test_attn_decode_with_two_groups_of_heads_walking_the_same_pages(nh, nkv, hd, window, in_block):
+    """Two groups of query heads of a kv head in one block, their warps reading the same rings of pages: the very
+    numbers that a block per group gives, and the reference's."""
+    split = 128
+    lens = [1000, 64, 1, 700, 257, 256, 513, 1024, 769, 2 * split + 1, 6 * split]
+    lens = [min(n, 4 * in_block * split) for n in lens]
+    case = PagedCase(lens=lens, new=[1, 1, 1, 2, 1, 1, 1, 1, 1, 1, 1], nh=nh, nkv=nkv, hd=hd, dtype=torch.bfloat16,
+                     seed=nh + hd + in_block)
+    T = case.q.shape[0]
+    q = case.q.reshape(T, nh * hd).to(DEV).contiguous()
+    scale = 0.7 / math.sqrt(hd)
+    n = (max(lens) + split - 1) // split
+    if window > 0:
+        n = min(n, (window + split - 2) // split + 1)
+    want = case.reference(window, scale)
+    group = nh // nkv
+    ran = 0
+    for parts in (2, 4, 8, 16):
+        if group % parts or group // parts > 8:
+            continue
+        outs = []
+        for twins in (1, 2, 2):
+            out = torch.full_like(q, 7.0)
+            K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                            nh, nkv, hd, 64, window, scale, split, n, None, head_split=parts, in_block=in_block,
+                            twins=twins)
+            close(out, want, 1e-2, f"{parts} groups per kv head, twins {twins}")
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+        ran += 1
+    assert ran and K().attn_decode_status() == 0
+    from exl3_server_b200.ops.lib import KernelLibraryError
+    with pytest.raises(KernelLibraryError, match="twins is 1 or 2"):
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, window, scale, split, n, None, head_split=1, in_block=in_block, twins=2)
+    with pytest.raises(KernelLibraryError, match="twins is 1 or 2"):
+        scratch = torch.zeros(K().attn_tokens_scratch_bytes(T, nh, hd, n) // 4, device=DEV)
+        K().attn_decode(q, q.stride(0), out, case.k_pool, case.v_pool, case.table, case.tok_pos, case.tok_seq, T,
+                        nh, nkv, hd, 64, window, scale, split, n, scratch, head_split=2, in_block=0, twins=2)
+
+
 @pytest.mark.parametrize("hd", [64, 128])
 def test_attn_decode_many_items_per_warp(hd):
     # more work items than the grid has warps: every warp's ring of pages runs across the ends of items,
@@ -848,11 +892,35 @@ def test_attn_decode_rotates_and_writes_the_new_token(nh, nkv, hd, window, rotar
                     inv_freq=(K().rotary_table(inv_freq) if split == 256 else inv_freq).to(DEV), rot=rot,
                     pos_scale=pos_scale, write_new=True, head_split=head_split)
     close(out, case.reference(window, scale), 1e-2, "attn_decode, own key and value")
-    for b in range(B):
-        pos = lens[b] - 1
-        pg = int(case.table[b, pos // 64])
-        close(case.k_pool[pg, :, pos % 64], case.k[b][pos], 1e-2, "key written to the cache")
-        assert torch.equal(case.v_pool[pg, :, pos % 64].cpu(), v_raw[b])
+
+    def written():
+        for b in range(B):
+            pos = lens[b] - 1
+            pg = int(case.table[b, pos // 64])
+            close(case.k_pool[pg, :, pos % 64], case.k[b][pos], 1e-2, "key written to the cache")
+            assert torch.equal(case.v_pool[pg, :, pos % 64].cpu(), v_raw[b])
+    written()
+    # the same with a block, and a cluster of two, per item; and with two groups of heads of a kv head per block
+    group = nh // nkv
+    for in_block in (1, 2):
+        if n > 4 * in_block:
+            continue
+        for twins in (1, 2):
+            parts = 2 if group % 2 == 0 else 1
+            if twins == 2 and (parts != 2 or group // parts > 8):
+                continue
+            for b in range(B):
+                pos = lens[b] - 1
+                pg = int(case.table[b, pos // 64])
+                case.k_pool[pg, :, pos % 64] = 100.0
+                case.v_pool[pg, :, pos % 64] = -100.0
+            other = torch.empty_like(out)
+            K().attn_decode(qkv, qkv.stride(0), other, case.k_pool, case.v_pool, case.table, case.tok_pos,
+                            case.tok_seq, B, nh, nkv, hd, 64, window, scale, split, n, None,
+                            inv_freq=inv_freq.to(DEV), rot=rot, pos_scale=pos_scale, write_new=True,
+                            head_split=parts, in_block=in_block, twins=twins)
+            close(other, case.reference(window, scale), 1e-2, f"in_block {in_block}, twins {twins}")
+            written()
     assert K().attn_decode_status() == 0
 
 

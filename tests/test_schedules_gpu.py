@@ -265,13 +265,14 @@ def test_a_recorded_step_runs_again_after_a_later_one_needed_more_scratch(tmp_pa
     eng.check_kernels()
 
 
-@pytest.mark.parametrize("head_dim,heads,kv_heads,short_form", [(64, 4, 2, 1), (128, 8, 1, 2)])
+@pytest.mark.parametrize("head_dim,heads,kv_heads,short_form", [(64, 4, 2, 1), (128, 8, 1, 2), (128, 32, 2, 2)])
 def test_every_way_of_merging_the_decode_attentions_chunks_is_reached_through_the_engine(head_dim, heads, kv_heads,
                                                                                           short_form, tmp_path,
                                                                                           monkeypatch):
     """One sequence of 1,500 tokens decodes in a cluster of two blocks per item and one of 200 in a block per item
     (with 8 query heads on one kv head of 128: eight groups of one head, in clusters again): the engine's own
-    choice on a GPU of 148 SMs, recorded here; 40 sequences of 300 tokens in whatever way it picks.  Every position's logits against the plain implementation."""
+    choice on a GPU of 148 SMs, recorded here; 40 sequences of 300 tokens in whatever way it picks: with 16 query
+    heads on a kv head, two groups of 8 in one block, their warps walking the same pages.  Every position's logits against the plain implementation."""
     from exl3_server_b200 import LlamaConfig, write_random_model
     from exl3_server_b200.ops import kernels as K
     cfg = LlamaConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -279,20 +280,24 @@ def test_every_way_of_merging_the_decode_attentions_chunks_is_reached_through_th
                       max_position_embeddings=4096, tie_word_embeddings=False)
     folder = write_random_model(cfg, str(tmp_path / "m"), seed=31, std=0.08, norm_std=0.1, dtype=torch.bfloat16)
     pm = PlainModel(folder)
-    seen = []
+    seen, twins = [], []
     real = K.attn_decode
 
     def spy(*args, **kw):
         seen.append(int(kw.get("in_block", 0)))
+        twins.append(int(kw.get("twins", 1)))
         return real(*args, **kw)
     monkeypatch.setattr(K, "attn_decode", spy)
     eng = engine_for(folder, "bfloat16", max_tokens=40 * 320 + 2048)
     for n, prompt, tail, form in ((1, 1500, 24, 2), (1, 200, 24, short_form), (40, 300, 4, None)):
         seen.clear()
+        twins.clear()
         reqs = random_requests(cfg.vocab_size, [prompt + tail] * n, seed=prompt)
         got = run_trace(eng, batched_trace(reqs, [list(reqs)], {r: prompt for r in reqs}))
         assert seen and (form is None or K.sm_count(torch.device("cuda:0")) != 148 or form in seen), \
             f"{n} x {prompt}: forms {sorted(set(seen))}"
+        if n == 40 and heads // kv_heads == 16 and K.sm_count(torch.device("cuda:0")) == 148:
+            assert 2 in twins
         for rid in list(reqs)[:3]:
             assert rel_err(got[rid], pm.logits(reqs[rid]).numpy()) <= TOL["bfloat16"], (n, prompt, rid)
         assert eng.cache.tokens_held() == 0

@@ -88,3 +88,14 @@ def test_a_step_lists_its_tiles_heaviest_first_with_their_keys():
     for i in range(n):
         r, a = int(seq[i]), int(q0[i])
         assert keys[i] == starts[r] + min(a + 128, counts[r])
+
+
+def test_wide_groups_in_a_block_go_to_two_warps_per_ring():
+    eight_b = mixer(32, 2, 128)
+    assert eight_b._decode_twins(1, 1) == (2, 2)       # 16 heads: two groups of 8 in one block
+    assert eight_b._decode_twins(1, 2) == (2, 2)
+    assert eight_b._decode_twins(1, 0) == (1, 1)       # warps sharing all chunks: as it was
+    assert eight_b._decode_twins(2, 1) == (2, 1)       # groups of 8 fit one warp's instruction columns
+    assert mixer(12, 1, 64)._decode_twins(1, 1) == (2, 2)
+    assert mixer(36, 36, 64)._decode_twins(1, 2) == (1, 1)
+    assert mixer(22, 2, 64)._decode_twins(1, 1) == (1, 1)      # 11 heads do not halve
