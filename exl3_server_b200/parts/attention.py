@@ -332,10 +332,10 @@ class Attention:
     def _decode_twins(self, head_split: int, in_block: int):
         """``(head_split, twins)``: where a block (or a cluster) per item would take a group of 10 to 16 query heads
         as two blocks of instruction columns in one warp, the group is cut in two and the halves go to two warps
-        that walk the same pages out of the same ring (``twins`` 2): the same work on twice the warps.  The matrix
-        instruction is what such a warp waits for (some 22 to 25 cycles each, 128 of them for 16 KB of keys and
-        values of 16 heads of 128); 64 sequences of 2,048 tokens with 32 query heads on 2 kv heads of 128: 32.0
-        against 33.4 us, of 4,096 tokens 50.6 against 52.5, of 512 tokens 15.8 against 16.8."""
+        that walk the same pages out of the same ring (``twins`` 2): the same work on twice the warps, whose chains
+        of dependent matrix instructions then overlap a little.  64 sequences of 2,048 tokens with 32 query heads
+        on 2 kv heads of 128: 32.0 against 33.4 us, of 4,096 tokens 50.6 against 52.5, of 512 tokens 15.8 against
+        16.8."""
         g = self.spec.heads // self.spec.kv_heads // head_split
         if in_block and g > 8 and g % 2 == 0:
             return 2 * head_split, 2
